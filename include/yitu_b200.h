@@ -1,0 +1,221 @@
+/*
+ * yitu_b200 — C ABI of the B200 (sm_100a) message-passing kernels that replace the CUDA
+ * extensions of CGCL-codes/YiTu on its GNN aggregation path:
+ *
+ *   YiTu_GNN.YiTu_GNN_kernel  (ccsrc/kernel/YiTu_GNN.cpp:247-258)   SAG / forward / backward /
+ *                                                                   forward_gin / backward_gin / build_part
+ *   graph_ext                 (YiTu_GNN/YiTu_H/src/entry.cpp:184-193) spmm_* / sddmm_* / hfused_*
+ *
+ * Conventions
+ *   - torch-free: raw device pointers, explicit sizes, a CUDA stream per call.  Every pointer is
+ *     DEVICE memory unless the parameter name ends in `_host`.
+ *   - inputs are borrowed and never written; outputs and workspaces are allocated by the caller.
+ *   - a graph is a CSR by destination row: indptr[n_rows+1] (int32 or int64), indices[nnz] (int32,
+ *     column = source node).  With index_mask != 0 an index is "stitched": column = idx & index_mask and
+ *     segment (relation) id = (uint32)idx >> 24, the packed format of xgnn_h/block.py:36-67.
+ *   - every function returns YITU_OK (0) or an error code; yitu_last_error() gives the detail text of the
+ *     calling thread's last failure.  Nothing here calls exit() (the reference does on a launch error,
+ *     ccsrc/kernel/YiTu_GNN_kernel.cu:309-314).
+ *   - no state is kept between calls and no call is tied to a thread, so forward may run on the user
+ *     thread and backward on an autograd thread.
+ */
+#ifndef YITU_B200_H
+#define YITU_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *yitu_stream_t; /* same type as cudaStream_t */
+
+enum {
+    YITU_OK = 0,
+    YITU_ERR_INVALID_ARG = 1,
+    YITU_ERR_CUDA = 2,
+    YITU_ERR_WORKSPACE = 3,   /* workspace / scratch too small */
+    YITU_ERR_UNSUPPORTED = 4, /* shape outside what this kernel was built for */
+    YITU_ERR_LIMIT = 5        /* size beyond a documented fixed limit */
+};
+
+const char *yitu_status_string(int status);
+const char *yitu_last_error(void);
+int yitu_version(void);
+
+/* ---------------------------------------------------------------------------------------------- graph */
+typedef struct yitu_csr_t {
+    int64_t n_rows;      /* destination nodes */
+    int64_t n_cols;      /* source nodes */
+    int64_t nnz;         /* stored edges */
+    const void *indptr;  /* [n_rows+1] */
+    int32_t indptr_is64; /* 0: int32 row pointers, 1: int64 */
+    int32_t index_mask;  /* 0: plain column ids; 0xffffff: stitched (segment id in the top 8 bits) */
+    const int32_t *indices; /* [nnz] */
+} yitu_csr_t;
+
+/* Schedule that splits rows longer than chunk_edges into chunks of chunk_edges edges, so that a hub row
+ * of a power-law graph is aggregated by many warps and reduced in a fixed order (no float atomics).
+ * It plays the role of the reference's neighbour-group table (ccsrc/kernel/YiTu_GNN.cpp:203-245), which
+ * splits EVERY row into groups of partSize and merges them with atomics. */
+typedef struct yitu_hub_plan_t {
+    int32_t chunk_edges;
+    int32_t reserved;
+    int64_t n_chunks;
+    const int32_t *chunk_row;   /* [n_chunks] row of each chunk, ascending */
+    const int64_t *chunk_begin; /* [n_chunks] first edge of each chunk */
+} yitu_hub_plan_t;
+
+int64_t yitu_hub_plan_workspace_bytes(int64_t n_rows);
+/* Step 1: counts the chunks (*n_chunks_host, synchronises the stream) and leaves per-row offsets in
+ * `workspace`.  Step 2 (yitu_hub_plan_fill) writes the two tables from the same workspace. */
+int yitu_hub_plan_count(const yitu_csr_t *g, int32_t chunk_edges, void *workspace, int64_t workspace_bytes,
+                        int64_t *n_chunks_host, yitu_stream_t stream);
+int yitu_hub_plan_fill(const yitu_csr_t *g, int32_t chunk_edges, const void *workspace, int64_t n_chunks,
+                       int32_t *chunk_row, int64_t *chunk_begin, yitu_stream_t stream);
+
+/* CSR -> CSC (rows = sources) plus the edge permutation, stable: within a column the edges keep their CSR
+ * order (ascending destination).  t_indptr has the width of g->indptr.  Replaces nothing in the reference:
+ * its backward kernels scatter with atomicAdd instead (YiTu_GNN/YiTu_H/src/spmm_cuda.cu:32-38,
+ * sddmm_cuda.cu:58-63) and the ccsrc backward reuses the forward CSR (YiTu_GNN_kernel.cu:448-466). */
+int64_t yitu_csr_transpose_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t nnz);
+int yitu_csr_transpose(const yitu_csr_t *g, void *t_indptr, int32_t *t_rows, int32_t *t_perm, void *workspace,
+                       int64_t workspace_bytes, yitu_stream_t stream);
+
+/* Edge-balanced contiguous row partition: bounds[p] = min{ r : indptr[r] >= ceil(p*nnz/P) }, bounds[0]=0,
+ * bounds[P]=n_rows (int64, device).  Reworks the node-count-balanced range partition of
+ * YiTu_GNN/mmap/partition.py:12-22,165-197 (whose rebased-indptr convention the callers keep). */
+int yitu_partition_rows(const yitu_csr_t *g, int32_t n_parts, int64_t *bounds, yitu_stream_t stream);
+int yitu_partition_rows_host(int64_t n_rows, const void *indptr_host, int32_t indptr_is64, int32_t n_parts,
+                             int64_t *bounds_host);
+
+/* Neighbour-group table, on the host, bit-identical to build_part (ccsrc/kernel/YiTu_GNN.cpp:203-245):
+ * float32 storage, and the terminal pointer is written only while the last node's groups are emitted. */
+int64_t yitu_build_part_count_host(int32_t part_size, const int32_t *indptr_host, int64_t n_nodes);
+int yitu_build_part_host(int32_t part_size, const int32_t *indptr_host, int64_t n_nodes, float *part_ptr_host,
+                         float *part2node_host);
+
+/* stitch_csr (YiTu_GNN/YiTu_H/xgnn_h/block.py:36-67) on the host: concatenates row r of up to 16 blocks,
+ * new index = (block id << 24) + column + columns of the blocks before.  out_indices needs sum(nnz) entries.
+ * Fails with YITU_ERR_LIMIT where the reference asserts (more than 16 blocks, column > 2^24). */
+int yitu_stitch_csr_host(int32_t n_blocks, int64_t n_rows, const int32_t *const *indptrs_host,
+                         const int32_t *const *indices_host, const int64_t *n_cols_host, int32_t *out_indptr_host,
+                         int32_t *out_indices_host);
+
+/* ---------------------------------------------------------------------------------------------- SpMM */
+enum {
+    YITU_W_NONE = 0,      /* w = 1                       SAG, GIN, gspmm(edge=None)  */
+    YITU_W_NODE = 1,      /* w = norm_dst[row]*norm_src[col]   ccsrc GCN             */
+    YITU_W_EDGE = 2,      /* w = values[e]                                            */
+    YITU_W_EDGE_HEAD = 3  /* w = values[e*H + h]         graph_ext.spmm_forward       */
+};
+
+/* out[r,h,k] = alpha * row_scale[r] * sum_{e in row r} w(e,h) * x[col_e,h,k]   (+ out[r,h,k] if accumulate)
+ *
+ * Replaces the aggregation kernels of
+ *   ccsrc/kernel/YiTu_GNN_kernel.cu:179-257 (SAG), :319-415 / :477-556 (GCN fwd / bwd),
+ *   :620-694 / :753-823 (GIN fwd / bwd), and YiTu_GNN/YiTu_H/src/spmm_cuda.cu:4-21 (multi-head SpMM);
+ * run over the transposed graph (yitu_csr_transpose, edge_perm = t_perm) it is also the grad_x half of
+ * spmm_cuda.cu:24-42.  The dense X*W of the GCN/GIN layers stays outside (a library GEMM). */
+typedef struct yitu_spmm_args_t {
+    yitu_csr_t graph;
+    int64_t n_heads;          /* H (1 for plain SpMM) */
+    int64_t n_feats;          /* F; a feature row holds H*F floats */
+    int32_t weight_mode;      /* YITU_W_* */
+    int32_t accumulate;       /* 0: overwrite out, 1: add to it */
+    const float *edge_values; /* W_EDGE: [nnz]; W_EDGE_HEAD: [nnz,H] */
+    const int32_t *edge_perm; /* optional: edge e reads edge_values[edge_perm[e]] */
+    const float *norm_dst;    /* W_NODE: [n_rows] */
+    const float *norm_src;    /* W_NODE: [n_cols] */
+    const float *row_scale;   /* optional [n_rows] */
+    float alpha;              /* scalar epilogue (GIN epsilon; 1/#relations) */
+    int32_t reserved;
+    const float *x;           /* [n_cols, x_stride] source features */
+    int64_t x_stride;         /* floats between feature rows (>= H*F) */
+    float *out;               /* [n_rows, out_stride] */
+    int64_t out_stride;
+    const yitu_hub_plan_t *plan; /* optional hub-row schedule (host struct, device tables) */
+    float *scratch;              /* plan != NULL: >= plan->n_chunks * H*F floats */
+    int64_t scratch_bytes;
+} yitu_spmm_args_t;
+
+int yitu_spmm_csr_f32(const yitu_spmm_args_t *args, yitu_stream_t stream);
+
+/* values[e] = 1 / (number of edges of e's row that carry e's segment id): with YITU_W_EDGE over a stitched
+ * graph this turns the SpMM into "mean per relation, then sum over relations" in ONE pass and one output
+ * write per destination row — the mathematics of HeteroGraphConv over GCNLayer with norm = 1/in_degree
+ * (YiTu_GNN/YiTu_H/test/common/model.py:15-30,142-171; xgnn_h/mp.py:223-227).  Rows without edges of a
+ * segment simply contribute nothing (the reference would form 0 * inf there). */
+int yitu_segment_mean_weights_f32(const yitu_csr_t *g, float *values, yitu_stream_t stream);
+
+/* grad_a[e,h] = sum_k g[row_e,h,k] * x[col_e,h,k] — the edge-value half of
+ * YiTu_GNN/YiTu_H/src/spmm_cuda.cu:24-42, without atomics (one owner per (e,h)). */
+int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out, const float *x,
+                      float *grad_a, yitu_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------- GAT */
+/* attn[e,h] = softmax over {edges of the same row and segment} of LeakyReLU_slope(query[seg,row,h] + key[col,h]).
+ * Replaces sddmm_forward (YiTu_GNN/YiTu_H/src/sddmm_cuda.cu:5-33,69-89).  Unlike the reference the row maximum
+ * is subtracted before exponentiation (same value, no overflow).  n_segments = query.size(0) (<= 16). */
+int yitu_edge_softmax_fwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
+                              const float *query, const float *key, float *attn, yitu_stream_t stream);
+
+/* Replaces sddmm_backward (sddmm_cuda.cu:36-67,91-118): writes grad_query[seg,row,h] (every entry, zeros
+ * included) and edge_grad[e,h] = d loss / d (query+key) per edge; grad_key is then the per-source sum of
+ * edge_grad, taken with yitu_edge_gather_sum_f32 over the transposed graph (no atomics). */
+int yitu_edge_softmax_bwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
+                              const float *query, const float *key, const float *attn, const float *grad_attn,
+                              float *grad_query, float *edge_grad, yitu_stream_t stream);
+
+/* out[c,h] = sum_{j in column c of the transposed graph} edge_vals[t_perm[j], h] */
+int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indptr_is64, const int32_t *t_perm,
+                             int64_t n_heads, const float *edge_vals, float *out, yitu_stream_t stream);
+
+/* Fused GAT layer core: scores, LeakyReLU, edge softmax (online maximum/sum) and the weighted aggregation in
+ * one pass over each row's edges — the composition sddmm_forward + spmm_forward of the reference
+ * (xgnn_h/sparse.py:38-51,84-91; layer YiTu_GNN/YiTu_H/test/common/model.py:75-106) without the [nnz,H]
+ * attention tensor.  Plain (unstitched) graphs, H <= 32, F a multiple of 4 with F/4 a power of two, H*F <= 512;
+ * other shapes return YITU_ERR_UNSUPPORTED and the caller composes the unfused ops. */
+typedef struct yitu_gat_args_t {
+    yitu_csr_t graph;
+    int64_t n_heads, n_feats;
+    float slope;
+    int32_t reserved;
+    const float *query; /* [n_rows,H] */
+    const float *key;   /* [n_cols,H] */
+    const float *x;     /* [n_cols,H,F] */
+    float *out;         /* [n_rows,H,F] */
+    float *row_max;     /* [n_rows,H] softmax statistics kept for the backward pass */
+    float *row_sum;     /* [n_rows,H] */
+} yitu_gat_args_t;
+int yitu_gat_fwd_f32(const yitu_gat_args_t *args, yitu_stream_t stream);
+
+typedef struct yitu_gat_bwd_args_t {
+    yitu_gat_args_t fwd;       /* same tensors as the forward call (out, row_max, row_sum now inputs) */
+    const float *grad_out;     /* [n_rows,H,F] */
+    const void *t_indptr;      /* transposed graph from yitu_csr_transpose */
+    const int32_t *t_rows;
+    const int32_t *t_perm;
+    float *grad_query;         /* [n_rows,H] */
+    float *grad_key;           /* [n_cols,H] */
+    float *grad_x;             /* [n_cols,H,F] */
+    float *edge_attn;          /* scratch [nnz,H] */
+    float *edge_grad;          /* scratch [nnz,H] */
+} yitu_gat_bwd_args_t;
+int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *args, yitu_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------- multi-GPU */
+/* dst[i, :] = row ids[i] of a feature matrix that is sharded by contiguous row ranges over several GPUs:
+ * shard p holds rows [shard_bounds_host[p], shard_bounds_host[p+1]) at shard_ptrs_host[p] (a pointer this GPU
+ * can dereference: its own memory, or a peer's mapped through CUDA IPC / peer access).  Rows are fetched with
+ * plain 128-bit loads over NVLink — no collective, no multicast — so each needed source row crosses the link
+ * once and lands in local memory, where the SpMM gathers it.  Both `_host` arrays are HOST memory
+ * (n_shards <= 16, n_shards+1 bounds).  row_floats must be a multiple of 4 and all pointers 16-byte aligned.
+ * Reworks the feature exchange of YiTu_GNN/distributed/communication.py:14-51,230-264. */
+int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host, const int64_t *shard_bounds_host,
+                         const int32_t *ids, int64_t n_ids, int64_t row_floats, float *dst, yitu_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YITU_B200_H */

@@ -1,0 +1,308 @@
+"""graph_ext parity on the GPU: SpMM with per-head values, edge softmax ("SDDMM"), their backward passes,
+stitched (segmented) graphs, the horizontally fused call and the fused GAT kernels, against the CPU checker;
+then the reference's own dense-math identities (YiTu_GNN/YiTu_H/test/test_kernel.py) through autograd."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from conftest import assert_close, random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+SHAPES = [(1, 1), (1, 64), (3, 5), (8, 32), (4, 16), (7, 12), (32, 8), (16, 4), (2, 256), (5, 100), (33, 3)]
+
+
+@pytest.mark.parametrize("H,F", SHAPES)
+def test_spmm_forward_backward(oracle, H, F):
+    from yitu_b200 import graph_ext
+    rng = np.random.default_rng(H * 131 + F)
+    n_dst, n_src = 97, 143
+    indptr, indices = random_csr(rng, n_dst, n_src, density=0.06, hubs=2, hub_deg=120)
+    vals = rng.standard_normal((indices.shape[0], H)).astype(np.float32)
+    x = rng.standard_normal((n_src, H, F)).astype(np.float32)
+    g = rng.standard_normal((n_dst, H, F)).astype(np.float32)
+    ip, ix = _dev(indptr), _dev(indices)
+    out = graph_ext.spmm_forward(_dev(vals), ip, ix, _dev(x))
+    ref = oracle.spmm(indptr, indices, x, n_heads=H, wmode=oracle.W_EDGE_HEAD, values=vals, index_mask=0xFFFFFF)
+    assert_close(out.cpu().numpy(), ref, what="spmm_forward")
+    ga, gx = graph_ext.spmm_backward(_dev(vals), ip, ix, _dev(x), _dev(g))
+    rga, rgx = oracle.spmm_backward(vals, indptr, indices, x, g)
+    assert_close(ga.cpu().numpy(), rga, what="grad_a")
+    assert_close(gx.cpu().numpy(), rgx, what="grad_x")
+
+
+@pytest.mark.parametrize("H", [1, 2, 3, 8, 16, 24, 32, 40])
+@pytest.mark.parametrize("B", [1, 3])
+def test_sddmm_forward_backward(oracle, H, B):
+    from yitu_b200 import graph_ext, xgnn_h
+    rng = np.random.default_rng(H * 17 + B)
+    n_dst = 120
+    blocks = []
+    for b in range(B):
+        n_src = 50 + 30 * b
+        ip, ix = random_csr(rng, n_dst, n_src, density=0.08, hubs=1, hub_deg=45)
+        blocks.append((ip, ix, n_src))
+    if B == 1:
+        indptr, indices, n_src = blocks[0]
+    else:
+        indptr, indices, n_src = oracle.stitch_csr(blocks)
+        st = xgnn_h.stitch_csr([xgnn_h.Block([n_dst, c], [torch.from_numpy(a), torch.from_numpy(b)])
+                                for a, b, c in blocks])
+        assert np.array_equal(st.adj_sparse[0].numpy(), indptr) and np.array_equal(st.adj_sparse[1].numpy(), indices)
+        assert st.size == [n_dst, n_src]
+    q = rng.standard_normal((B, n_dst, H)).astype(np.float32)
+    k = rng.standard_normal((n_src, H)).astype(np.float32)
+    g = rng.standard_normal((indices.shape[0], H)).astype(np.float32)
+    ip, ix = _dev(indptr), _dev(indices)
+    attn = graph_ext.sddmm_forward(ip, ix, _dev(q), _dev(k))
+    ref = oracle.sddmm_forward(indptr, indices, q, k)
+    assert_close(attn.cpu().numpy(), ref, what="attn")
+    gq, gk = graph_ext.sddmm_backward(ip, ix, _dev(q), _dev(k), _dev(ref), _dev(g))
+    rgq, rgk = oracle.sddmm_backward(indptr, indices, q, k, ref, g)
+    assert_close(gq.cpu().numpy(), rgq, what="grad_query")
+    assert_close(gk.cpu().numpy(), rgk, what="grad_key")
+
+
+def test_sddmm_large_scores_do_not_overflow(oracle):
+    """The reference exponentiates raw scores; here the row maximum is subtracted first."""
+    from yitu_b200 import graph_ext
+    rng = np.random.default_rng(3)
+    indptr, indices = random_csr(rng, 40, 40, density=0.2)
+    q = (rng.standard_normal((1, 40, 4)) * 60).astype(np.float32)
+    k = (rng.standard_normal((40, 4)) * 60).astype(np.float32)
+    attn = graph_ext.sddmm_forward(_dev(indptr), _dev(indices), _dev(q), _dev(k))
+    assert torch.isfinite(attn).all()
+    assert_close(attn.cpu().numpy(), oracle.sddmm_forward(indptr, indices, q, k), what="attn (large scores)")
+
+
+@pytest.mark.parametrize("H,F", [(8, 32), (1, 64), (4, 16), (2, 128), (16, 4), (3, 8), (32, 16), (1, 4)])
+def test_fused_gat(oracle, H, F):
+    from yitu_b200 import graph_ext
+    rng = np.random.default_rng(H * 1000 + F)
+    n_dst, n_src = 150, 130
+    indptr, indices = random_csr(rng, n_dst, n_src, density=0.1, hubs=2, hub_deg=100)
+    q = rng.standard_normal((n_dst, H)).astype(np.float32)
+    k = rng.standard_normal((n_src, H)).astype(np.float32)
+    x = rng.standard_normal((n_src, H, F)).astype(np.float32)
+    g = rng.standard_normal((n_dst, H, F)).astype(np.float32)
+    assert graph_ext.gat_supported(None, None, H, F)
+    ip, ix = _dev(indptr), _dev(indices)
+    out, rmax, rsum = graph_ext.gat_forward(ip, ix, _dev(q), _dev(k), _dev(x))
+    ref_out, ref_attn = oracle.gat_forward(indptr, indices, q, k, x)
+    assert_close(out.cpu().numpy(), ref_out, what="gat out")
+    gq, gk, gx = graph_ext.gat_backward(ip, ix, _dev(q), _dev(k), _dev(x), out, rmax, rsum, _dev(g))
+    rgq, rgk, rgx = oracle.gat_backward(indptr, indices, q, k, x, ref_attn, g)
+    assert_close(gq.cpu().numpy(), rgq, rtol=2e-5, what="gat grad_query")
+    assert_close(gk.cpu().numpy(), rgk, rtol=2e-5, what="gat grad_key")
+    assert_close(gx.cpu().numpy(), rgx, rtol=2e-5, what="gat grad_x")
+
+
+def test_fused_gat_matches_two_operator_route():
+    from yitu_b200 import xgnn_h
+    from yitu_b200.xgnn_h import sparse
+    rng = np.random.default_rng(9)
+    indptr, indices = random_csr(rng, 200, 200, density=0.1)
+    blk = xgnn_h.Block([200, 200], [_dev(indptr), _dev(indices)])
+    q = torch.randn(200, 8, device="cuda", requires_grad=True)
+    k = torch.randn(200, 8, device="cuda", requires_grad=True)
+    x = torch.randn(200, 8, 32, device="cuda", requires_grad=True)
+    w = torch.randn(200, 8, 32, device="cuda")
+    y1 = sparse.fused_gat(blk, q, k, x)
+    (y1 * w).sum().backward()
+    g1 = [t.grad.clone() for t in (q, k, x)]
+    for t in (q, k, x):
+        t.grad = None
+    y2 = sparse.gspmm(blk, sparse.fused_gsddmm(blk, q, k), x)
+    (y2 * w).sum().backward()
+    assert_close(y1.detach().cpu().numpy(), y2.detach().cpu().numpy(), what="fused vs unfused out")
+    for a, t, n in zip(g1, (q, k, x), "qkx"):
+        assert_close(a.cpu().numpy(), t.grad.cpu().numpy(), rtol=3e-5, what="fused vs unfused grad_" + n)
+
+
+def test_hfused_forward_and_backward(oracle):
+    from yitu_b200 import graph_ext
+    rng = np.random.default_rng(21)
+    n_dst = 64
+    ipa, ixa = random_csr(rng, n_dst, 80, density=0.1)
+    ipb, ixb = random_csr(rng, n_dst, 70, density=0.1)
+    H, F = 4, 8
+    vals = rng.standard_normal((ixb.shape[0], H)).astype(np.float32)
+    xb = rng.standard_normal((70, H, F)).astype(np.float32)
+    q = rng.standard_normal((1, n_dst, H)).astype(np.float32)
+    k = rng.standard_normal((80, H)).astype(np.float32)
+    out, attn = graph_ext.hfused_forward(_dev(vals), _dev(ipb), _dev(ixb), _dev(xb), _dev(ipa), _dev(ixa), _dev(q),
+                                         _dev(k))
+    assert_close(attn.cpu().numpy(), oracle.sddmm_forward(ipa, ixa, q, k), what="hfused attn")
+    assert_close(out.cpu().numpy(), oracle.spmm(ipb, ixb, xb, n_heads=H, wmode=oracle.W_EDGE_HEAD, values=vals),
+                 what="hfused spmm")
+    g_out = rng.standard_normal((n_dst, H, F)).astype(np.float32)
+    g_attn = rng.standard_normal(attn.shape).astype(np.float32)
+    res = graph_ext.hfused_backward(_dev(vals), _dev(ipb), _dev(ixb), _dev(xb), _dev(g_out), _dev(ipa), _dev(ixa),
+                                    _dev(q), _dev(k), attn, _dev(g_attn))
+    assert len(res) == 2
+    rgq, rgk = oracle.sddmm_backward(ipa, ixa, q, k, attn.cpu().numpy(), g_attn)
+    assert_close(res[0].cpu().numpy(), rgq, what="hfused grad_query")
+    assert_close(res[1].cpu().numpy(), rgk, what="hfused grad_key")
+
+
+def test_segment_mean_rgcn(oracle):
+    """mean per relation then sum over relations, in one pass over the stitched graph."""
+    from yitu_b200 import ops, xgnn_h
+    rng = np.random.default_rng(33)
+    n_dst, D = 90, 64
+    blocks, feats = [], []
+    for b in range(3):
+        n_src = 40 + 25 * b
+        ip, ix = random_csr(rng, n_dst, n_src, density=0.1)
+        blocks.append((ip, ix, n_src))
+        feats.append(rng.standard_normal((n_src, D)).astype(np.float32))
+    st = xgnn_h.stitch_csr([xgnn_h.Block([n_dst, c], [torch.from_numpy(a), torch.from_numpy(b)])
+                            for a, b, c in blocks]).to("cuda")
+    xcat = np.concatenate(feats)
+    g = ops.prepared(st.adj_sparse[0], st.adj_sparse[1], xcat.shape[0], ops.STITCH_MASK)
+    got = ops.spmm(g, _dev(xcat), mode=ops.W_EDGE, edge_values=g.segment_mean_weights())
+    ref = np.zeros((n_dst, D), dtype=np.float64)
+    for (ip, ix, _), f in zip(blocks, feats):
+        deg = np.diff(ip).astype(np.float64)
+        s = oracle.spmm(ip, ix, f).astype(np.float64)
+        ref += np.where(deg[:, None] > 0, s / np.maximum(deg, 1)[:, None], 0.0)
+    assert_close(got.cpu().numpy(), ref.astype(np.float32), rtol=2e-5, what="segment mean")
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The reference's own kernel tests, restated (dense torch algebra vs the sparse operators, through autograd).
+# YiTu_GNN/YiTu_H/test/test_kernel.py uses unseeded sizes and atol=1e-3; these are seeded and use 1e-4.
+# ---------------------------------------------------------------------------------------------------------
+def _rand_adjacency(gen, n_rows, n_cols, density=0.02):
+    while True:
+        adj = (torch.rand(n_rows, n_cols, generator=gen) < density).float()
+        if adj.max() != 0:
+            return adj
+
+
+def _to_csr(dense):
+    nz = dense.nonzero()
+    counts = torch.bincount(nz[:, 0], minlength=dense.size(0))
+    indptr = torch.zeros(dense.size(0) + 1, dtype=torch.int32)
+    indptr[1:] = torch.cumsum(counts, 0)
+    return indptr, nz[:, 1].to(torch.int32)
+
+
+def _to_dense_mha(n_rows, n_cols, indptr, indices, values):
+    rows = torch.repeat_interleave(torch.arange(n_rows), (indptr[1:] - indptr[:-1]).long())
+    dense = torch.zeros(values.size(1), n_rows, n_cols)
+    dense[:, rows, indices.long() & 0xFFFFFF] = values.detach().cpu().t()
+    return dense
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_reference_check_gspmm(seed):
+    from yitu_b200 import xgnn_h
+    from yitu_b200.xgnn_h import sparse
+    gen = torch.Generator().manual_seed(seed)
+    n_src, n_dst, H, F = [int(torch.randint(1, hi + 1, (1,), generator=gen)) for hi in (512, 512, 32, 256)]
+    adj = _rand_adjacency(gen, n_dst, n_src)
+    indptr, indices = _to_csr(adj)
+    x = torch.randn(n_src, H, F, generator=gen).cuda()
+    values = torch.randn(indices.size(0), H, generator=gen).cuda().requires_grad_()
+    linear = nn.Linear(F, F).cuda()
+    blk = xgnn_h.Block([n_dst, n_src], [indptr, indices]).to("cuda")
+    dense = _to_dense_mha(n_dst, n_src, indptr, indices, values).cuda().requires_grad_()
+    y1 = torch.bmm(dense, linear(x).transpose(0, 1)).transpose(0, 1)
+    y1.sum().backward()
+    g1 = linear.weight.grad.clone()
+    g2 = adj.cuda().unsqueeze(0) * dense.grad
+    linear.zero_grad()
+    y2 = sparse.gspmm(blk, values, linear(x))
+    y2.sum().backward()
+    g3 = linear.weight.grad.clone()
+    g4 = _to_dense_mha(n_dst, n_src, indptr, indices, values.grad).cuda()
+    assert torch.allclose(y1, y2, atol=1e-4)
+    assert torch.allclose(g1, g3, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(g2, g4, atol=1e-4)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_reference_check_gsddmm(seed):
+    from yitu_b200 import xgnn_h
+    from yitu_b200.xgnn_h import sparse
+    gen = torch.Generator().manual_seed(100 + seed)
+    n_src, n_dst, H, F = [int(torch.randint(1, hi + 1, (1,), generator=gen)) for hi in (512, 512, 16, 256)]
+    adj = _rand_adjacency(gen, n_dst, n_src)
+    indptr, indices = _to_csr(adj)
+    x_dst = torch.randn(n_dst, H, F, generator=gen).cuda()
+    x_src = torch.randn(n_src, H, F, generator=gen).cuda()
+    lq, lk = nn.Linear(F, 1).cuda(), nn.Linear(F, 1).cuda()
+    blk = xgnn_h.Block([n_dst, n_src], [indptr, indices]).to("cuda")
+    adj = adj.cuda()
+    q, k = lq(x_dst).squeeze(-1), lk(x_src).squeeze(-1)          # [n_dst,H], [n_src,H]
+    e = nn.functional.leaky_relu(q.unsqueeze(1) + k.unsqueeze(0), 0.2)   # [n_dst,n_src,H]
+    e = torch.where(adj.unsqueeze(-1) > 0, e, torch.full_like(e, -1e38)).permute(2, 0, 1)
+    attn1 = torch.softmax(e, dim=-1) * adj.unsqueeze(0)
+    y1 = torch.bmm(attn1, x_src.transpose(0, 1)).transpose(0, 1)
+    y1.sum().backward()
+    gq1, gk1 = lq.weight.grad.clone(), lk.weight.grad.clone()
+    lq.zero_grad(); lk.zero_grad()
+    q, k = lq(x_dst).squeeze(-1), lk(x_src).squeeze(-1)
+    y2 = sparse.gspmm(blk, sparse.fused_gsddmm(blk, q, k), x_src)
+    y2.sum().backward()
+    assert torch.allclose(y1, y2, atol=1e-4)
+    assert torch.allclose(gq1, lq.weight.grad, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(gk1, lk.weight.grad, atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_reference_check_stitch(seed):
+    """Sum over relations of (sddmm, spmm) == one stitched (sddmm, spmm): outputs and input gradients."""
+    from yitu_b200 import xgnn_h
+    from yitu_b200.xgnn_h import sparse
+    gen = torch.Generator().manual_seed(200 + seed)
+    n_dst, H, F = [int(torch.randint(1, hi + 1, (1,), generator=gen)) for hi in (256, 8, 64)]
+    n_blocks = int(torch.randint(2, 5, (1,), generator=gen))
+    blocks, xs, qs, ks = [], [], [], []
+    for _ in range(n_blocks):
+        n_src = int(torch.randint(1, 257, (1,), generator=gen))
+        adj = _rand_adjacency(gen, n_dst, n_src, density=0.05)
+        indptr, indices = _to_csr(adj)
+        blocks.append(xgnn_h.Block([n_dst, n_src], [indptr, indices]))
+        xs.append(torch.randn(n_src, H, F, generator=gen).cuda().requires_grad_())
+        qs.append(torch.randn(n_dst, H, generator=gen).cuda().requires_grad_())
+        ks.append(torch.randn(n_src, H, generator=gen).cuda().requires_grad_())
+    stitched = xgnn_h.stitch_csr(blocks).to("cuda")
+    y1 = 0
+    for blk, x, q, k in zip(blocks, xs, qs, ks):
+        blk.to("cuda")
+        y1 = y1 + sparse.gspmm(blk, sparse.fused_gsddmm(blk, q, k), x)
+    y1.sum().backward()
+    grads1 = [t.grad.clone() for t in xs + qs + ks]
+    for t in xs + qs + ks:
+        t.grad = None
+    attn = sparse.fused_gsddmm(stitched, torch.stack(qs), torch.cat(ks))
+    y2 = sparse.gspmm(stitched, attn, torch.cat(xs))
+    y2.sum().backward()
+    assert torch.allclose(y1, y2, atol=1e-4)
+    for a, t in zip(grads1, xs + qs + ks):
+        assert torch.allclose(a, t.grad, atol=1e-4)
+
+
+def test_reference_check_bundle():
+    from yitu_b200.xgnn_h import bundle
+    gen = torch.Generator().manual_seed(7)
+    x = torch.randn(300, 70, generator=gen).cuda().requires_grad_()
+    fc1, fc2 = nn.Linear(70, 9, bias=False).cuda(), nn.Linear(70, 9, bias=False).cuda()
+    y1, y2 = fc1(x), fc2(x)
+    (y1 + y2).sum().backward()
+    gx, g1, g2 = x.grad.clone(), fc1.weight.grad.clone(), fc2.weight.grad.clone()
+    x.grad = None
+    fc1.zero_grad(); fc2.zero_grad()
+    y3, y4 = bundle.GEMMBundleFunction.apply(x, fc1.weight, fc2.weight, None, None)
+    (y3 + y4).sum().backward()
+    assert torch.allclose(y1, y3, atol=1e-4) and torch.allclose(y2, y4, atol=1e-4)
+    assert torch.allclose(gx, x.grad, atol=1e-4)
+    assert torch.allclose(g1, fc1.weight.grad, atol=1e-3) and torch.allclose(g2, fc2.weight.grad, atol=1e-3)

@@ -1,0 +1,596 @@
+// GAT attention kernels for sm_100a.
+//
+//   edge_softmax_{fwd,bwd}  stand-alone "SDDMM" of the reference (u_add_v -> LeakyReLU -> per-segment edge
+//                           softmax) with [nnz,H] attention in memory — the drop-in operator path;
+//   edge_dot                grad of the per-edge values of a multi-head SpMM;
+//   edge_gather_sum         per-source sum of per-edge gradients over the transposed graph (replaces the
+//                           reference's atomicAdd scatter);
+//   gat_fwd / gat_bwd       the fused layer core: one pass over a row's edges computes scores, an online
+//                           max/sum softmax and the weighted aggregation; the backward recomputes the
+//                           attention from the saved row statistics.
+//
+// All of them are bound by gather bandwidth (HBM/L2); none uses float atomics.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace yitu {
+
+__device__ __forceinline__ int pow2_shift(int v) { return 31 - __clz(v); }
+
+// ---------------------------------------------------------------------------------------------------------
+// Stand-alone edge softmax.  One warp per row; a lane is (edge slot, head): HB = pow2 >= min(H,32) lanes
+// span the heads (coalesced key / attn accesses), 32/HB edges advance together.
+// ---------------------------------------------------------------------------------------------------------
+struct SoftmaxParams {
+    int64_t n_rows;
+    const void *indptr;
+    const int *indices;
+    int is64, mask, B, H, HB;
+    float slope;
+    const float *q, *k, *attn_in, *grad_attn;
+    float *attn_out, *grad_q, *edge_grad;
+};
+
+__global__ void __launch_bounds__(256) edge_softmax_fwd_kernel(const __grid_constant__ SoftmaxParams p) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= p.n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int hs = lane & (p.HB - 1);
+    const int slot = lane >> pow2_shift(p.HB);
+    const int ES = 32 / p.HB;
+    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    for (int s = 0; s < p.B; ++s) {
+        for (int hc = 0; hc < p.H; hc += p.HB) {
+            const int h = hc + hs;
+            const bool hv = h < p.H;
+            const float qv = hv ? __ldg(p.q + (static_cast<int64_t>(s) * p.n_rows + row) * p.H + h) : 0.0f;
+            float m = -CUDART_INF_F, l = 0.0f;
+            for (int64_t e = eb + slot; e < ee; e += ES) {
+                const int raw = __ldg(p.indices + e);
+                const int bid = p.mask ? static_cast<int>(static_cast<unsigned>(raw) >> 24) : 0;
+                if (bid != s || !hv) continue;
+                const int col = p.mask ? (raw & p.mask) : raw;
+                const float z = leaky_relu(qv + __ldg(p.k + static_cast<int64_t>(col) * p.H + h), p.slope);
+                if (z > m) {
+                    l = l * expf(m - z) + 1.0f;
+                    m = z;
+                } else {
+                    l += expf(z - m);
+                }
+            }
+            for (int o = p.HB; o < 32; o <<= 1) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+                const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+                const float M = fmaxf(m, m2);
+                if (M > -CUDART_INF_F) l = l * expf(m - M) + l2 * expf(m2 - M);
+                m = M;
+            }
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            for (int64_t e = eb + slot; e < ee; e += ES) {
+                const int raw = __ldg(p.indices + e);
+                const int bid = p.mask ? static_cast<int>(static_cast<unsigned>(raw) >> 24) : 0;
+                if (bid != s || !hv) continue;
+                const int col = p.mask ? (raw & p.mask) : raw;
+                const float z = leaky_relu(qv + __ldg(p.k + static_cast<int64_t>(col) * p.H + h), p.slope);
+                p.attn_out[e * p.H + h] = expf(z - m) * inv;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) edge_softmax_bwd_kernel(const __grid_constant__ SoftmaxParams p) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= p.n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int hs = lane & (p.HB - 1);
+    const int slot = lane >> pow2_shift(p.HB);
+    const int ES = 32 / p.HB;
+    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    for (int s = 0; s < p.B; ++s) {
+        for (int hc = 0; hc < p.H; hc += p.HB) {
+            const int h = hc + hs;
+            const bool hv = h < p.H;
+            const float qv = hv ? __ldg(p.q + (static_cast<int64_t>(s) * p.n_rows + row) * p.H + h) : 0.0f;
+            float t = 0.0f;  // sum over the segment of attn * grad
+            for (int64_t e = eb + slot; e < ee; e += ES) {
+                const int raw = __ldg(p.indices + e);
+                const int bid = p.mask ? static_cast<int>(static_cast<unsigned>(raw) >> 24) : 0;
+                if (bid != s || !hv) continue;
+                t = fmaf(__ldg(p.attn_in + e * p.H + h), __ldg(p.grad_attn + e * p.H + h), t);
+            }
+            for (int o = p.HB; o < 32; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            float gq = 0.0f;
+            for (int64_t e = eb + slot; e < ee; e += ES) {
+                const int raw = __ldg(p.indices + e);
+                const int bid = p.mask ? static_cast<int>(static_cast<unsigned>(raw) >> 24) : 0;
+                if (bid != s || !hv) continue;
+                const int col = p.mask ? (raw & p.mask) : raw;
+                const float a = __ldg(p.attn_in + e * p.H + h);
+                const float gs = a * (__ldg(p.grad_attn + e * p.H + h) - t);
+                const float z = qv + __ldg(p.k + static_cast<int64_t>(col) * p.H + h);
+                const float gv = gs * (z < 0.0f ? p.slope : 1.0f);
+                p.edge_grad[e * p.H + h] = gv;
+                gq += gv;
+            }
+            for (int o = p.HB; o < 32; o <<= 1) gq += __shfl_xor_sync(0xffffffffu, gq, o);
+            if (slot == 0 && hv) p.grad_q[(static_cast<int64_t>(s) * p.n_rows + row) * p.H + h] = gq;
+        }
+    }
+}
+
+// out[c,h] = sum over column c of the transposed graph of vals[perm[j], h]
+__global__ void __launch_bounds__(256)
+edge_gather_sum_kernel(int64_t n_cols, const void *t_indptr, int is64, const int *perm, int H, int HB,
+                       const float *vals, float *out) {
+    const int64_t c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (c >= n_cols) return;
+    const int lane = threadIdx.x & 31;
+    const int hs = lane & (HB - 1);
+    const int slot = lane >> pow2_shift(HB);
+    const int ES = 32 / HB;
+    const int64_t b = load_ptr(t_indptr, is64, c), e = load_ptr(t_indptr, is64, c + 1);
+    for (int hc = 0; hc < H; hc += HB) {
+        const int h = hc + hs;
+        float a = 0.0f;
+        if (h < H)
+            for (int64_t j = b + slot; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
+        for (int o = HB; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (slot == 0 && h < H) out[c * H + h] = a;
+    }
+}
+
+// grad_a[e,h] = <g[row,h,:], x[col,h,:]>.  A group of LP = pow2 >= min(F,32) lanes owns one (edge, head) pair.
+__global__ void __launch_bounds__(256)
+edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices, int mask, int H, int F, int LP,
+                const float *g, const float *x, float *grad_a) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & (LP - 1);
+    const int grp = lane >> pow2_shift(LP);
+    const int G = 32 / LP;
+    const int64_t eb = load_ptr(indptr, is64, row), ee = load_ptr(indptr, is64, row + 1);
+    const int64_t D = static_cast<int64_t>(H) * F;
+    const int64_t pairs = (ee - eb) * H;
+    const float *gr = g + row * D;
+    for (int64_t pb = 0; pb < pairs; pb += G) {  // uniform trip count: every lane joins the shuffles
+        const int64_t pi = pb + grp;
+        float a = 0.0f;
+        int64_t e = 0;
+        int h = 0;
+        if (pi < pairs) {
+            e = eb + pi / H;
+            h = static_cast<int>(pi % H);
+            const int raw = __ldg(indices + e);
+            const int col = mask ? (raw & mask) : raw;
+            const float *xr = x + static_cast<int64_t>(col) * D + static_cast<int64_t>(h) * F;
+            const float *gh = gr + static_cast<int64_t>(h) * F;
+            for (int k = gl; k < F; k += LP) a = fmaf(__ldg(gh + k), __ldg(xr + k), a);
+        }
+        for (int o = LP >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (pi < pairs && gl == 0) grad_a[e * H + h] = a;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused GAT forward.  One warp per destination row, tiles of 32 edges.
+//   per tile: lanes fetch 32 column ids; (edge, head) pairs are spread over the lanes to compute the scores
+//   with coalesced key reads; lane h folds the tile into head h's running (max, sum); then every lane
+//   gathers its NV 128-bit slices of each source row and accumulates p * x.  Accumulators are rescaled when
+//   the running maximum moves (online softmax), and divided by the sum once at the end.
+// Shared memory per warp: 32 column ids, 32*H scores/probabilities, H-sized scale / max / sum / query rows.
+// ---------------------------------------------------------------------------------------------------------
+struct GatParams {
+    int64_t n_rows;
+    const void *indptr;
+    const int *indices;
+    int is64, H, F, hshift;  // hshift = log2(H) if H is a power of two, else -1
+    float slope;
+    const float *q, *k, *x;
+    float *out, *row_max, *row_sum;
+    // backward
+    const float *grad_out;
+    float *grad_q, *edge_attn, *edge_grad;
+};
+
+__device__ __forceinline__ int warp_smem_floats_fwd(int H) { return 32 + 32 * H + 4 * 32; }
+
+template <int NV>
+__global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ GatParams p) {
+    extern __shared__ float smem[];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+    if (row >= p.n_rows) return;
+    const int H = p.H;
+    float *base = smem + wib * warp_smem_floats_fwd(H);
+    int *s_col = reinterpret_cast<int *>(base);
+    float *s_p = base + 32;
+    float *s_scale = s_p + 32 * H;
+    float *s_m = s_scale + 32;
+    float *s_q = s_m + 32;
+    float *s_l = s_q + 32;
+
+    const int64_t D = static_cast<int64_t>(H) * p.F;
+    int hd[NV];
+    bool valid[NV];
+    int64_t off[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        off[i] = static_cast<int64_t>(i * 32 + lane) * 4;
+        valid[i] = off[i] < D;
+        hd[i] = valid[i] ? static_cast<int>(off[i] / p.F) : 0;
+    }
+    float acc[NV][4];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+    if (lane < H) s_q[lane] = __ldg(p.q + row * H + lane);
+    float m_run = -CUDART_INF_F, l_run = 0.0f;  // lane h owns head h
+    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    __syncwarp();
+
+    for (int64_t e0 = eb; e0 < ee; e0 += 32) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
+        int my_col = lane < n ? ld_stream(p.indices + e0 + lane) : 0;
+        const int c_first = __shfl_sync(0xffffffffu, my_col, 0);
+        s_col[lane] = lane < n ? my_col : c_first;
+        __syncwarp();
+        const int npairs = n * H;
+        for (int idx = lane; idx < npairs; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            s_p[idx] = leaky_relu(s_q[h] + __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + h), p.slope);
+        }
+        __syncwarp();
+        if (lane < H) {
+            float tm = -CUDART_INF_F;
+            for (int e = 0; e < n; ++e) tm = fmaxf(tm, s_p[e * H + lane]);
+            const float m_new = fmaxf(m_run, tm);
+            const float sc = expf(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+            s_scale[lane] = sc;
+            s_m[lane] = m_new;
+            l_run *= sc;
+            m_run = m_new;
+        }
+        __syncwarp();
+        const int n4 = (n + 3) & ~3;
+        for (int idx = lane; idx < n4 * H; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            s_p[idx] = idx < npairs ? expf(s_p[idx] - s_m[h]) : 0.0f;
+        }
+        __syncwarp();
+        if (lane < H) {
+            float ls = 0.0f;
+            for (int e = 0; e < n; ++e) ls += s_p[e * H + lane];
+            l_run += ls;
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const float sc = s_scale[hd[i]];
+            acc[i][0] *= sc; acc[i][1] *= sc; acc[i][2] *= sc; acc[i][3] *= sc;
+        }
+        for (int j = 0; j < n4; j += 4) {
+            float4 v[4][NV];
+            float w[4][NV];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float *xr = p.x + static_cast<int64_t>(s_col[j + u]) * D;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    if (valid[i]) {
+                        v[u][i] = __ldg(reinterpret_cast<const float4 *>(xr + off[i]));
+                        w[u][i] = s_p[(j + u) * H + hd[i]];
+                    } else {
+                        v[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        w[u][i] = 0.0f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    acc[i][0] = fmaf(w[u][i], v[u][i].x, acc[i][0]);
+                    acc[i][1] = fmaf(w[u][i], v[u][i].y, acc[i][1]);
+                    acc[i][2] = fmaf(w[u][i], v[u][i].z, acc[i][2]);
+                    acc[i][3] = fmaf(w[u][i], v[u][i].w, acc[i][3]);
+                }
+        }
+        __syncwarp();
+    }
+    if (lane < H) {
+        s_l[lane] = l_run;
+        p.row_max[row * H + lane] = m_run;
+        p.row_sum[row * H + lane] = l_run;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (!valid[i]) continue;
+        const float l = s_l[hd[i]];
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        *reinterpret_cast<float4 *>(p.out + row * D + off[i]) =
+            make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused GAT backward, pass over destination rows.  Recomputes attn = exp(score - max)/sum from the saved
+// row statistics, forms d attn = <grad_out[row,h,:], x[col,h,:]> with an in-head shuffle reduction
+// (LPH = F/4 lanes per head, a power of two), applies the softmax and LeakyReLU derivatives using
+// delta[h] = <grad_out[row,h,:], out[row,h,:]> (= sum_e attn_e * d attn_e), and writes per-edge attn and
+// d score tiles (coalesced) for the source-side pass, plus grad_query.
+// Shared memory per warp: 32 ids + 3 * 32*H floats + 3 * 32 floats.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int warp_smem_floats_bwd(int H) { return 32 + 3 * 32 * H + 3 * 32; }
+
+template <int NV>
+__global__ void __launch_bounds__(256) gat_bwd_rows_kernel(const __grid_constant__ GatParams p) {
+    extern __shared__ float smem[];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+    if (row >= p.n_rows) return;
+    const int H = p.H;
+    float *base = smem + wib * warp_smem_floats_bwd(H);
+    int *s_col = reinterpret_cast<int *>(base);
+    float *s_a = base + 32;
+    float *s_f = s_a + 32 * H;
+    float *s_dz = s_f + 32 * H;
+    float *s_q = s_dz + 32 * H;
+    float *s_m = s_q + 32;
+    float *s_il = s_m + 32;
+
+    const int64_t D = static_cast<int64_t>(H) * p.F;
+    const int LPH = p.F >> 2;  // lanes per head
+    int hd[NV];
+    bool valid[NV];
+    int64_t off[NV];
+    float4 g[NV];
+    float delta[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        off[i] = static_cast<int64_t>(i * 32 + lane) * 4;
+        valid[i] = off[i] < D;
+        hd[i] = valid[i] ? static_cast<int>(off[i] / p.F) : 0;
+        float d = 0.0f;
+        g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid[i]) {
+            g[i] = __ldg(reinterpret_cast<const float4 *>(p.grad_out + row * D + off[i]));
+            const float4 o = __ldg(reinterpret_cast<const float4 *>(p.out + row * D + off[i]));
+            d = g[i].x * o.x + g[i].y * o.y + g[i].z * o.z + g[i].w * o.w;
+        }
+        for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+        delta[i] = d;
+    }
+    if (lane < H) {
+        s_q[lane] = __ldg(p.q + row * H + lane);
+        s_m[lane] = __ldg(p.row_max + row * H + lane);
+        const float l = __ldg(p.row_sum + row * H + lane);
+        s_il[lane] = l > 0.0f ? 1.0f / l : 0.0f;
+    }
+    float gq = 0.0f;  // lane h owns grad_query[row, h]
+    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    __syncwarp();
+
+    for (int64_t e0 = eb; e0 < ee; e0 += 32) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
+        int my_col = lane < n ? ld_stream(p.indices + e0 + lane) : 0;
+        const int c_first = __shfl_sync(0xffffffffu, my_col, 0);
+        s_col[lane] = lane < n ? my_col : c_first;
+        __syncwarp();
+        const int npairs = n * H;
+        for (int idx = lane; idx < npairs; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            const float z = s_q[h] + __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + h);
+            s_a[idx] = expf(leaky_relu(z, p.slope) - s_m[h]) * s_il[h];
+            s_f[idx] = z < 0.0f ? p.slope : 1.0f;
+        }
+        __syncwarp();
+        const int n2 = (n + 1) & ~1;
+        for (int j = 0; j < n2; j += 2) {
+            float4 v[2][NV];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float *xr = p.x + static_cast<int64_t>(s_col[j + u]) * D;
+#pragma unroll
+                for (int i = 0; i < NV; ++i)
+                    v[u][i] = valid[i] ? __ldg(reinterpret_cast<const float4 *>(xr + off[i]))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    float d = g[i].x * v[u][i].x + g[i].y * v[u][i].y + g[i].z * v[u][i].z + g[i].w * v[u][i].w;
+                    for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+                    if (valid[i] && (lane & (LPH - 1)) == 0 && j + u < n) {
+                        const int idx = (j + u) * H + hd[i];
+                        s_dz[idx] = s_a[idx] * (d - delta[i]) * s_f[idx];
+                    }
+                }
+        }
+        __syncwarp();
+        for (int idx = lane; idx < npairs; idx += 32) {
+            p.edge_attn[e0 * H + idx] = s_a[idx];
+            p.edge_grad[e0 * H + idx] = s_dz[idx];
+        }
+        if (lane < H) {
+            float a = 0.0f;
+            for (int e = 0; e < n; ++e) a += s_dz[e * H + lane];
+            gq += a;
+        }
+        __syncwarp();
+    }
+    if (lane < H) p.grad_q[row * H + lane] = gq;
+}
+
+static int head_block(int64_t H) {
+    int hb = 1;
+    while (hb < H && hb < 32) hb <<= 1;
+    return hb;
+}
+
+}  // namespace yitu
+
+using namespace yitu;
+
+static int check_softmax_args(const yitu_csr_t *g, int32_t n_segments, int64_t H) {
+    if (int rc = validate_csr(g)) return rc;
+    YITU_REQUIRE(n_segments >= 1 && n_segments <= 256, YITU_ERR_INVALID_ARG, "n_segments=%d", n_segments);
+    YITU_REQUIRE(n_segments == 1 || g->index_mask != 0, YITU_ERR_INVALID_ARG,
+                 "several segments need stitched indices (index_mask=0xffffff)");
+    YITU_REQUIRE(H >= 1 && H < (1 << 20), YITU_ERR_INVALID_ARG, "n_heads=%lld", (long long)H);
+    return YITU_OK;
+}
+
+extern "C" int yitu_edge_softmax_fwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
+                                         const float *query, const float *key, float *attn, yitu_stream_t stream) {
+    if (int rc = check_softmax_args(g, n_segments, n_heads)) return rc;
+    if (g->n_rows == 0 || g->nnz == 0) return YITU_OK;
+    YITU_REQUIRE(query && key && attn, YITU_ERR_INVALID_ARG, "NULL tensor");
+    SoftmaxParams p{};
+    p.n_rows = g->n_rows; p.indptr = g->indptr; p.indices = g->indices; p.is64 = g->indptr_is64;
+    p.mask = g->index_mask; p.B = n_segments; p.H = static_cast<int>(n_heads); p.HB = head_block(n_heads);
+    p.slope = slope; p.q = query; p.k = key; p.attn_out = attn;
+    edge_softmax_fwd_kernel<<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0,
+                              reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_edge_softmax_bwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
+                                         const float *query, const float *key, const float *attn,
+                                         const float *grad_attn, float *grad_query, float *edge_grad,
+                                         yitu_stream_t stream) {
+    if (int rc = check_softmax_args(g, n_segments, n_heads)) return rc;
+    if (g->n_rows == 0) return YITU_OK;
+    YITU_REQUIRE(query && grad_query, YITU_ERR_INVALID_ARG, "NULL tensor");
+    YITU_REQUIRE(g->nnz == 0 || (key && attn && grad_attn && edge_grad), YITU_ERR_INVALID_ARG, "NULL tensor");
+    SoftmaxParams p{};
+    p.n_rows = g->n_rows; p.indptr = g->indptr; p.indices = g->indices; p.is64 = g->indptr_is64;
+    p.mask = g->index_mask; p.B = n_segments; p.H = static_cast<int>(n_heads); p.HB = head_block(n_heads);
+    p.slope = slope; p.q = query; p.k = key; p.attn_in = attn; p.grad_attn = grad_attn;
+    p.grad_q = grad_query; p.edge_grad = edge_grad;
+    edge_softmax_bwd_kernel<<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0,
+                              reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indptr_is64,
+                                        const int32_t *t_perm, int64_t n_heads, const float *edge_vals, float *out,
+                                        yitu_stream_t stream) {
+    YITU_REQUIRE(n_cols >= 0 && n_heads >= 1 && t_indptr, YITU_ERR_INVALID_ARG, "bad argument");
+    if (n_cols == 0) return YITU_OK;
+    YITU_REQUIRE(out, YITU_ERR_INVALID_ARG, "out is NULL");
+    edge_gather_sum_kernel<<<static_cast<unsigned>((n_cols + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        n_cols, t_indptr, indptr_is64, t_perm, static_cast<int>(n_heads), head_block(n_heads), edge_vals, out);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out,
+                                 const float *x, float *grad_a, yitu_stream_t stream) {
+    if (int rc = validate_csr(g)) return rc;
+    YITU_REQUIRE(n_heads >= 1 && n_feats >= 1, YITU_ERR_INVALID_ARG, "bad shape");
+    if (g->n_rows == 0 || g->nnz == 0) return YITU_OK;
+    YITU_REQUIRE(grad_out && x && grad_a, YITU_ERR_INVALID_ARG, "NULL tensor");
+    edge_dot_kernel<<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        g->n_rows, g->indptr, g->indptr_is64, g->indices, g->index_mask, static_cast<int>(n_heads),
+        static_cast<int>(n_feats), head_block(n_feats), grad_out, x, grad_a);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+static int check_gat(const yitu_gat_args_t *a, bool backward) {
+    YITU_REQUIRE(a != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
+    if (int rc = validate_csr(&a->graph)) return rc;
+    const int64_t H = a->n_heads, F = a->n_feats;
+    YITU_REQUIRE(H >= 1 && F >= 1, YITU_ERR_INVALID_ARG, "bad shape");
+    YITU_REQUIRE(a->graph.index_mask == 0, YITU_ERR_UNSUPPORTED, "fused GAT takes plain (unstitched) graphs");
+    YITU_REQUIRE(H <= 32 && F % 4 == 0 && H * F <= 512, YITU_ERR_UNSUPPORTED,
+                 "fused GAT needs H <= 32, F %% 4 == 0, H*F <= 512 (H=%lld F=%lld)", (long long)H, (long long)F);
+    if (backward) {
+        const int64_t lph = F / 4;
+        YITU_REQUIRE(lph <= 32 && (lph & (lph - 1)) == 0, YITU_ERR_UNSUPPORTED,
+                     "fused GAT backward needs F/4 a power of two <= 32 (F=%lld)", (long long)F);
+    }
+    YITU_REQUIRE(a->graph.n_rows == 0 || (a->query && a->out && a->row_max && a->row_sum), YITU_ERR_INVALID_ARG,
+                 "NULL tensor");
+    YITU_REQUIRE(a->graph.nnz == 0 || (a->key && a->x), YITU_ERR_INVALID_ARG, "NULL tensor");
+    YITU_REQUIRE(aligned16(a->x) && aligned16(a->out), YITU_ERR_INVALID_ARG, "x / out must be 16-byte aligned");
+    return YITU_OK;
+}
+
+static void fill_gat(GatParams &p, const yitu_gat_args_t *a) {
+    p.n_rows = a->graph.n_rows; p.indptr = a->graph.indptr; p.indices = a->graph.indices;
+    p.is64 = a->graph.indptr_is64; p.H = static_cast<int>(a->n_heads); p.F = static_cast<int>(a->n_feats);
+    p.hshift = (p.H & (p.H - 1)) == 0 ? 31 - __builtin_clz(p.H) : -1;
+    p.slope = a->slope; p.q = a->query; p.k = a->key; p.x = a->x;
+    p.out = a->out; p.row_max = a->row_max; p.row_sum = a->row_sum;
+}
+
+template <typename K>
+static int launch_rows(K kernel, const GatParams &p, int smem_floats_per_warp, cudaStream_t st) {
+    const int warps = 8;
+    const size_t smem = static_cast<size_t>(warps) * smem_floats_per_warp * sizeof(float);
+    if (smem > 48 * 1024)
+        YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<static_cast<unsigned>((p.n_rows + warps - 1) / warps), warps * 32, smem, st>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) {
+    if (int rc = check_gat(a, false)) return rc;
+    if (a->graph.n_rows == 0) return YITU_OK;
+    GatParams p{};
+    fill_gat(p, a);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t D = a->n_heads * a->n_feats;
+    const int sm = 32 + 32 * p.H + 4 * 32;
+    if (D <= 128) return launch_rows(gat_fwd_kernel<1>, p, sm, st);
+    if (D <= 256) return launch_rows(gat_fwd_kernel<2>, p, sm, st);
+    return launch_rows(gat_fwd_kernel<4>, p, sm, st);
+}
+
+extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
+    YITU_REQUIRE(b != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
+    const yitu_gat_args_t *a = &b->fwd;
+    if (int rc = check_gat(a, true)) return rc;
+    const yitu_csr_t &g = a->graph;
+    YITU_REQUIRE(g.nnz < (1ll << 31), YITU_ERR_LIMIT, "fused GAT backward needs nnz < 2^31");
+    YITU_REQUIRE(b->grad_out && b->grad_query && b->grad_key && b->grad_x && b->t_indptr, YITU_ERR_INVALID_ARG,
+                 "NULL tensor");
+    YITU_REQUIRE(g.nnz == 0 || (b->t_rows && b->t_perm && b->edge_attn && b->edge_grad), YITU_ERR_INVALID_ARG,
+                 "NULL transposed graph or scratch");
+    YITU_REQUIRE(aligned16(b->grad_out) && aligned16(b->grad_x), YITU_ERR_INVALID_ARG,
+                 "grad_out / grad_x must be 16-byte aligned");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t H = a->n_heads, F = a->n_feats, D = H * F;
+    if (g.n_rows > 0) {
+        GatParams p{};
+        fill_gat(p, a);
+        p.grad_out = b->grad_out; p.grad_q = b->grad_query; p.edge_attn = b->edge_attn; p.edge_grad = b->edge_grad;
+        const int sm = 32 + 3 * 32 * p.H + 3 * 32;
+        int rc;
+        if (D <= 128) rc = launch_rows(gat_bwd_rows_kernel<1>, p, sm, st);
+        else if (D <= 256) rc = launch_rows(gat_bwd_rows_kernel<2>, p, sm, st);
+        else rc = launch_rows(gat_bwd_rows_kernel<4>, p, sm, st);
+        if (rc) return rc;
+    }
+    // source-side pass: grad_x = A^T-weighted gather of grad_out rows, grad_key = per-source sum of d score
+    yitu_spmm_args_t s{};
+    s.graph.n_rows = g.n_cols; s.graph.n_cols = g.n_rows; s.graph.nnz = g.nnz;
+    s.graph.indptr = b->t_indptr; s.graph.indptr_is64 = g.indptr_is64; s.graph.index_mask = 0;
+    s.graph.indices = b->t_rows;
+    s.n_heads = H; s.n_feats = F; s.weight_mode = YITU_W_EDGE_HEAD;
+    s.edge_values = b->edge_attn; s.edge_perm = b->t_perm; s.alpha = 1.0f;
+    s.x = b->grad_out; s.x_stride = D; s.out = b->grad_x; s.out_stride = D;
+    if (int rc = yitu_spmm_csr_f32(&s, stream)) return rc;
+    return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
+                                    stream);
+}

@@ -1,0 +1,79 @@
+// Shared helpers of the yitu_b200 CUDA library (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/yitu_b200.h"
+
+namespace yitu {
+
+void set_error(const char *fmt, ...);
+
+#define YITU_REQUIRE(cond, code, ...)      \
+    do {                                   \
+        if (!(cond)) {                     \
+            ::yitu::set_error(__VA_ARGS__); \
+            return (code);                 \
+        }                                  \
+    } while (0)
+
+#define YITU_CUDA(expr)                                                                              \
+    do {                                                                                             \
+        cudaError_t e_ = (expr);                                                                     \
+        if (e_ != cudaSuccess) {                                                                     \
+            ::yitu::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return YITU_ERR_CUDA;                                                                    \
+        }                                                                                            \
+    } while (0)
+
+#define YITU_LAUNCH_CHECK()                                                                      \
+    do {                                                                                         \
+        cudaError_t e_ = cudaGetLastError();                                                     \
+        if (e_ != cudaSuccess) {                                                                 \
+            ::yitu::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return YITU_ERR_CUDA;                                                                \
+        }                                                                                        \
+    } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ int64_t load_ptr(const void *indptr, int is64, int64_t i) {
+    return is64 ? __ldg(reinterpret_cast<const int64_t *>(indptr) + i)
+                : static_cast<int64_t>(__ldg(reinterpret_cast<const int32_t *>(indptr) + i));
+}
+
+__device__ __forceinline__ float leaky_relu(float v, float slope) {
+    return fmaxf(0.0f, v) + slope * fminf(0.0f, v);
+}
+
+// Read-only 128-bit / 32-bit loads of data that is streamed once (indices, edge values):
+// keep them out of L1 so the gathered feature rows own it.
+__device__ __forceinline__ int ld_stream(const int *p) {
+    int v;
+    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_stream(const float *p) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+inline int validate_csr(const yitu_csr_t *g) {
+    YITU_REQUIRE(g != nullptr, YITU_ERR_INVALID_ARG, "graph is NULL");
+    YITU_REQUIRE(g->n_rows >= 0 && g->n_cols >= 0 && g->nnz >= 0, YITU_ERR_INVALID_ARG,
+                 "negative graph size (n_rows=%lld n_cols=%lld nnz=%lld)", (long long)g->n_rows,
+                 (long long)g->n_cols, (long long)g->nnz);
+    YITU_REQUIRE(g->indptr != nullptr, YITU_ERR_INVALID_ARG, "graph.indptr is NULL");
+    YITU_REQUIRE(g->nnz == 0 || g->indices != nullptr, YITU_ERR_INVALID_ARG, "graph.indices is NULL");
+    YITU_REQUIRE(g->n_rows < (1ll << 31) && g->n_cols < (1ll << 31), YITU_ERR_LIMIT,
+                 "node ids must fit int32 (n_rows=%lld n_cols=%lld)", (long long)g->n_rows, (long long)g->n_cols);
+    YITU_REQUIRE(g->indptr_is64 || g->nnz < (1ll << 31), YITU_ERR_LIMIT,
+                 "nnz=%lld needs int64 row pointers", (long long)g->nnz);
+    YITU_REQUIRE(g->index_mask == 0 || g->index_mask == 0xffffff, YITU_ERR_INVALID_ARG,
+                 "index_mask must be 0 or 0xffffff");
+    return YITU_OK;
+}
+
+}  // namespace yitu

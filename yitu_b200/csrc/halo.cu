@@ -1,0 +1,59 @@
+// Halo fetch for the row-partitioned SpMM: copies the listed rows of a feature matrix that is sharded over
+// several GPUs into a dense local buffer, reading remote shards with ordinary loads through NVLink peer
+// mappings.  One warp per row, 128-bit accesses; bound by NVLink bandwidth for remote rows.
+#include "common.cuh"
+
+namespace yitu {
+
+struct HaloParams {
+    const float *ptr[16];
+    int64_t bound[17];
+    int n_shards;
+    const int *ids;
+    int64_t n_ids, row_floats;
+    float *dst;
+};
+
+__global__ void __launch_bounds__(256) halo_gather_kernel(const __grid_constant__ HaloParams p) {
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int64_t nvec = p.row_floats >> 2;
+    for (int64_t i = warp; i < p.n_ids; i += n_warps) {
+        const int64_t id = __ldg(p.ids + i);
+        int s = 0;
+        while (s + 1 < p.n_shards && id >= p.bound[s + 1]) ++s;
+        const float4 *src = reinterpret_cast<const float4 *>(p.ptr[s] + (id - p.bound[s]) * p.row_floats);
+        float4 *dst = reinterpret_cast<float4 *>(p.dst + i * p.row_floats);
+        for (int64_t v = lane; v < nvec; v += 32) dst[v] = src[v];
+    }
+}
+
+}  // namespace yitu
+
+using namespace yitu;
+
+extern "C" int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host,
+                                    const int64_t *shard_bounds_host, const int32_t *ids, int64_t n_ids,
+                                    int64_t row_floats, float *dst, yitu_stream_t stream) {
+    YITU_REQUIRE(n_shards >= 1 && n_shards <= 16, YITU_ERR_LIMIT, "n_shards=%d (1..16)", n_shards);
+    YITU_REQUIRE(shard_ptrs_host && shard_bounds_host, YITU_ERR_INVALID_ARG, "NULL shard table");
+    YITU_REQUIRE(row_floats > 0 && row_floats % 4 == 0, YITU_ERR_INVALID_ARG, "row_floats must be a multiple of 4");
+    if (n_ids == 0) return YITU_OK;
+    YITU_REQUIRE(ids && dst && aligned16(dst), YITU_ERR_INVALID_ARG, "NULL or misaligned ids/dst");
+    HaloParams p{};
+    p.n_shards = n_shards;
+    for (int s = 0; s < n_shards; ++s) {
+        YITU_REQUIRE(shard_ptrs_host[s] && aligned16(shard_ptrs_host[s]), YITU_ERR_INVALID_ARG,
+                     "shard %d pointer NULL or misaligned", s);
+        p.ptr[s] = shard_ptrs_host[s];
+        p.bound[s] = shard_bounds_host[s];
+    }
+    p.bound[n_shards] = shard_bounds_host[n_shards];
+    p.ids = ids; p.n_ids = n_ids; p.row_floats = row_floats; p.dst = dst;
+    const int64_t blocks = (n_ids + 7) / 8;
+    const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
+    halo_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}

@@ -1,0 +1,291 @@
+// CSR pull SpMM for sm_100a:  out[r,:] = alpha*row_scale[r] * sum_{e in row r} w(e) * x[col_e,:]
+//
+// Work decomposition
+//   * a group of LPR lanes (4..32, one warp for rows of >= 128 floats) owns one destination row, or one
+//     chunk of a hub row; each lane keeps NV independent 128-bit accumulators, so a warp has up to
+//     4 edges x NV x 512 B of feature gathers in flight;
+//   * column ids / edge weights are fetched LPR at a time, one per lane (coalesced, streamed past L1)
+//     and broadcast with warp shuffles, so the gather loop issues nothing but 128-bit loads and FMAs;
+//   * rows longer than plan->chunk_edges are cut into chunks handled by the first n_chunks groups of the
+//     grid (scheduled first: they are the longest tasks); partial sums land in scratch and a second tiny
+//     kernel adds them in chunk order.  No float atomics anywhere: results are run-to-run identical.
+//
+// The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
+// values), per row = 4*D written + one row pointer.
+#include "common.cuh"
+
+namespace yitu {
+
+struct SpmmParams {
+    int64_t n_rows, D, H, F;
+    const void *indptr;
+    const int *indices;
+    int is64, mask, wmode, accumulate;
+    const float *values;
+    const int *perm;
+    const float *norm_dst, *norm_src, *row_scale;
+    float alpha;
+    const float *x;
+    int64_t xs;
+    float *out;
+    int64_t os;
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+    float *scratch;
+};
+
+template <int VEC>
+__device__ __forceinline__ void load_vec(float (&r)[VEC], const float *p) {
+    if constexpr (VEC == 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    } else {
+        r[0] = __ldg(p);
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec(float *p, const float (&r)[VEC]) {
+    if constexpr (VEC == 4) {
+        *reinterpret_cast<float4 *>(p) = make_float4(r[0], r[1], r[2], r[3]);
+    } else {
+        *p = r[0];
+    }
+}
+
+template <int LPR, int NV, int VEC, bool PER_HEAD>
+__global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmParams p) {
+    const int lane = threadIdx.x & 31;
+    const int l = lane & (LPR - 1);
+    const unsigned gmask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
+    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / LPR;
+    const int64_t d0 = static_cast<int64_t>(blockIdx.y) * (LPR * NV * VEC);
+
+    int64_t row, eb, ee;
+    float *dst;
+    bool raw;
+    if (gid < p.n_chunks) {
+        row = __ldg(p.chunk_row + gid);
+        eb = __ldg(p.chunk_begin + gid);
+        const int64_t rend = load_ptr(p.indptr, p.is64, row + 1);
+        ee = min(eb + static_cast<int64_t>(p.chunk_edges), rend);
+        dst = p.scratch + gid * p.D;
+        raw = true;
+    } else {
+        row = gid - p.n_chunks;
+        if (row >= p.n_rows) return;
+        eb = load_ptr(p.indptr, p.is64, row);
+        ee = load_ptr(p.indptr, p.is64, row + 1);
+        if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;  // hub row: done by its chunks
+        dst = p.out + row * p.os;
+        raw = false;
+    }
+
+    int64_t off[NV];
+    bool valid[NV];
+    int hd[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        off[i] = d0 + static_cast<int64_t>(i * LPR + l) * VEC;
+        valid[i] = off[i] < p.D;
+        hd[i] = PER_HEAD ? static_cast<int>(off[i] / p.F) : 0;
+    }
+
+    float acc[NV][VEC];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[i][v] = 0.0f;
+
+    const float nd = (p.wmode == YITU_W_NODE) ? __ldg(p.norm_dst + row) : 0.0f;
+
+    for (int64_t e0 = eb; e0 < ee; e0 += LPR) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(LPR), ee - e0));
+        int my_col = 0, my_vi = 0;
+        float my_w = 0.0f;
+        if (l < n) {
+            const int64_t e = e0 + l;
+            const int rawidx = ld_stream(p.indices + e);
+            my_col = p.mask ? (rawidx & p.mask) : rawidx;
+            if constexpr (PER_HEAD) {
+                my_vi = p.perm ? ld_stream(p.perm + e) : static_cast<int>(e);
+            } else {
+                if (p.wmode == YITU_W_NONE) {
+                    my_w = 1.0f;
+                } else if (p.wmode == YITU_W_NODE) {
+                    my_w = nd * __ldg(p.norm_src + my_col);
+                } else {
+                    const int64_t vi = p.perm ? static_cast<int64_t>(ld_stream(p.perm + e)) : e;
+                    my_w = ld_stream(p.values + vi);
+                }
+            }
+        }
+        // lanes past the end of the row repeat the tile's first edge with weight 0, so the gather loop
+        // below runs in steps of 4 edges without a remainder path (the repeated row is an L1 hit)
+        const int c_first = __shfl_sync(gmask, my_col, 0, LPR);
+        const int v_first = PER_HEAD ? __shfl_sync(gmask, my_vi, 0, LPR) : 0;
+        if (l >= n) {
+            my_col = c_first;
+            my_vi = v_first;
+        }
+        const int n4 = (n + 3) & ~3;
+        for (int j = 0; j < n4; j += 4) {
+            int c[4], vi[4];
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                c[u] = __shfl_sync(gmask, my_col, j + u, LPR);
+                if constexpr (PER_HEAD) {
+                    vi[u] = __shfl_sync(gmask, my_vi, j + u, LPR);
+                } else {
+                    w[u] = __shfl_sync(gmask, my_w, j + u, LPR);
+                }
+            }
+            float v[4][NV][VEC];
+            float wh[4][NV];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float *xr = p.x + static_cast<int64_t>(c[u]) * p.xs;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    if (valid[i]) {
+                        load_vec<VEC>(v[u][i], xr + off[i]);
+                        if constexpr (PER_HEAD)
+                            wh[u][i] = (j + u < n) ? __ldg(p.values + static_cast<int64_t>(vi[u]) * p.H + hd[i]) : 0.0f;
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) v[u][i][q] = 0.0f;
+                        wh[u][i] = 0.0f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const float ww = PER_HEAD ? wh[u][i] : w[u];
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) acc[i][q] = fmaf(ww, v[u][i][q], acc[i][q]);
+                }
+        }
+    }
+
+    if (raw) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (valid[i]) store_vec<VEC>(dst + off[i], acc[i]);
+    } else {
+        const float s = p.alpha * (p.row_scale ? __ldg(p.row_scale + row) : 1.0f);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (!valid[i]) continue;
+            float r[VEC];
+            if (p.accumulate) {
+                load_vec<VEC>(r, dst + off[i]);
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) r[q] = fmaf(s, acc[i][q], r[q]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) r[q] = s * acc[i][q];
+            }
+            store_vec<VEC>(dst + off[i], r);
+        }
+    }
+}
+
+// Adds the chunk partials of each hub row in chunk order and applies the epilogue.
+__global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__ SpmmParams p) {
+    const int64_t chunk = blockIdx.x;
+    const int64_t row = __ldg(p.chunk_row + chunk);
+    const int64_t rb = load_ptr(p.indptr, p.is64, row);
+    if (__ldg(p.chunk_begin + chunk) != rb) return;  // only a row's first chunk reduces
+    const int64_t re = load_ptr(p.indptr, p.is64, row + 1);
+    const int64_t nch = (re - rb + p.chunk_edges - 1) / p.chunk_edges;
+    const float s = p.alpha * (p.row_scale ? __ldg(p.row_scale + row) : 1.0f);
+    for (int64_t d = threadIdx.x; d < p.D; d += blockDim.x) {
+        float a = 0.0f;
+        for (int64_t k = 0; k < nch; ++k) a += p.scratch[(chunk + k) * p.D + d];
+        float *o = p.out + row * p.os + d;
+        *o = p.accumulate ? fmaf(s, a, *o) : s * a;
+    }
+}
+
+template <int LPR, int NV, int VEC>
+static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
+    const int64_t groups = p.n_chunks + p.n_rows;
+    if (groups == 0) return YITU_OK;
+    const int gpb = 256 / LPR;
+    const int64_t gx = (groups + gpb - 1) / gpb;
+    const int64_t gy = (p.D + LPR * NV * VEC - 1) / (LPR * NV * VEC);
+    YITU_REQUIRE(gx < (1ll << 31) && gy <= 65535, YITU_ERR_LIMIT, "spmm grid too large (%lld x %lld)",
+                 (long long)gx, (long long)gy);
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    if (per_head)
+        spmm_kernel<LPR, NV, VEC, true><<<grid, 256, 0, st>>>(p);
+    else
+        spmm_kernel<LPR, NV, VEC, false><<<grid, 256, 0, st>>>(p);
+    YITU_LAUNCH_CHECK();
+    if (p.n_chunks > 0) {
+        hub_reduce_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
+    return YITU_OK;
+}
+
+}  // namespace yitu
+
+using namespace yitu;
+
+extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream) {
+    YITU_REQUIRE(a != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
+    if (int rc = validate_csr(&a->graph)) return rc;
+    const yitu_csr_t &g = a->graph;
+    YITU_REQUIRE(a->n_heads >= 1 && a->n_feats >= 1, YITU_ERR_INVALID_ARG, "n_heads=%lld n_feats=%lld",
+                 (long long)a->n_heads, (long long)a->n_feats);
+    const int64_t D = a->n_heads * a->n_feats;
+    YITU_REQUIRE(a->x_stride >= D && a->out_stride >= D, YITU_ERR_INVALID_ARG,
+                 "row strides (%lld, %lld) smaller than H*F=%lld", (long long)a->x_stride,
+                 (long long)a->out_stride, (long long)D);
+    YITU_REQUIRE(g.n_rows == 0 || a->out != nullptr, YITU_ERR_INVALID_ARG, "out is NULL");
+    YITU_REQUIRE(g.nnz == 0 || a->x != nullptr, YITU_ERR_INVALID_ARG, "x is NULL");
+    YITU_REQUIRE(a->weight_mode >= YITU_W_NONE && a->weight_mode <= YITU_W_EDGE_HEAD, YITU_ERR_INVALID_ARG,
+                 "unknown weight_mode %d", a->weight_mode);
+    if (a->weight_mode == YITU_W_NODE)
+        YITU_REQUIRE(a->norm_dst && a->norm_src, YITU_ERR_INVALID_ARG, "W_NODE needs norm_dst and norm_src");
+    if (a->weight_mode == YITU_W_EDGE || a->weight_mode == YITU_W_EDGE_HEAD)
+        YITU_REQUIRE(g.nnz == 0 || a->edge_values, YITU_ERR_INVALID_ARG, "edge_values is NULL");
+    const bool per_head = a->weight_mode == YITU_W_EDGE_HEAD;
+    if (per_head)
+        YITU_REQUIRE(g.nnz < (1ll << 31), YITU_ERR_LIMIT, "per-head edge values need nnz < 2^31");
+
+    SpmmParams p{};
+    p.n_rows = g.n_rows; p.D = D; p.H = a->n_heads; p.F = a->n_feats;
+    p.indptr = g.indptr; p.indices = g.indices; p.is64 = g.indptr_is64; p.mask = g.index_mask;
+    p.wmode = a->weight_mode; p.accumulate = a->accumulate;
+    p.values = a->edge_values; p.perm = a->edge_perm;
+    p.norm_dst = a->norm_dst; p.norm_src = a->norm_src; p.row_scale = a->row_scale; p.alpha = a->alpha;
+    p.x = a->x; p.xs = a->x_stride; p.out = a->out; p.os = a->out_stride;
+    if (a->plan && a->plan->n_chunks > 0) {
+        YITU_REQUIRE(a->plan->chunk_edges >= 32, YITU_ERR_INVALID_ARG, "plan.chunk_edges must be >= 32");
+        YITU_REQUIRE(a->plan->chunk_row && a->plan->chunk_begin, YITU_ERR_INVALID_ARG, "plan tables are NULL");
+        YITU_REQUIRE(a->scratch != nullptr && a->scratch_bytes >= a->plan->n_chunks * D * 4, YITU_ERR_WORKSPACE,
+                     "scratch needs %lld bytes, got %lld", (long long)(a->plan->n_chunks * D * 4),
+                     (long long)a->scratch_bytes);
+        p.n_chunks = a->plan->n_chunks; p.chunk_edges = a->plan->chunk_edges;
+        p.chunk_row = a->plan->chunk_row; p.chunk_begin = a->plan->chunk_begin; p.scratch = a->scratch;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    const bool vec_ok = (D % 4 == 0) && (a->x_stride % 4 == 0) && (a->out_stride % 4 == 0) && aligned16(a->x) &&
+                        aligned16(a->out) && (p.scratch == nullptr || aligned16(p.scratch)) &&
+                        (!per_head || a->n_feats % 4 == 0);
+    if (!vec_ok) return launch<32, 4, 1>(p, per_head, st);
+    if (D <= 16) return launch<4, 1, 4>(p, per_head, st);
+    if (D <= 32) return launch<8, 1, 4>(p, per_head, st);
+    if (D <= 64) return launch<16, 1, 4>(p, per_head, st);
+    if (D <= 128) return launch<32, 1, 4>(p, per_head, st);
+    if (D <= 256) return launch<32, 2, 4>(p, per_head, st);
+    return launch<32, 4, 4>(p, per_head, st);
+}

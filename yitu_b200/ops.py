@@ -1,0 +1,277 @@
+"""Tensor-level wrappers over the C ABI: argument checks, output allocation, stream forwarding, and the
+per-graph cache of derived structures (hub-row schedule, transposed graph).
+
+torch is plumbing here (device memory, the current stream); every aggregation runs in libyitu_b200.so.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import Csr, GatArgs, GatBwdArgs, HubPlan, SpmmArgs, W_EDGE, W_EDGE_HEAD, W_NODE, W_NONE, check, lib
+
+DEFAULT_CHUNK_EDGES = 512
+STITCH_MASK = 0xFFFFFF
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(t, name, dtype=None):
+    """Input contract of the reference bindings: CUDA, contiguous (ccsrc/kernel/YiTu_GNN.cpp:65-69) and,
+    for graph_ext, an exact dtype (YiTu_GNN/YiTu_H/src/common.h:6-12).  Violations raise RuntimeError."""
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError("%s must be a tensor" % name)
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return t
+
+
+def make_csr(indptr, indices, n_cols, index_mask=0):
+    is64 = indptr.dtype == torch.int64
+    if not is64 and indptr.dtype != torch.int32:
+        raise RuntimeError("row pointers must be int32 or int64, got %s" % indptr.dtype)
+    if indices.dtype != torch.int32:
+        raise RuntimeError("column indices must be int32, got %s" % indices.dtype)
+    return Csr(indptr.numel() - 1, int(n_cols), indices.numel(), _ptr(indptr), int(is64), int(index_mask),
+               _ptr(indices))
+
+
+class PreparedGraph:
+    """Derived structures of one CSR, built on first use and kept while the row-pointer tensor lives.
+
+    The reference prepares its schedule on the host once per graph (build_part,
+    examples/YiTu_GNN/single/gcn/main.py:90-100) and passes it with every call; the operators here take the
+    reference's arguments unchanged and find their own schedule through this cache instead.
+    """
+
+    def __init__(self, indptr, indices, n_cols, index_mask=0):
+        self.indptr, self.indices = indptr, indices
+        self.n_rows, self.n_cols, self.nnz = indptr.numel() - 1, int(n_cols), indices.numel()
+        self.index_mask = int(index_mask)
+        self.device = indptr.device
+        self.csr = make_csr(indptr, indices, n_cols, index_mask)
+        self._plans = {}
+        self._transpose = None
+        self._t_prepared = None
+        self._seg_mean = None
+
+    # hub-row schedule ---------------------------------------------------------------------------
+    def plan(self, chunk_edges=DEFAULT_CHUNK_EDGES):
+        """(HubPlan struct or None, tensors kept alive)."""
+        if chunk_edges in self._plans:
+            return self._plans[chunk_edges]
+        L = lib()
+        with torch.cuda.device(self.device):
+            ws_bytes = L.yitu_hub_plan_workspace_bytes(self.n_rows)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+            n_chunks = C.c_int64(0)
+            check(L.yitu_hub_plan_count(C.byref(self.csr), chunk_edges, _ptr(ws), ws_bytes, C.byref(n_chunks),
+                                        _stream(self.device)))
+            n = n_chunks.value
+            if n == 0:
+                result = None
+            else:
+                rows = torch.empty(n, dtype=torch.int32, device=self.device)
+                begins = torch.empty(n, dtype=torch.int64, device=self.device)
+                check(L.yitu_hub_plan_fill(C.byref(self.csr), chunk_edges, _ptr(ws), n, _ptr(rows), _ptr(begins),
+                                           _stream(self.device)))
+                result = (HubPlan(chunk_edges, 0, n, _ptr(rows), _ptr(begins)), rows, begins)
+        self._plans[chunk_edges] = result
+        return result
+
+    # transposed graph ---------------------------------------------------------------------------
+    def transpose(self):
+        """(t_indptr, t_rows, t_perm): CSC of this graph; t_perm[j] = CSR position of transposed edge j."""
+        if self._transpose is None:
+            L = lib()
+            with torch.cuda.device(self.device):
+                ws_bytes = L.yitu_csr_transpose_workspace_bytes(self.n_rows, self.n_cols, self.nnz)
+                ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=self.device)
+                t_indptr = torch.empty(self.n_cols + 1, dtype=self.indptr.dtype, device=self.device)
+                t_rows = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
+                t_perm = torch.empty(self.nnz, dtype=torch.int32, device=self.device)
+                check(L.yitu_csr_transpose(C.byref(self.csr), _ptr(t_indptr), _ptr(t_rows), _ptr(t_perm), _ptr(ws),
+                                           ws_bytes, _stream(self.device)))
+            self._transpose = (t_indptr, t_rows, t_perm)
+        return self._transpose
+
+    def t_prepared(self):
+        if self._t_prepared is None:
+            t_indptr, t_rows, _ = self.transpose()
+            self._t_prepared = PreparedGraph(t_indptr, t_rows, self.n_rows, 0)
+        return self._t_prepared
+
+    def segment_mean_weights(self):
+        """values[e] = 1 / #edges of e's (row, segment): mean per relation, summed over relations."""
+        if self._seg_mean is None:
+            vals = torch.empty(self.nnz, dtype=torch.float32, device=self.device)
+            with torch.cuda.device(self.device):
+                check(lib().yitu_segment_mean_weights_f32(C.byref(self.csr), _ptr(vals), _stream(self.device)))
+            self._seg_mean = vals
+        return self._seg_mean
+
+
+def prepared(indptr, indices, n_cols, index_mask=0):
+    """PreparedGraph cached on the row-pointer tensor object (dies with it; rebuilt if either tensor is
+    modified in place or paired with another index tensor)."""
+    stamp = (indices.data_ptr(), indices.numel(), indices._version, indptr._version)
+    cache = getattr(indptr, "_yitu_prepared", None)
+    if cache is None or cache[0] != stamp:
+        cache = (stamp, {})
+        indptr._yitu_prepared = cache
+    key = (int(n_cols), int(index_mask))
+    if key not in cache[1]:
+        cache[1][key] = PreparedGraph(indptr, indices, n_cols, index_mask)
+    return cache[1][key]
+
+
+def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, norm_dst=None, norm_src=None,
+         row_scale=None, alpha=1.0, out=None, accumulate=False, chunk_edges=DEFAULT_CHUNK_EDGES):
+    """out[r,h,k] = alpha*row_scale[r] * sum_e w(e,h) * x[col_e,h,k] through yitu_spmm_csr_f32.
+
+    x: [n_cols, H*F] or [n_cols, H, F] float32 CUDA; returns a tensor shaped like x with n_rows rows."""
+    if x.dtype != torch.float32:
+        raise RuntimeError("features must be float32, got %s" % x.dtype)
+    if x.size(0) != graph.n_cols:
+        raise RuntimeError("features have %d rows, the graph has %d source nodes" % (x.size(0), graph.n_cols))
+    x2 = x.reshape(x.size(0), -1)
+    D = x2.size(1)
+    if D % n_heads:
+        raise RuntimeError("feature width %d is not a multiple of n_heads=%d" % (D, n_heads))
+    if out is None:
+        out = torch.empty((graph.n_rows,) + tuple(x.shape[1:]), dtype=torch.float32, device=x.device)
+        accumulate = False
+    a = SpmmArgs()
+    a.graph = graph.csr
+    a.n_heads, a.n_feats = n_heads, D // n_heads
+    a.weight_mode, a.accumulate = mode, int(accumulate)
+    a.edge_values, a.edge_perm = _ptr(edge_values), _ptr(edge_perm)
+    a.norm_dst, a.norm_src, a.row_scale = _ptr(norm_dst), _ptr(norm_src), _ptr(row_scale)
+    a.alpha = float(alpha)
+    a.x, a.x_stride = _ptr(x2), D
+    a.out, a.out_stride = _ptr(out), D
+    keep = None
+    if chunk_edges:
+        pl = graph.plan(chunk_edges)
+        if pl is not None:
+            scratch = torch.empty(pl[0].n_chunks * D, dtype=torch.float32, device=x.device)
+            a.plan = C.pointer(pl[0])
+            a.scratch, a.scratch_bytes = _ptr(scratch), scratch.numel() * 4
+            keep = (pl, scratch)
+    with torch.cuda.device(x.device):
+        check(lib().yitu_spmm_csr_f32(C.byref(a), _stream(x.device)))
+    del keep
+    return out
+
+
+def edge_dot(graph, grad_out, x):
+    """grad_a[e,h] = <grad_out[row_e,h,:], x[col_e,h,:]>; grad_out [n_rows,H,F], x [n_cols,H,F]."""
+    H, F = x.size(1), x.size(2)
+    grad_a = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().yitu_edge_dot_f32(C.byref(graph.csr), H, F, _ptr(grad_out), _ptr(x), _ptr(grad_a),
+                                      _stream(x.device)))
+    return grad_a
+
+
+def edge_softmax_fwd(graph, query, key, slope=0.2):
+    """attn [nnz,H]; query [B,n_rows,H], key [n_cols,H]."""
+    B, H = query.size(0), key.size(1)
+    attn = torch.zeros((graph.nnz, H), dtype=torch.float32, device=key.device)
+    with torch.cuda.device(key.device):
+        check(lib().yitu_edge_softmax_fwd_f32(C.byref(graph.csr), B, H, slope, _ptr(query), _ptr(key), _ptr(attn),
+                                              _stream(key.device)))
+    return attn
+
+
+def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2):
+    """(grad_query [B,n_rows,H], grad_key [n_cols,H])."""
+    B, H = query.size(0), key.size(1)
+    grad_q = torch.empty_like(query)
+    edge_grad = torch.zeros_like(attn)
+    grad_k = torch.empty_like(key)
+    t_indptr, _, t_perm = graph.transpose()
+    L = lib()
+    with torch.cuda.device(key.device):
+        st = _stream(key.device)
+        check(L.yitu_edge_softmax_bwd_f32(C.byref(graph.csr), B, H, slope, _ptr(query), _ptr(key), _ptr(attn),
+                                          _ptr(grad_attn), _ptr(grad_q), _ptr(edge_grad), st))
+        check(L.yitu_edge_gather_sum_f32(graph.n_cols, _ptr(t_indptr), int(t_indptr.dtype == torch.int64),
+                                         _ptr(t_perm), H, _ptr(edge_grad), _ptr(grad_k), st))
+    return grad_q, grad_k
+
+
+def _gat_args(graph, query, key, x, out, row_max, row_sum, slope):
+    a = GatArgs()
+    a.graph = graph.csr
+    a.n_heads, a.n_feats, a.slope = x.size(1), x.size(2), slope
+    a.query, a.key, a.x = _ptr(query), _ptr(key), _ptr(x)
+    a.out, a.row_max, a.row_sum = _ptr(out), _ptr(row_max), _ptr(row_sum)
+    return a
+
+
+def gat_fused_supported(graph, n_heads, n_feats, backward=True):
+    lph = n_feats // 4
+    ok = graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
+    if backward:
+        ok = ok and lph <= 32 and (lph & (lph - 1)) == 0
+    return ok
+
+
+def gat_fwd(graph, query, key, x, slope=0.2):
+    """Fused scores + edge softmax + aggregation: (out [n_rows,H,F], row_max [n_rows,H], row_sum [n_rows,H])."""
+    H, F = x.size(1), x.size(2)
+    out = torch.empty((graph.n_rows, H, F), dtype=torch.float32, device=x.device)
+    row_max = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
+    row_sum = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
+    a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope)
+    with torch.cuda.device(x.device):
+        check(lib().yitu_gat_fwd_f32(C.byref(a), _stream(x.device)))
+    return out, row_max, row_sum
+
+
+def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2):
+    """(grad_query, grad_key, grad_x) of gat_fwd."""
+    H = x.size(1)
+    t_indptr, t_rows, t_perm = graph.transpose()
+    b = GatBwdArgs()
+    b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope)
+    grad_q = torch.empty_like(query)
+    grad_k = torch.empty_like(key)
+    grad_x = torch.empty_like(x)
+    edge_attn = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
+    edge_grad = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
+    b.grad_out = _ptr(grad_out)
+    b.t_indptr, b.t_rows, b.t_perm = _ptr(t_indptr), _ptr(t_rows), _ptr(t_perm)
+    b.grad_query, b.grad_key, b.grad_x = _ptr(grad_q), _ptr(grad_k), _ptr(grad_x)
+    b.edge_attn, b.edge_grad = _ptr(edge_attn), _ptr(edge_grad)
+    with torch.cuda.device(x.device):
+        check(lib().yitu_gat_bwd_f32(C.byref(b), _stream(x.device)))
+    return grad_q, grad_k, grad_x
+
+
+def partition_rows(graph, n_parts):
+    """Edge-balanced contiguous row ranges as an int64 device tensor [n_parts+1]."""
+    bounds = torch.empty(n_parts + 1, dtype=torch.int64, device=graph.device)
+    with torch.cuda.device(graph.device):
+        check(lib().yitu_partition_rows(C.byref(graph.csr), n_parts, _ptr(bounds), _stream(graph.device)))
+    return bounds
+
+
+def partition_rows_host(indptr, n_parts):
+    """Same partition from a CPU row-pointer tensor (int32 or int64)."""
+    indptr = indptr.contiguous()
+    bounds = torch.empty(n_parts + 1, dtype=torch.int64)
+    check(lib().yitu_partition_rows_host(indptr.numel() - 1, _ptr(indptr), int(indptr.dtype == torch.int64), n_parts,
+                                         _ptr(bounds)))
+    return bounds

@@ -1,0 +1,57 @@
+"""Block (CSR holder) and stitch_csr — interface of YiTu_GNN/YiTu_H/xgnn_h/block.py:5-67."""
+import ctypes as C
+from typing import List
+
+import torch
+
+from .._lib import check, lib
+
+
+class Block:
+    """size = [n_dst, n_src]; adj_sparse = [indptr int32, indices int32]; optional right_norm = 1/in_degree."""
+
+    def __init__(self, size: list, adj: list, right_norm=None):
+        self.size = size
+        self.adj_sparse = adj
+        self.right_norm = right_norm
+
+    def to(self, device):
+        self.adj_sparse = [self.adj_sparse[0].to(device), self.adj_sparse[1].to(device)]
+        if self.right_norm is not None:
+            self.right_norm = self.right_norm.to(device)
+        return self
+
+    def num_edges(self):
+        assert self.adj_sparse[1].dim() == 1
+        return self.adj_sparse[1].numel()
+
+    def num_src_nodes(self):
+        return self.size[1]
+
+    def num_dst_nodes(self):
+        assert self.adj_sparse[0].dim() == 1
+        assert self.size[0] == self.adj_sparse[0].size(0) - 1
+        return self.size[0]
+
+
+def stitch_csr(block_list: List[Block]):
+    """Pack up to 16 blocks with equal row counts into one segmented CSR: row r = row r of every block in
+    turn, index = (block id << 24) + column + columns of the blocks before.  Same result as the reference's
+    per-edge Python loop, computed by the library's host routine; the result lives on the CPU like there."""
+    rows = [blk.size[0] for blk in block_list]
+    assert len(rows) <= 16
+    assert min(rows) == max(rows)
+    n_rows = rows[0]
+    ips = [blk.adj_sparse[0].to("cpu", torch.int32).contiguous() for blk in block_list]
+    ids = [blk.adj_sparse[1].to("cpu", torch.int32).contiguous() for blk in block_list]
+    n_cols = torch.tensor([blk.size[1] for blk in block_list], dtype=torch.int64)
+    out_ip = torch.zeros(n_rows + 1, dtype=torch.int32)
+    out_id = torch.zeros(sum(i.numel() for i in ids), dtype=torch.int32)
+    PP = C.c_void_p * len(block_list)
+    try:
+        check(lib().yitu_stitch_csr_host(len(block_list), n_rows, PP(*[t.data_ptr() for t in ips]),
+                                         PP(*[t.data_ptr() for t in ids]), C.c_void_p(n_cols.data_ptr()),
+                                         C.c_void_p(out_ip.data_ptr()), C.c_void_p(out_id.data_ptr())))
+    except RuntimeError as e:  # the reference asserts
+        raise AssertionError(str(e))
+    return Block(size=[n_rows, int(n_cols.sum())], adj=[out_ip, out_id])
