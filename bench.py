@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the GNN aggregation hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload spmm|gat|rgcn|partitioned] [--impl reference]
+
+Prints ONE JSON line.  metric = aggregation throughput in Gedge*feat/s (stored edges x feature width per
+second, whole job).  A step is one pass of the workload's hot path over the resident synthetic graph:
+
+  spmm         1 GPU  R-MAT N=2^21, 2^26 sampled edges (deduplicated), fp32 per-edge symmetric-normalised
+                      weights, D=256: forward A*X and the transposed product A^T*G (2 * nnz * D edge-feats)
+  gat          1 GPU  uniform random N=2^20, 2^25 edges + self loops, 8 heads x 32: fused GAT forward+backward
+  rgcn         1 GPU  4 node types, 8 bipartite R-MAT relations x 4M edges, D=64: mean per relation, sum per type
+  partitioned  N GPUs R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, D=128, rows split into N
+                      edge-balanced ranges, halo source rows fetched over NVLink (strong scaling)
+
+Default: N=1 -> spmm; N>1 -> partitioned.  Inputs are far larger than L2 (126 MB), so no flush is needed
+between timed iterations.  `--impl reference` times the CPU restatement of the reference kernels (the
+reference has no CPU implementation of this path) on all host cores, on a bounded row slice.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "aggregation_gedge_feat_per_s"
+UNIT = "Gedge*feat/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def load_traffic(key):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary (None until profiled)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get(key)
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------ workloads
+class SpmmWorkload:
+    """configs[1]: forward and transposed sum-aggregation SpMM."""
+    name = "spmm_rmat_n2097152_e67108864_d256_fwd_bwd"
+    dominant_kernel = "spmm_kernel<32,2,4,false>"
+
+    def __init__(self, device, n=1 << 21, e=1 << 26, d=256):
+        import torch
+        from yitu_b200 import graphs, ops
+        self.torch, self.ops = torch, ops
+        self.n, self.d = n, d
+        self.indptr, self.indices, self.values = graphs.spmm_rmat(device=device, n=n, e=e)
+        self.nnz = self.indices.numel()
+        self.g = ops.PreparedGraph(self.indptr, self.indices, n)
+        self.gt = self.g.t_prepared()
+        self.values_t = self.values[self.g.transpose()[2].long()].contiguous()  # static weights, permuted once
+        self.x = graphs.randn_features(1, n, d, device=device)
+        self.grad = graphs.randn_features(2, n, d, device=device)
+        self.out = torch.empty_like(self.x)
+        self.gout = torch.empty_like(self.x)
+        self.g.plan(), self.gt.plan()
+        self.units_per_step = 2 * self.nnz * d
+        self.launches_per_step = 2 * (1 + (1 if self.g.plan() else 0))
+        self.kernel_launches_per_step = 2
+        # algorithmic bytes of ONE SpMM launch: per edge a feature row, a column id and a weight; per row a
+        # pointer and the written output row
+        self.kernel_bytes = self.nnz * (4 * d + 8) + (n + 1) * 4 + 4 * n * d
+        self.traffic_key = "spmm_rmat_d256"
+
+    def step(self, kernel_events=None):
+        t, ops = self.torch, self.ops
+        if kernel_events is not None:
+            a, b, c = (t.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record()
+        ops.spmm(self.g, self.x, mode=ops.W_EDGE, edge_values=self.values, out=self.out)
+        if kernel_events is not None:
+            b.record()
+        ops.spmm(self.gt, self.grad, mode=ops.W_EDGE, edge_values=self.values_t, out=self.gout)
+        if kernel_events is not None:
+            c.record()
+            kernel_events.append((a, b))
+            kernel_events.append((b, c))
+
+    def e2e_setup(self):
+        t = self.torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_g = self.grad.cpu().pin_memory()
+        self.h_out = t.empty(self.x.shape, dtype=t.float32).pin_memory()
+        self.h_gout = t.empty(self.x.shape, dtype=t.float32).pin_memory()
+        self.h2d = 2 * self.x.numel() * 4
+        self.d2h = 2 * self.x.numel() * 4
+
+    def e2e_step(self):
+        ops = self.ops
+        x = self.h_x.to(self.x.device, non_blocking=True)
+        g = self.h_g.to(self.x.device, non_blocking=True)
+        out = ops.spmm(self.g, x, mode=ops.W_EDGE, edge_values=self.values)
+        gout = ops.spmm(self.gt, g, mode=ops.W_EDGE, edge_values=self.values_t)
+        self.h_out.copy_(out, non_blocking=True)
+        self.h_gout.copy_(gout, non_blocking=True)
+
+    def verify(self):
+        """A*1 equals the in-degree exactly; cheap, size-independent."""
+        t, ops = self.torch, self.ops
+        ones = t.ones(self.n, 4, device=self.x.device)
+        deg = (self.indptr[1:] - self.indptr[:-1]).float()
+        assert t.equal(ops.spmm(self.g, ones)[:, 0], deg), "SpMM self-check failed"
+
+    def cpu_sample(self, seconds_hint=15.0):
+        """Row slice for the CPU baseline: ~1/16 of the rows from the middle of the graph, full features."""
+        lo, hi = self.n // 2, self.n // 2 + self.n // 16
+        ip = self.indptr[lo:hi + 1].cpu().numpy().astype("int64")
+        e0, e1 = int(ip[0]), int(ip[-1])
+        return dict(indptr=ip - e0, indices=self.indices[e0:e1].cpu().numpy(), values=self.values[e0:e1].cpu().numpy(),
+                    x=self.x.cpu().numpy(), nnz=e1 - e0, d=self.d,
+                    sample="rows [%d,%d) of %d (%d of %d edges), forward SpMM, full feature matrix" % (
+                        lo, hi, self.n, e1 - e0, self.nnz))
+
+
+class GatWorkload:
+    """configs[2]: fused GAT layer core forward + backward."""
+    name = "gat_uniform_n1048576_e33554432_h8_f32_fwd_bwd"
+    dominant_kernel = "gat_fwd_kernel<2>"
+
+    def __init__(self, device, n=1 << 20, e=1 << 25, H=8, F=32):
+        import torch
+        from yitu_b200 import graphs, ops
+        self.torch, self.ops = torch, ops
+        self.n, self.H, self.F, self.d = n, H, F, H * F
+        self.indptr, self.indices = graphs.gat_uniform(device=device, n=n, e=e)
+        self.nnz = self.indices.numel()
+        self.g = ops.PreparedGraph(self.indptr, self.indices, n)
+        self.g.transpose()
+        self.g.t_prepared().plan()
+        self.x = graphs.randn_features(1, n, H * F, device=device).view(n, H, F)
+        a_src = graphs.uniform_values(5, (H, F), -0.1, 0.1, device=device)
+        a_dst = graphs.uniform_values(6, (H, F), -0.1, 0.1, device=device)
+        self.k = (self.x * a_src).sum(-1).contiguous()
+        self.q = (self.x * a_dst).sum(-1).contiguous()
+        self.grad = graphs.randn_features(2, n, H * F, device=device).view(n, H, F)
+        self.units_per_step = 2 * self.nnz * self.d
+        self.launches_per_step = 1 + 3
+        self.kernel_launches_per_step = 1
+        self.kernel_bytes = self.nnz * (4 + 4 * H + 4 * H * F) + n * (4 + 4 * H + 4 * H * F + 8 * H)
+        self.traffic_key = "gat_fwd_h8_f32"
+
+    def step(self, kernel_events=None):
+        t, ops = self.torch, self.ops
+        if kernel_events is not None:
+            a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            a.record()
+        out, rmax, rsum = ops.gat_fwd(self.g, self.q, self.k, self.x)
+        if kernel_events is not None:
+            b.record()
+            kernel_events.append((a, b))
+        self.res = ops.gat_bwd(self.g, self.q, self.k, self.x, out, rmax, rsum, self.grad)
+
+    def e2e_setup(self):
+        t = self.torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_g = self.grad.cpu().pin_memory()
+        self.h_out = t.empty(self.x.shape, dtype=t.float32).pin_memory()
+        self.h2d = 2 * self.x.numel() * 4
+        self.d2h = self.x.numel() * 4
+
+    def e2e_step(self):
+        ops = self.ops
+        x = self.h_x.to(self.x.device, non_blocking=True)
+        g = self.h_g.to(self.x.device, non_blocking=True)
+        out, rmax, rsum = ops.gat_fwd(self.g, self.q, self.k, x)
+        gq, gk, gx = ops.gat_bwd(self.g, self.q, self.k, x, out, rmax, rsum, g)
+        self.h_out.copy_(gx, non_blocking=True)
+
+    def verify(self):
+        t, ops = self.torch, self.ops
+        out, _, rsum = ops.gat_fwd(self.g, self.q, self.k, t.ones_like(self.x))
+        assert float((out - 1.0).abs().max()) < 1e-5, "GAT self-check failed (softmax weights must sum to 1)"
+
+    def cpu_sample(self, seconds_hint=15.0):
+        lo, hi = 0, self.n // 16
+        ip = self.indptr[lo:hi + 1].cpu().numpy().astype("int64")
+        e0, e1 = int(ip[0]), int(ip[-1])
+        return dict(indptr=ip - e0, indices=self.indices[e0:e1].cpu().numpy(), q=self.q[lo:hi].cpu().numpy(),
+                    k=self.k.cpu().numpy(), x=self.x.cpu().numpy(), nnz=e1 - e0, d=self.d, gat=True,
+                    sample="rows [%d,%d) of %d (%d of %d edges), GAT forward (edge softmax + SpMM)" % (
+                        lo, hi, self.n, e1 - e0, self.nnz))
+
+
+class RgcnWorkload:
+    """configs[3]: hetero RGCN aggregation: per destination type one pass over the stitched relations."""
+    name = "rgcn_4types_8rel_x4M_d64"
+    dominant_kernel = "spmm_kernel<16,1,4,false>"
+
+    def __init__(self, device, d=64):
+        import torch
+        from yitu_b200 import graphs, ops
+        from yitu_b200.xgnn_h import Block, stitch_csr
+        self.torch, self.ops, self.d = torch, ops, d
+        sizes = graphs.HETERO_TYPES
+        rels = graphs.hetero_rgcn(device=device)
+        self.feats = [graphs.randn_features(10 + r, sizes[st], d, device=device) for r, (st, dt, _, _) in enumerate(rels)]
+        self.groups = []
+        self.nnz, self.kernel_bytes = 0, 0
+        for dt in sorted({r[1] for r in rels}):
+            ids = [i for i, r in enumerate(rels) if r[1] == dt]
+            st_blk = stitch_csr([Block([sizes[dt], sizes[rels[i][0]]], [rels[i][2], rels[i][3]]) for i in ids]).to(device)
+            xcat = torch.cat([self.feats[i] for i in ids])
+            g = ops.prepared(st_blk.adj_sparse[0], st_blk.adj_sparse[1], xcat.size(0), ops.STITCH_MASK)
+            w = g.segment_mean_weights()
+            g.plan()
+            self.groups.append((g, w, xcat, torch.empty(sizes[dt], d, device=device), st_blk))
+            self.nnz += g.nnz
+            self.kernel_bytes += g.nnz * (4 * d + 8) + (sizes[dt] + 1) * 4 + 4 * sizes[dt] * d
+        self.kernel_bytes //= len(self.groups)
+        self.units_per_step = self.nnz * d
+        self.launches_per_step = sum(1 + (1 if g.plan() else 0) for g, *_ in self.groups)
+        self.kernel_launches_per_step = len(self.groups)
+        self.traffic_key = "rgcn_d64"
+
+    def step(self, kernel_events=None):
+        t, ops = self.torch, self.ops
+        for g, w, xcat, out, _ in self.groups:
+            if kernel_events is not None:
+                a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+                a.record()
+            ops.spmm(g, xcat, mode=ops.W_EDGE, edge_values=w, out=out)
+            if kernel_events is not None:
+                b.record()
+                kernel_events.append((a, b))
+
+    def e2e_setup(self):
+        self.h_x = [xc.cpu().pin_memory() for _, _, xc, _, _ in self.groups]
+        self.h_out = [o.cpu().pin_memory() for _, _, _, o, _ in self.groups]
+        self.h2d = sum(x.numel() * 4 for x in self.h_x)
+        self.d2h = sum(o.numel() * 4 for o in self.h_out)
+
+    def e2e_step(self):
+        ops = self.ops
+        for (g, w, xcat, out, _), hx, ho in zip(self.groups, self.h_x, self.h_out):
+            x = hx.to(xcat.device, non_blocking=True)
+            ho.copy_(ops.spmm(g, x, mode=ops.W_EDGE, edge_values=w), non_blocking=True)
+
+    def verify(self):
+        t, ops = self.torch, self.ops
+        g, w, xcat, out, _ = self.groups[0]
+        res = ops.spmm(g, t.ones_like(xcat), mode=ops.W_EDGE, edge_values=w)[:, 0]
+        assert float((res - res.round()).abs().max()) < 1e-4, "RGCN self-check failed (sum of per-relation means of 1)"
+
+    def cpu_sample(self, seconds_hint=15.0):
+        g, w, xcat, out, _ = self.groups[0]
+        return dict(indptr=g.indptr.cpu().numpy().astype("int64"), indices=g.indices.cpu().numpy(),
+                    values=w.cpu().numpy(), x=xcat.cpu().numpy(), nnz=g.nnz, d=self.d, mask=0xFFFFFF,
+                    sample="destination type 0: %d rows, %d edges (of %d), stitched mean aggregation" % (
+                        g.n_rows, g.nnz, self.nnz))
+
+
+def cpu_baseline(sample, repeats=1):
+    """Times the CPU restatement (oracle/yitu_oracle.c, OpenMP over destination rows) on the sample."""
+    from oracle import oracle as O
+    cores = len(os.sched_getaffinity(0))
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    O.build()
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        if sample.get("gat"):
+            O.gat_forward(sample["indptr"], sample["indices"], sample["q"], sample["k"], sample["x"])
+        else:
+            O.spmm(sample["indptr"], sample["indices"], sample["x"], wmode=O.W_EDGE, values=sample["values"],
+                   index_mask=sample.get("mask", 0))
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": sample["nnz"] * sample["d"] / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": sample["sample"], "seconds": round(best, 3)}
+
+
+WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload}
+
+
+def run_single(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    wl = WORKLOADS[args.workload](dev)
+
+    if args.impl == "reference":
+        base = cpu_baseline(wl.cpu_sample(), repeats=max(1, args.steps))
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds"] * 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": wl.name, "note": "CPU restatement of the reference kernels; the reference has "
+                           "no CPU implementation of this path"},
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    wl.verify()
+    for _ in range(max(3, args.warmup)):
+        wl.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    time.sleep(0.3)
+    kernel_events = []
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        wl.step(kernel_events)
+    stop.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_total = start.elapsed_time(stop)
+    ms_step = ms_total / args.steps
+    value = wl.units_per_step / (ms_step * 1e-3) / 1e9
+    kms = [a.elapsed_time(b) for a, b in kernel_events]
+    k_avg_ms = sum(kms) / len(kms)
+    peak, peak_kind = load_peaks()
+    achieved = wl.kernel_bytes / (k_avg_ms * 1e-3) / 1e9
+
+    # end to end: pinned host features in, results back to pinned host memory, every step
+    wl.e2e_setup()
+    for _ in range(2):
+        wl.e2e_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_steps = max(2, min(args.steps, 5))
+    e0.record()
+    for _ in range(e_steps):
+        wl.e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_value = wl.units_per_step / (e0.elapsed_time(e1) / e_steps * 1e-3) / 1e9
+
+    base = None if args.no_cpu_baseline else cpu_baseline(wl.cpu_sample())
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "nnz": wl.nnz, "l2": "inputs_larger_than_l2",
+                       "edge_feats_per_step": wl.units_per_step},
+            "roofline": {"bound": "hbm", "kernel": wl.dominant_kernel, "achieved": achieved, "peak": peak,
+                         "peak_kind": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8000": achieved / 8000.0, "algorithmic_bytes_per_launch": wl.kernel_bytes,
+                         "avg_launch_ms": k_avg_ms, "traffic": load_traffic(wl.traffic_key)},
+            "cpu_baseline": base,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
+            "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="partitioned workload at 1/16 size (development)")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload is None:
+        args.workload = "spmm" if max(args.gpus, world) == 1 else "partitioned"
+    if args.workload == "partitioned":
+        from yitu_b200.distributed import bench_partitioned
+        bench_partitioned.run(args)
+        return
+    if int(os.environ.get("RANK", "0")) != 0:
+        return  # single-GPU workloads: extra ranks have nothing to do
+    run_single(args)
+
+
+if __name__ == "__main__":
+    main()
