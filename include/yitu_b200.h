@@ -141,6 +141,18 @@ typedef struct yitu_spmm_args_t {
 
 int yitu_spmm_csr_f32(const yitu_spmm_args_t *args, yitu_stream_t stream);
 
+/* The same SpMM for callers that may not allocate device memory (fixed-budget memory pools, plugins that
+ * are handed their buffers, latency-critical loops): the hub partial sums go to a 16 MiB array built into the
+ * library instead of args->scratch, which is ignored.  No counterpart in the reference.
+ *   - returns YITU_ERR_LIMIT when plan->n_chunks * H*F * 4 bytes exceed yitu_static_scratch_bytes();
+ *   - every GPU that loads the library holds the array until the process exits;
+ *   - all calls on a device share it: calls that overlap on the GPU race, so keep them on one stream;
+ *   - the first call on each device looks up the array's address (no allocation); make it before any
+ *     stream capture starts.
+ * Inputs, outputs and the hub plan are still the caller's. */
+int64_t yitu_static_scratch_bytes(void);
+int yitu_spmm_csr_f32_static(const yitu_spmm_args_t *args, yitu_stream_t stream);
+
 /* values[e] = 1 / (number of edges of e's row that carry e's segment id): with YITU_W_EDGE over a stitched
  * graph this turns the SpMM into "mean per relation, then sum over relations" in ONE pass and one output
  * write per destination row — the mathematics of HeteroGraphConv over GCNLayer with norm = 1/in_degree

@@ -59,6 +59,8 @@ SYMBOLS = {
     "yitu_build_part_host": (C.c_int, [c_i32, c_vp, c_i64, c_vp, c_vp]),
     "yitu_stitch_csr_host": (C.c_int, [c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "yitu_spmm_csr_f32": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
+    "yitu_static_scratch_bytes": (c_i64, []),
+    "yitu_spmm_csr_f32_static": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
     "yitu_segment_mean_weights_f32": (C.c_int, [C.POINTER(Csr), c_vp, c_vp]),
     "yitu_edge_dot_f32": (C.c_int, [C.POINTER(Csr), c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "yitu_edge_softmax_fwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp]),
