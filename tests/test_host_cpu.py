@@ -1,0 +1,172 @@
+"""Host-side logic of the product without a GPU: the C-ABI library loads and exports every declared symbol, the
+host tables (build_part, stitch_csr, row partition) match the reference's outputs bit for bit, the drop-in
+modules enforce the reference's input contract, and the graph generator is reproducible."""
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def _golden(name):
+    with open(os.path.join(GOLDEN, name + ".json")) as f:
+        return json.load(f)
+
+
+def test_library_exports_every_declared_symbol():
+    from yitu_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "yitu_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(yitu_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 20
+    L = _lib.lib()
+    for name in declared:
+        assert hasattr(L, name), "libyitu_b200.so does not export %s" % name
+    assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree: %s" % (declared ^ set(_lib.SYMBOLS))
+    assert L.yitu_version() >= 100
+    assert L.yitu_status_string(0) == b"ok"
+    assert L.yitu_static_scratch_bytes() == 16 << 20
+
+
+def test_struct_layouts_match_the_header():
+    """Sizes the C compiler gives the argument structs (LP64) — guards the ctypes mirrors."""
+    import ctypes as C
+    from yitu_b200 import _lib
+    assert C.sizeof(_lib.Csr) == 48
+    assert C.sizeof(_lib.HubPlan) == 32
+    assert C.sizeof(_lib.SpmmArgs) == 48 + 8 * 2 + 4 * 2 + 8 * 5 + 4 * 2 + 8 * 4 + 8 * 3
+    assert C.sizeof(_lib.GatArgs) == 48 + 16 + 8 + 48
+    assert C.sizeof(_lib.GatBwdArgs) == C.sizeof(_lib.GatArgs) + 9 * 8
+
+
+def test_build_part_bit_identical_to_reference():
+    from yitu_b200 import YiTu_GNN_kernel as K
+    for case in _golden("build_part"):
+        pp, p2n = K.build_part(case["part_size"], torch.IntTensor(case["indptr"]))
+        assert pp.dtype == torch.float32 and p2n.dtype == torch.float32 and not pp.is_cuda
+        assert pp.tolist() == case["part_ptr"] and p2n.tolist() == case["part2node"], case
+    with pytest.raises(RuntimeError):
+        K.build_part(32, torch.tensor([0, 1], dtype=torch.int64))
+
+
+def test_stitch_csr_bit_identical_to_reference():
+    from yitu_b200.xgnn_h import Block, stitch_csr
+    for case in _golden("stitch_csr"):
+        blocks = [Block([case["n_rows"], b["n_cols"]], [torch.IntTensor(b["indptr"]), torch.IntTensor(b["indices"])])
+                  for b in case["blocks"]]
+        st = stitch_csr(blocks)
+        assert st.size == case["size"]
+        assert st.adj_sparse[0].dtype == torch.int32 and st.adj_sparse[1].dtype == torch.int32
+        assert st.adj_sparse[0].tolist() == case["indptr"] and st.adj_sparse[1].tolist() == case["indices"]
+        assert st.num_edges() == len(case["indices"]) and st.num_dst_nodes() == case["n_rows"]
+
+
+def test_stitch_csr_limits():
+    from yitu_b200.xgnn_h import Block, stitch_csr
+    one = Block([1, 1], [torch.IntTensor([0, 1]), torch.IntTensor([0])])
+    with pytest.raises(AssertionError):
+        stitch_csr([one] * 17)
+    with pytest.raises(AssertionError):  # unequal row counts
+        stitch_csr([one, Block([2, 1], [torch.IntTensor([0, 1, 1]), torch.IntTensor([0])])])
+    big = Block([1, (1 << 24) + 5], [torch.IntTensor([0, 1]), torch.IntTensor([(1 << 24) + 3])])
+    with pytest.raises(AssertionError):  # column beyond 2^24, as the reference asserts
+        stitch_csr([big])
+
+
+def test_partition_rows_host(oracle):
+    from yitu_b200 import ops
+    rng = np.random.default_rng(4)
+    deg = rng.integers(0, 50, size=999)
+    deg[::97] = 3000
+    indptr = np.concatenate([[0], np.cumsum(deg)])
+    for dtype in (torch.int32, torch.int64):
+        for parts in (1, 2, 4, 8, 13):
+            got = ops.partition_rows_host(torch.from_numpy(indptr).to(dtype), parts)
+            assert got.tolist() == oracle.partition_rows(indptr.astype(np.int64), parts).tolist()
+
+
+def test_operators_reject_cpu_tensors():
+    """The reference's CHECK_INPUT (ccsrc/kernel/YiTu_GNN.cpp:65-69, YiTu_H/src/common.h:6-12) raises for
+    non-CUDA tensors; so do the drop-in modules, before anything touches a device."""
+    from yitu_b200 import YiTu_GNN_kernel as K, graph_ext
+    x = torch.randn(4, 8)
+    ip = torch.tensor([0, 1, 2, 3, 4], dtype=torch.int32)
+    ix = torch.tensor([0, 1, 2, 3], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        K.forward(x, torch.randn(8, 2), ip, ix, torch.ones(4), ip, ix, 32, 32, 2)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        graph_ext.spmm_forward(torch.randn(4, 1), ip, ix, x.view(4, 1, 8))
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        graph_ext.sddmm_forward(ip, ix, torch.randn(1, 4, 2), torch.randn(4, 2))
+
+
+def test_install_as_reference_modules():
+    import sys
+    import yitu_b200
+    saved = {k: sys.modules.get(k) for k in ("graph_ext", "YiTu_GNN", "YiTu_GNN.YiTu_GNN_kernel")}
+    try:
+        yitu_b200.install_as_reference_modules()
+        import graph_ext
+        from YiTu_GNN import YiTu_GNN_kernel
+        for fn in ("spmm_forward", "spmm_backward", "sddmm_forward", "sddmm_backward", "hfused_forward",
+                   "hfused_backward", "b2gemm", "b2gemm_backward"):
+            assert callable(getattr(graph_ext, fn))
+        for fn in ("SAG", "forward", "backward", "forward_gin", "backward_gin", "build_part"):
+            assert callable(getattr(YiTu_GNN_kernel, fn))
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+
+
+# ------------------------------------------------------------------------------------------- generators
+def _mix64_numpy(z):
+    z = z.astype(np.uint64)
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def test_mixer_matches_unsigned_reference_implementation():
+    from yitu_b200 import graphs
+    idx = torch.arange(0, 5000, dtype=torch.int64) * 7919 - 12345
+    got = graphs._mix64(idx).numpy().view(np.uint64)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(got, _mix64_numpy(idx.numpy().view(np.uint64)))
+
+
+def test_graph_generators_are_reproducible_and_canonical():
+    from yitu_b200 import graphs
+    a = graphs.gcn_small(n=4096, e=40000, seed=0)
+    b = graphs.gcn_small(n=4096, e=40000, seed=0)
+    c = graphs.gcn_small(n=4096, e=40000, seed=1)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    assert not torch.equal(a[1][:1000], c[1][:1000])
+    indptr, indices, norm = a
+    assert indptr.dtype == torch.int32 and indices.dtype == torch.int32
+    ip, ix = indptr.numpy(), indices.numpy()
+    for r in (0, 1, 17, 4095):
+        row = ix[ip[r]:ip[r + 1]]
+        assert np.all(np.diff(row) > 0), "columns must be ascending and unique within a row"
+        assert r in row, "self-loop present"
+    deg = np.diff(ip)
+    assert np.allclose(norm.numpy(), 1.0 / np.sqrt(deg), rtol=1e-6)
+    assert deg.max() > 20 * deg.mean(), "R-MAT skew expected"
+    # chunked generation does not change the stream
+    s1, d1 = graphs.rmat_edges(3, 1000, 700, 5000, chunk=1 << 25)
+    s2, d2 = graphs.rmat_edges(3, 1000, 700, 5000, chunk=777)
+    assert torch.equal(s1, s2) and torch.equal(d1, d2)
+    assert int(s1.max()) < 1000 and int(d1.max()) < 700 and int(s1.min()) >= 0
+    x = graphs.randn_features(5, 2000, 64)
+    assert abs(float(x.mean())) < 0.02 and abs(float(x.std()) - 1.0) < 0.02
+    rels = graphs.hetero_rgcn(type_sizes=(500, 300, 200, 100), e_per_rel=2000)
+    assert len(rels) == 8 and {r[1] for r in rels} == {0, 1, 2, 3}
+    for st, dt, ipr, ixr in rels:
+        assert ipr.numel() == (500, 300, 200, 100)[dt] + 1 and int(ixr.max()) < (500, 300, 200, 100)[st]
