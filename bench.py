@@ -430,6 +430,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--no-single", action="store_true", help="partitioned: skip the 1-GPU comparison run on rank 0")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload is None:

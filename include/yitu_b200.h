@@ -227,6 +227,17 @@ int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *args, yitu_stream_t stream);
 int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host, const int64_t *shard_bounds_host,
                          const int32_t *ids, int64_t n_ids, int64_t row_floats, float *dst, yitu_stream_t stream);
 
+/* Feature shards that peers can read.  yitu_shared_alloc allocates `bytes` of device memory on the current
+ * device (one cudaMalloc, so the pointer is an allocation base) and fills `handle_out` with its 64-byte CUDA IPC
+ * handle; another PROCESS passes those bytes to yitu_shared_open, with its own GPU current, and receives a pointer
+ * valid in kernels on that GPU (peer access over NVLink is enabled lazily by the driver).  yitu_shared_close
+ * unmaps an opened pointer, yitu_shared_free releases an allocated one.  Host-side calls; `handle` is host memory.
+ * Reworks the role of the pickled tensor exchange in YiTu_GNN/distributed/communication.py:83-162. */
+int yitu_shared_alloc(int64_t bytes, void **ptr_out, unsigned char *handle_out);
+int yitu_shared_open(const unsigned char *handle, void **ptr_out);
+int yitu_shared_close(void *ptr);
+int yitu_shared_free(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif

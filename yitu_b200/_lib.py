@@ -69,6 +69,10 @@ SYMBOLS = {
     "yitu_edge_gather_sum_f32": (C.c_int, [c_i64, c_vp, c_i32, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "yitu_gat_fwd_f32": (C.c_int, [C.POINTER(GatArgs), c_vp]),
     "yitu_gat_bwd_f32": (C.c_int, [C.POINTER(GatBwdArgs), c_vp]),
+    "yitu_shared_alloc": (C.c_int, [c_i64, C.POINTER(c_vp), c_vp]),
+    "yitu_shared_open": (C.c_int, [c_vp, C.POINTER(c_vp)]),
+    "yitu_shared_close": (C.c_int, [c_vp]),
+    "yitu_shared_free": (C.c_int, [c_vp]),
     "yitu_halo_gather_f32": (C.c_int, [c_i32, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
 }
 

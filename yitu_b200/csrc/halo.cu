@@ -1,6 +1,8 @@
 // Halo fetch for the row-partitioned SpMM: copies the listed rows of a feature matrix that is sharded over
 // several GPUs into a dense local buffer, reading remote shards with ordinary loads through NVLink peer
 // mappings.  One warp per row, 128-bit accesses; bound by NVLink bandwidth for remote rows.
+#include <cstring>
+
 #include "common.cuh"
 
 namespace yitu {
@@ -55,5 +57,46 @@ extern "C" int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_
     const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
     halo_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
     YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Peer-readable feature shards (CUDA IPC).  Allocation happens once per shard at set-up, never per step.
+// ---------------------------------------------------------------------------------------------------------
+static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+
+extern "C" int yitu_shared_alloc(int64_t bytes, void **ptr_out, unsigned char *handle_out) {
+    YITU_REQUIRE(bytes > 0 && ptr_out && handle_out, YITU_ERR_INVALID_ARG, "bad argument");
+    void *p = nullptr;
+    YITU_CUDA(cudaMalloc(&p, static_cast<size_t>(bytes)));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        set_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+        return YITU_ERR_CUDA;
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return YITU_OK;
+}
+
+extern "C" int yitu_shared_open(const unsigned char *handle, void **ptr_out) {
+    YITU_REQUIRE(handle && ptr_out, YITU_ERR_INVALID_ARG, "bad argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *p = nullptr;
+    YITU_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr_out = p;
+    return YITU_OK;
+}
+
+extern "C" int yitu_shared_close(void *ptr) {
+    if (ptr) YITU_CUDA(cudaIpcCloseMemHandle(ptr));
+    return YITU_OK;
+}
+
+extern "C" int yitu_shared_free(void *ptr) {
+    if (ptr) YITU_CUDA(cudaFree(ptr));
     return YITU_OK;
 }

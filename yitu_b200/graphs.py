@@ -119,14 +119,16 @@ def in_degrees(indptr):
     return (indptr[1:] - indptr[:-1]).to(torch.float32)
 
 
-def randn_features(seed, n, d, device="cpu", chunk_rows=1 << 20):
-    """N(0,1) float32 features, reproducible per (seed, row) on any device: Box-Muller over the mixer."""
+def randn_features(seed, n, d, device="cpu", chunk_rows=1 << 20, row_begin=0):
+    """N(0,1) float32 features, reproducible per (seed, row) on any device: Box-Muller over the mixer.
+    Returns rows [row_begin, row_begin + n) of the conceptual matrix, so a rank can make its shard alone."""
     out = torch.empty((n, d), dtype=torch.float32, device=device)
     flat = out.view(-1)
     total = n * d
     step = chunk_rows * d
+    base = row_begin * d
     for s in range(0, total, step):
-        idx = torch.arange(s, min(s + step, total), dtype=torch.int64, device=device)
+        idx = torch.arange(base + s, base + min(s + step, total), dtype=torch.int64, device=device)
         bits = _draw(seed, idx, 977)
         u1 = ((bits & 0xFFFFFF).to(torch.float32) + 1.0) * (1.0 / 16777216.0)          # (0,1]
         u2 = (((bits >> 24) & 0xFFFFFF).to(torch.float32)) * (1.0 / 16777216.0)        # [0,1)
