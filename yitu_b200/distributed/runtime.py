@@ -59,9 +59,9 @@ class SharedBuffer:
 class PartitionedSpmm:
     def __init__(self, shard, d, device, group=None, mode="peer", overlap=True, weight_mode=ops.W_EDGE):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
         self.rank = shard.rank
-        self.mode = mode if self.world > 1 else "local"
+        self.mode = mode if self.world > 1 else "local"  # "local": the shard is the whole graph, no exchange
         self.overlap = overlap and self.mode == "peer"
         self.weight_mode = weight_mode
         n_local = shard.n_local
