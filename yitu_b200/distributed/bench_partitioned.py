@@ -128,8 +128,12 @@ def run(args):
     launches_per_step = len([1 for tag, _, _ in events]) / args.steps
     k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (one or two launches)
     k_bytes = shard.nnz * (4 * d + 8) + (shard.n_local + 1) * 8 + 4 * shard.n_local * d
+    by_owner = [0.0] * world  # bytes this rank pulls from each owner per step
+    if getattr(runner, "plan", None) is not None and world > 1:
+        off = runner.plan.owner_offsets
+        by_owner = [float((off[p + 1] - off[p]) * d * 4) for p in range(world)]
     stats = torch.tensor([k_ms, sum(fetch_ms) / args.steps if fetch_ms else 0.0, float(runner.halo_bytes),
-                          float(shard.nnz), float(shard.n_local)], device=dev, dtype=torch.float64)
+                          float(shard.nnz), float(shard.n_local)] + by_owner, device=dev, dtype=torch.float64)
     all_stats = [torch.zeros_like(stats) for _ in range(world)]
     if world > 1:
         dist.all_gather(all_stats, stats)
@@ -180,7 +184,10 @@ def run(args):
                            "parallelism": "row_partition_%d" % world, "halo": best, "trial_ms": trial,
                            "l2": "inputs_larger_than_l2", "rows_per_rank": [int(s[4]) for s in per_rank],
                            "edges_per_rank": [int(s[3]) for s in per_rank],
-                           "halo_bytes_per_rank": [int(s[2]) for s in per_rank]},
+                           "halo_bytes_per_rank": [int(s[2]) for s in per_rank],
+                           "egress_bytes_per_rank": [int(sum(s[5 + o] for s in per_rank)) for o in range(world)],
+                           "spmm_ms_per_rank": [round(s[0], 3) for s in per_rank],
+                           "fetch_ms_per_rank": [round(s[1], 3) for s in per_rank]},
                 "roofline": {"bound": "hbm", "kernel": "spmm_kernel<32,1,4,false> (rank 0 shard)",
                              "achieved": achieved, "peak": peak, "peak_kind": "of " + peak_kind, "unit": "GB/s",
                              "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
