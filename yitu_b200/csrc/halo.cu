@@ -13,21 +13,50 @@ struct HaloParams {
     int n_shards;
     const int *ids;
     int64_t n_ids, row_floats;
+    int64_t stripes, per_stripe;  // visiting order: item j -> id position (j % stripes) * per_stripe + j / stripes
     float *dst;
 };
 
+// One warp moves ROWS rows at a time: all ROWS 128-bit loads of a lane are issued before the first store, so
+// a warp keeps ROWS * 512 B in flight on the link.  The grid is small (two 8-warp CTAs per SM) so that an SpMM
+// running on another stream keeps most of every SM.  The id list is sorted, hence grouped by owner; it is
+// visited in a striped order so that at any moment the pulls are spread over all owners (all links busy)
+// instead of every rank hammering owner 0 first, then owner 1, ...
+template <int ROWS>
 __global__ void __launch_bounds__(256) halo_gather_kernel(const __grid_constant__ HaloParams p) {
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     const int64_t nvec = p.row_floats >> 2;
-    for (int64_t i = warp; i < p.n_ids; i += n_warps) {
-        const int64_t id = __ldg(p.ids + i);
-        int s = 0;
-        while (s + 1 < p.n_shards && id >= p.bound[s + 1]) ++s;
-        const float4 *src = reinterpret_cast<const float4 *>(p.ptr[s] + (id - p.bound[s]) * p.row_floats);
-        float4 *dst = reinterpret_cast<float4 *>(p.dst + i * p.row_floats);
-        for (int64_t v = lane; v < nvec; v += 32) dst[v] = src[v];
+    const int64_t total = p.stripes * p.per_stripe;
+    for (int64_t j0 = warp * ROWS; j0 < total; j0 += n_warps * ROWS) {
+        const float4 *src[ROWS];
+        float4 *dst[ROWS];
+        bool ok[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const int64_t j = j0 + r;
+            const int64_t i = (j % p.stripes) * p.per_stripe + j / p.stripes;
+            ok[r] = j < total && i < p.n_ids;
+            src[r] = nullptr;
+            dst[r] = nullptr;
+            if (ok[r]) {
+                const int64_t id = __ldg(p.ids + i);
+                int s = 0;
+                while (s + 1 < p.n_shards && id >= p.bound[s + 1]) ++s;
+                src[r] = reinterpret_cast<const float4 *>(p.ptr[s] + (id - p.bound[s]) * p.row_floats);
+                dst[r] = reinterpret_cast<float4 *>(p.dst + i * p.row_floats);
+            }
+        }
+        for (int64_t v = lane; v < nvec; v += 32) {
+            float4 val[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (ok[r]) val[r] = src[r][v];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (ok[r]) dst[r][v] = val[r];
+        }
     }
 }
 
@@ -53,9 +82,12 @@ extern "C" int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_
     }
     p.bound[n_shards] = shard_bounds_host[n_shards];
     p.ids = ids; p.n_ids = n_ids; p.row_floats = row_floats; p.dst = dst;
-    const int64_t blocks = (n_ids + 7) / 8;
-    const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
-    halo_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    p.stripes = n_ids >= (1 << 16) ? 1024 : 1;
+    p.per_stripe = (n_ids + p.stripes - 1) / p.stripes;
+    constexpr int kRows = 4;
+    const int64_t blocks = (n_ids + 8 * kRows - 1) / (8 * kRows);
+    const unsigned grid = static_cast<unsigned>(blocks < 148 * 2 ? blocks : 148 * 2);
+    halo_gather_kernel<kRows><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
     YITU_LAUNCH_CHECK();
     return YITU_OK;
 }

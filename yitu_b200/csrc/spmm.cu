@@ -12,6 +12,8 @@
 //
 // The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
 // values), per row = 4*D written + one row pointer.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace yitu {
@@ -212,20 +214,30 @@ __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__
     }
 }
 
+static int block_threads() {
+    static const int v = [] {
+        const char *e = getenv("YITU_SPMM_BLOCK");
+        const int t = e ? atoi(e) : 128;
+        return (t == 32 || t == 64 || t == 128 || t == 256) ? t : 128;
+    }();
+    return v;
+}
+
 template <int LPR, int NV, int VEC>
 static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
     const int64_t groups = p.n_chunks + p.n_rows;
     if (groups == 0) return YITU_OK;
-    const int gpb = 256 / LPR;
+    const int threads = block_threads();
+    const int gpb = threads / LPR;
     const int64_t gx = (groups + gpb - 1) / gpb;
     const int64_t gy = (p.D + LPR * NV * VEC - 1) / (LPR * NV * VEC);
     YITU_REQUIRE(gx < (1ll << 31) && gy <= 65535, YITU_ERR_LIMIT, "spmm grid too large (%lld x %lld)",
                  (long long)gx, (long long)gy);
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
     if (per_head)
-        spmm_kernel<LPR, NV, VEC, true><<<grid, 256, 0, st>>>(p);
+        spmm_kernel<LPR, NV, VEC, true><<<grid, threads, 0, st>>>(p);
     else
-        spmm_kernel<LPR, NV, VEC, false><<<grid, 256, 0, st>>>(p);
+        spmm_kernel<LPR, NV, VEC, false><<<grid, threads, 0, st>>>(p);
     YITU_LAUNCH_CHECK();
     if (p.n_chunks > 0) {
         hub_reduce_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);

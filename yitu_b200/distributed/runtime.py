@@ -92,7 +92,7 @@ class PartitionedSpmm:
                     for p in range(self.world)]
             self._ptrs = (C.c_void_p * self.world)(*ptrs)
             self._bounds = (C.c_int64 * (self.world + 1))(*shard.bounds)
-            self.side = torch.cuda.Stream(device=self.device)
+            self.side = torch.cuda.Stream(device=self.device, priority=-1)
             if self.overlap:
                 (ipo, ixo, vo), (iph, ixh, vh) = split_local_halo(shard, self.plan)
                 self.g_own = ops.PreparedGraph(ipo, ixo, n_local)
