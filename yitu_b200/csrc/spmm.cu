@@ -12,14 +12,13 @@
 //
 // The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
 // values), per row = 4*D written + one row pointer.
-#include <cstdlib>
 
 #include "common.cuh"
 
 namespace yitu {
 
 struct SpmmParams {
-    int64_t n_rows, D, H, F;
+    int64_t n_rows, n_cols, D, H, F;
     const void *indptr;
     const int *indices;
     int is64, mask, wmode, accumulate;
@@ -57,8 +56,9 @@ __device__ __forceinline__ void store_vec(float *p, const float (&r)[VEC]) {
     }
 }
 
-template <int LPR, int NV, int VEC, bool PER_HEAD>
+template <int LPR, int NV, int VEC, int EU, bool PER_HEAD, bool IDX32>
 __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmParams p) {
+    static_assert(EU <= LPR && (EU & (EU - 1)) == 0, "edge unroll must be a power of two <= lanes per row");
     const int lane = threadIdx.x & 31;
     const int l = lane & (LPR - 1);
     const unsigned gmask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
@@ -125,19 +125,19 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
             }
         }
         // lanes past the end of the row repeat the tile's first edge with weight 0, so the gather loop
-        // below runs in steps of 4 edges without a remainder path (the repeated row is an L1 hit)
+        // below runs in steps of EU edges without a remainder path (the repeated row is an L1 hit)
         const int c_first = __shfl_sync(gmask, my_col, 0, LPR);
         const int v_first = PER_HEAD ? __shfl_sync(gmask, my_vi, 0, LPR) : 0;
         if (l >= n) {
             my_col = c_first;
             my_vi = v_first;
         }
-        const int n4 = (n + 3) & ~3;
-        for (int j = 0; j < n4; j += 4) {
-            int c[4], vi[4];
-            float w[4];
+        const int n_up = (n + EU - 1) & ~(EU - 1);
+        for (int j = 0; j < n_up; j += EU) {
+            int c[EU], vi[EU];
+            float w[EU];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < EU; ++u) {
                 c[u] = __shfl_sync(gmask, my_col, j + u, LPR);
                 if constexpr (PER_HEAD) {
                     vi[u] = __shfl_sync(gmask, my_vi, j + u, LPR);
@@ -145,15 +145,18 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
                     w[u] = __shfl_sync(gmask, my_w, j + u, LPR);
                 }
             }
-            float v[4][NV][VEC];
-            float wh[4][NV];
+            float v[EU][NV][VEC];
+            float wh[EU][NV];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < EU; ++u) {
                 const float *xr = p.x + static_cast<int64_t>(c[u]) * p.xs;
+                // 32-bit element offsets when the feature matrix has fewer than 2^32 elements
+                const uint32_t xr32 = static_cast<uint32_t>(c[u]) * static_cast<uint32_t>(p.xs);
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     if (valid[i]) {
-                        load_vec<VEC>(v[u][i], xr + off[i]);
+                        if constexpr (IDX32) load_vec<VEC>(v[u][i], p.x + (xr32 + static_cast<uint32_t>(off[i])));
+                        else load_vec<VEC>(v[u][i], xr + off[i]);
                         if constexpr (PER_HEAD)
                             wh[u][i] = (j + u < n) ? __ldg(p.values + static_cast<int64_t>(vi[u]) * p.H + hd[i]) : 0.0f;
                     } else {
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < EU; ++u)
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     const float ww = PER_HEAD ? wh[u][i] : w[u];
@@ -214,16 +217,11 @@ __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__
     }
 }
 
-static int block_threads() {
-    static const int v = [] {
-        const char *e = getenv("YITU_SPMM_BLOCK");
-        const int t = e ? atoi(e) : 128;
-        return (t == 32 || t == 64 || t == 128 || t == 256) ? t : 128;
-    }();
-    return v;
-}
+// 128-thread CTAs: with 256 a CTA waits for its longest row and occupancy drops (measured 7.57 -> 6.98 ms on the
+// D=256 R-MAT workload; 32/64/128/256 gave 6.86/7.21/6.98/7.57 ms and 128 was best over all workloads).
+static int block_threads() { return 128; }
 
-template <int LPR, int NV, int VEC>
+template <int LPR, int NV, int VEC, int EU>
 static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
     const int64_t groups = p.n_chunks + p.n_rows;
     if (groups == 0) return YITU_OK;
@@ -234,10 +232,15 @@ static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
     YITU_REQUIRE(gx < (1ll << 31) && gy <= 65535, YITU_ERR_LIMIT, "spmm grid too large (%lld x %lld)",
                  (long long)gx, (long long)gy);
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
-    if (per_head)
-        spmm_kernel<LPR, NV, VEC, true><<<grid, threads, 0, st>>>(p);
-    else
-        spmm_kernel<LPR, NV, VEC, false><<<grid, threads, 0, st>>>(p);
+    // element offsets into x fit 32 bits?
+    const bool idx32 = VEC == 4 && p.n_cols * p.xs < (1ll << 32);
+    if (per_head) {
+        if (idx32) spmm_kernel<LPR, NV, VEC, EU, true, true><<<grid, threads, 0, st>>>(p);
+        else spmm_kernel<LPR, NV, VEC, EU, true, false><<<grid, threads, 0, st>>>(p);
+    } else {
+        if (idx32) spmm_kernel<LPR, NV, VEC, EU, false, true><<<grid, threads, 0, st>>>(p);
+        else spmm_kernel<LPR, NV, VEC, EU, false, false><<<grid, threads, 0, st>>>(p);
+    }
     YITU_LAUNCH_CHECK();
     if (p.n_chunks > 0) {
         hub_reduce_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
@@ -273,7 +276,7 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
         YITU_REQUIRE(g.nnz < (1ll << 31), YITU_ERR_LIMIT, "per-head edge values need nnz < 2^31");
 
     SpmmParams p{};
-    p.n_rows = g.n_rows; p.D = D; p.H = a->n_heads; p.F = a->n_feats;
+    p.n_rows = g.n_rows; p.n_cols = g.n_cols; p.D = D; p.H = a->n_heads; p.F = a->n_feats;
     p.indptr = g.indptr; p.indices = g.indices; p.is64 = g.indptr_is64; p.mask = g.index_mask;
     p.wmode = a->weight_mode; p.accumulate = a->accumulate;
     p.values = a->edge_values; p.perm = a->edge_perm;
@@ -293,11 +296,13 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     const bool vec_ok = (D % 4 == 0) && (a->x_stride % 4 == 0) && (a->out_stride % 4 == 0) && aligned16(a->x) &&
                         aligned16(a->out) && (p.scratch == nullptr || aligned16(p.scratch)) &&
                         (!per_head || a->n_feats % 4 == 0);
-    if (!vec_ok) return launch<32, 4, 1>(p, per_head, st);
-    if (D <= 16) return launch<4, 1, 4>(p, per_head, st);
-    if (D <= 32) return launch<8, 1, 4>(p, per_head, st);
-    if (D <= 64) return launch<16, 1, 4>(p, per_head, st);
-    if (D <= 128) return launch<32, 1, 4>(p, per_head, st);
-    if (D <= 256) return launch<32, 2, 4>(p, per_head, st);
-    return launch<32, 4, 4>(p, per_head, st);
+    if (!vec_ok) return launch<32, 4, 1, 4>(p, per_head, st);
+    // lanes per row / 128-bit slices per lane / edges gathered per step, from a sweep on B200: narrower groups
+    // than the row lose coalescing; deeper unrolling pays while it fits the register budget
+    if (D <= 16) return launch<4, 1, 4, 4>(p, per_head, st);
+    if (D <= 32) return launch<8, 1, 4, 4>(p, per_head, st);
+    if (D <= 64) return launch<16, 1, 4, 4>(p, per_head, st);
+    if (D <= 128) return launch<32, 1, 4, 16>(p, per_head, st);
+    if (D <= 256) return launch<32, 2, 4, 8>(p, per_head, st);
+    return launch<32, 4, 4, 4>(p, per_head, st);
 }
