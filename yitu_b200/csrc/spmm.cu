@@ -10,6 +10,13 @@
 //     grid (scheduled first: they are the longest tasks); partial sums land in scratch and a second tiny
 //     kernel adds them in chunk order.  No float atomics anywhere: results are run-to-run identical.
 //
+// Measured alternatives that lost on B200 and are not kept: staging rows in a shared-memory ring with
+// cp.async.bulk + mbarrier (2.2x slower: 1 KiB per bulk copy is too fine a grain) or per-lane cp.async (equal
+// at best, only at the same occupancy); sub-warp groups narrower than the row (lose coalescing); a persistent
+// grid with software-pipelined row pointers / index tiles (1.7x slower than letting the CTA scheduler
+// balance short CTAs); batches of 8 consecutive rows per warp with the next row's index tile prefetched
+// (1.1-1.4x slower: fewer, longer warps hide less latency than many short ones).
+//
 // The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
 // values), per row = 4*D written + one row pointer.
 
@@ -221,7 +228,7 @@ __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__
 // D=256 R-MAT workload; 32/64/128/256 gave 6.86/7.21/6.98/7.57 ms and 128 was best over all workloads).
 static int block_threads() { return 128; }
 
-template <int LPR, int NV, int VEC, int EU>
+template <int LPR, int NV, int VEC, int EU, int EU_HEAD = 4>
 static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
     const int64_t groups = p.n_chunks + p.n_rows;
     if (groups == 0) return YITU_OK;
@@ -234,9 +241,9 @@ static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
     // element offsets into x fit 32 bits?
     const bool idx32 = VEC == 4 && p.n_cols * p.xs < (1ll << 32);
-    if (per_head) {
-        if (idx32) spmm_kernel<LPR, NV, VEC, EU, true, true><<<grid, threads, 0, st>>>(p);
-        else spmm_kernel<LPR, NV, VEC, EU, true, false><<<grid, threads, 0, st>>>(p);
+    if (per_head) {  // per-head weights cost registers per gathered slice: those variants unroll 4 edges only
+        if (idx32) spmm_kernel<LPR, NV, VEC, EU_HEAD, true, true><<<grid, threads, 0, st>>>(p);
+        else spmm_kernel<LPR, NV, VEC, EU_HEAD, true, false><<<grid, threads, 0, st>>>(p);
     } else {
         if (idx32) spmm_kernel<LPR, NV, VEC, EU, false, true><<<grid, threads, 0, st>>>(p);
         else spmm_kernel<LPR, NV, VEC, EU, false, false><<<grid, threads, 0, st>>>(p);
