@@ -84,3 +84,70 @@ def test_reference_sddmm_kernels(oracle, ref_ext, H, B, seed):
     assert_close(attn.cpu().numpy(), ref_attn.cpu().numpy(), rtol=2e-5, what="sddmm_forward vs reference kernel")
     assert_close(gq.cpu().numpy(), ref_gq.cpu().numpy(), rtol=2e-5, what="grad_query vs reference kernel")
     assert_close(gk.cpu().numpy(), ref_gk.cpu().numpy(), rtol=2e-5, what="grad_key vs reference kernel")
+
+
+@pytest.fixture(scope="module")
+def ref_ccsrc():
+    if not glob.glob(os.path.join(REF_DIR, "yitu_gnn_kernel_ref*.so")):
+        pytest.skip("reference YiTu_GNN_kernel not built (make -C oracle ref_gpu_ccsrc)")
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    return importlib.import_module("yitu_gnn_kernel_ref")
+
+
+def _symmetric_graph(rng, n, density):
+    dense = rng.random((n, n)) < density
+    dense = dense | dense.T
+    np.fill_diagonal(dense, True)
+    indptr = np.concatenate([[0], np.cumsum(dense.sum(1))]).astype(np.int32)
+    indices = np.nonzero(dense)[1].astype(np.int32)
+    return indptr, indices
+
+
+@pytest.mark.parametrize("n,d_in,d_out,seed", [(300, 48, 16, 0), (777, 64, 64, 1), (1500, 20, 7, 2)])
+def test_reference_ccsrc_kernels(oracle, ref_ccsrc, n, d_in, d_out, seed):
+    """GCN forward/backward, GIN forward/backward and SAG of the reference extension on a symmetric graph (the only
+    kind on which its backward is the gradient), against the CPU checker and against the drop-in module."""
+    from yitu_b200 import YiTu_GNN_kernel as K
+    rng = np.random.default_rng(200 + seed)
+    indptr, indices = _symmetric_graph(rng, n, 0.02)
+    deg = np.diff(indptr).astype(np.float32)
+    norm = (1.0 / np.sqrt(deg)).astype(np.float32)
+    x = rng.standard_normal((n, d_in)).astype(np.float32)
+    w = (rng.standard_normal((d_in, d_out)) * 0.2).astype(np.float32)
+    g = rng.standard_normal((n, d_out)).astype(np.float32)
+    pp, p2n = ref_ccsrc.build_part(32, torch.from_numpy(indptr))
+    mine_pp, mine_p2n = K.build_part(32, torch.from_numpy(indptr))
+    assert torch.equal(pp, mine_pp) and torch.equal(p2n, mine_p2n)
+    graph = (_dev(indptr), _dev(indices), _dev(norm), pp.int().cuda(), p2n.int().cuda(), 32, 32, 2)
+    dx, dw, dg = _dev(x), _dev(w), _dev(g)
+
+    ref_out = ref_ccsrc.forward(dx, dw, *graph)[0]
+    ref_din, ref_dw = ref_ccsrc.backward(dg, dx, dw, *graph)
+    torch.cuda.synchronize()
+    o_out = oracle.gcn_forward(x, w, indptr, indices, norm)
+    o_din, o_dw = oracle.gcn_backward(g, x, w, indptr, indices, norm, transpose=False)
+    assert_close(ref_out.cpu().numpy(), o_out, rtol=2e-5, what="reference GCN forward vs checker")
+    assert_close(ref_din.cpu().numpy(), o_din, rtol=3e-5, what="reference GCN d_input vs checker")
+    assert_close(ref_dw.cpu().numpy(), o_dw, rtol=3e-5, what="reference GCN d_weight vs checker")
+    out = K.forward(dx, dw, *graph)[0]
+    din, dwt = K.backward(dg, dx, dw, *graph)
+    assert_close(out.cpu().numpy(), ref_out.cpu().numpy(), rtol=2e-5, what="GCN forward vs reference kernel")
+    assert_close(din.cpu().numpy(), ref_din.cpu().numpy(), rtol=3e-5, what="GCN d_input vs reference kernel")
+    assert_close(dwt.cpu().numpy(), ref_dw.cpu().numpy(), rtol=3e-5, what="GCN d_weight vs reference kernel")
+
+    ref_sag = ref_ccsrc.SAG(dx, *graph)
+    assert_close(ref_sag.cpu().numpy(), oracle.spmm(indptr, indices, x), rtol=2e-5, what="reference SAG vs checker")
+    assert_close(K.SAG(dx, *graph).cpu().numpy(), ref_sag.cpu().numpy(), rtol=2e-5, what="SAG vs reference kernel")
+
+    gin_graph = (graph[0], graph[1], 0.5) + graph[3:]
+    ref_o, ref_agg = ref_ccsrc.forward_gin(dx, dw, *gin_graph)
+    o_o, o_agg = oracle.gin_forward(x, w, indptr, indices, 0.5)
+    assert_close(ref_agg.cpu().numpy(), o_agg, rtol=2e-5, what="reference GIN aggregate vs checker")
+    assert_close(ref_o.cpu().numpy(), o_o, rtol=3e-5, what="reference GIN output vs checker")
+    mine_o, mine_agg = K.forward_gin(dx, dw, *gin_graph)
+    assert_close(mine_agg.cpu().numpy(), ref_agg.cpu().numpy(), rtol=2e-5, what="GIN aggregate vs reference kernel")
+    ref_gi, ref_gw = ref_ccsrc.backward_gin(dg, ref_agg, dw, *gin_graph)
+    mine_gi, mine_gw = K.backward_gin(dg, ref_agg, dw, *gin_graph)
+    assert_close(mine_gi.cpu().numpy(), ref_gi.cpu().numpy(), rtol=3e-5, what="GIN d_input vs reference kernel")
+    assert_close(mine_gw.cpu().numpy(), ref_gw.cpu().numpy(), rtol=3e-5, what="GIN d_weight vs reference kernel")
