@@ -339,6 +339,69 @@ def cpu_baseline(sample, repeats=5):
 WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload}
 
 
+def run_reference_gpu_comparison(args):
+    """Times the reference's own CUDA kernels (compiled unmodified for sm_100a into oracle/_ref by
+    `make -C oracle ref_gpu ref_gpu_ccsrc`) beside this library on graphs inside the reference's limits:
+    fewer than 2^24 edges for the ccsrc neighbour-group table (float32 storage) and at most 65535 destination
+    rows per launch for the YiTu_H kernels.  Prints one JSON line; not the headline benchmark."""
+    import glob
+    import importlib
+    import torch
+    from yitu_b200 import YiTu_GNN_kernel as K, graph_ext, graphs
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not glob.glob(os.path.join(ref_dir, "graph_ext_ref*.so")) or not glob.glob(os.path.join(ref_dir, "yitu_gnn_kernel_ref*.so")):
+        print(json.dumps({"workload": "reference_gpu_comparison", "unavailable": "oracle/_ref builds are absent"}))
+        return
+    sys.path.insert(0, ref_dir)
+    ref_h = importlib.import_module("graph_ext_ref")
+    ref_c = importlib.import_module("yitu_gnn_kernel_ref")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    out = {"workload": "reference_gpu_comparison", "unit": "ms", "rows": []}
+    # ccsrc SAG (unweighted neighbour sum), R-MAT 2^18 nodes, 2^23 sampled edges, 64 and 256 features
+    n = 1 << 18
+    indptr, indices, _ = graphs.spmm_rmat(device=dev, n=n, e=1 << 23)
+    pp, p2n = K.build_part(32, indptr.cpu())
+    graph = (indptr, indices, torch.ones(n, device=dev), pp.int().to(dev), p2n.int().to(dev), 32, 32, 2)
+    for d in (64, 256):
+        x = graphs.randn_features(1, n, d, device=dev)
+        t_ref = timed(lambda: ref_c.SAG(x, *graph), 5)
+        t_new = timed(lambda: K.SAG(x, *graph), 20)
+        err = float((ref_c.SAG(x, *graph) - K.SAG(x, *graph)).abs().max())
+        out["rows"].append({"op": "YiTu_GNN_kernel.SAG", "n": n, "nnz": indices.numel(), "d": d, "reference_ms": t_ref,
+                            "this_ms": t_new, "speedup": t_ref / t_new, "max_abs_diff": err})
+    # graph_ext sddmm_forward + spmm_forward (GAT attention + aggregation), 65535 rows, 8 heads x 32
+    n = 65535
+    src, dst = graphs.uniform_edges(2, n, n, n * 32, device=dev)
+    indptr, indices = graphs.csr_by_destination(src, dst, n, n, self_loops=True)
+    H, F = 8, 32
+    xh = graphs.randn_features(3, n, H * F, device=dev).view(n, H, F)
+    q = graphs.uniform_values(4, (1, n, H), -1, 1, device=dev)
+    k = graphs.uniform_values(5, (n, H), -1, 1, device=dev)
+    t_ref = timed(lambda: ref_h.spmm_forward(ref_h.sddmm_forward(indptr, indices, q, k), indptr, indices, xh), 5)
+    t_two = timed(lambda: graph_ext.spmm_forward(graph_ext.sddmm_forward(indptr, indices, q, k), indptr, indices, xh), 20)
+    t_fused = timed(lambda: graph_ext.gat_forward(indptr, indices, q[0], k, xh), 20)
+    err = float((ref_h.spmm_forward(ref_h.sddmm_forward(indptr, indices, q, k), indptr, indices, xh) -
+                 graph_ext.gat_forward(indptr, indices, q[0], k, xh)[0]).abs().max())
+    out["rows"].append({"op": "graph_ext.sddmm_forward+spmm_forward", "n": n, "nnz": indices.numel(), "d": H * F,
+                        "reference_ms": t_ref, "this_ms_two_operators": t_two, "this_ms_fused": t_fused,
+                        "speedup": t_ref / t_fused, "max_abs_diff": err})
+    print(json.dumps(out))
+
+
 def run_single(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -426,7 +489,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned"])
+    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
@@ -441,6 +504,9 @@ def main():
         return
     if int(os.environ.get("RANK", "0")) != 0:
         return  # single-GPU workloads: extra ranks have nothing to do
+    if args.workload == "refgpu":
+        run_reference_gpu_comparison(args)
+        return
     run_single(args)
 
 
