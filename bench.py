@@ -372,8 +372,11 @@ def run_reference_gpu_comparison(args):
 
     out = {"workload": "reference_gpu_comparison", "unit": "ms", "rows": []}
     # ccsrc SAG (unweighted neighbour sum), R-MAT 2^18 nodes, 2^23 sampled edges, 64 and 256 features
+    # (self-loops keep the last node non-empty: with an empty last node the reference's group table ends in 0 and
+    # its kernel adds uninitialised shared memory to one output row)
     n = 1 << 18
-    indptr, indices, _ = graphs.spmm_rmat(device=dev, n=n, e=1 << 23)
+    src, dst = graphs.rmat_edges(1, n, n, 1 << 23, device=dev)
+    indptr, indices = graphs.csr_by_destination(src, dst, n, n, self_loops=True)
     pp, p2n = K.build_part(32, indptr.cpu())
     graph = (indptr, indices, torch.ones(n, device=dev), pp.int().to(dev), p2n.int().to(dev), 32, 32, 2)
     for d in (64, 256):
