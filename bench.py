@@ -104,7 +104,7 @@ class ClockSampler:
 class SpmmWorkload:
     """configs[1]: forward and transposed sum-aggregation SpMM."""
     name = "spmm_rmat_n2097152_e67108864_d256_fwd_bwd"
-    dominant_kernel = "spmm_kernel<32,2,4,false>"
+    dominant_kernel = "spmm_kernel<32,2,4,8,false,true>"
 
     def __init__(self, device, n=1 << 21, e=1 << 26, d=256):
         import torch
@@ -201,7 +201,7 @@ class GatWorkload:
         self.q = (self.x * a_dst).sum(-1).contiguous()
         self.grad = graphs.randn_features(2, n, H * F, device=device).view(n, H, F)
         self.units_per_step = 2 * self.nnz * self.d
-        self.launches_per_step = 1 + 3
+        self.launches_per_step = 1 + 5  # fused forward; backward = softmax, edge dot, softmax bwd, SpMM, gather sum
         self.kernel_launches_per_step = 1
         self.kernel_bytes = self.nnz * (4 + 4 * H + 4 * H * F) + n * (4 + 4 * H + 4 * H * F + 8 * H)
         self.traffic_key = "gat_fwd_h8_f32"
@@ -251,7 +251,7 @@ class GatWorkload:
 class RgcnWorkload:
     """configs[3]: hetero RGCN aggregation: per destination type one pass over the stitched relations."""
     name = "rgcn_4types_8rel_x4M_d64"
-    dominant_kernel = "spmm_kernel<16,1,4,false>"
+    dominant_kernel = "spmm_kernel<16,1,4,4,false,true>"
 
     def __init__(self, device, d=64):
         import torch
@@ -405,6 +405,33 @@ def run_reference_gpu_comparison(args):
     print(json.dumps(out))
 
 
+def partitioned_single_gpu_base(dev, steps=5):
+    """The N>1 workload (row-partitioned SpMM graph) on this one GPU, so that a scaling series that starts from the
+    default N=1 line has its like-for-like base: returns Gedge*feat/s and ms per step."""
+    import torch
+    from yitu_b200 import graphs
+    from yitu_b200.distributed import PartitionedSpmm, RowShard
+    n, e, d = 1 << 24, 1 << 29, 128
+    indptr, indices, values = graphs.spmm_partitioned(device=dev, n=n, e=e)
+    shard = RowShard(indptr, indices, values, [0, n], 0)
+    runner = PartitionedSpmm(shard, d, dev, mode="local")
+    runner.x_local.copy_(graphs.randn_features(1, n, d, device=dev))
+    for _ in range(3):
+        runner.step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        runner.step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    nnz = indices.numel()
+    runner.close()
+    return {"workload": "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d), "nnz": nnz, "ms_per_step": ms,
+            "value": nnz * d / (ms * 1e-3) / 1e9, "unit": UNIT}
+
+
 def run_single(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -481,8 +508,16 @@ def run_single(args):
                          "frac_of_nominal_8000": achieved / 8000.0, "algorithmic_bytes_per_launch": wl.kernel_bytes,
                          "avg_launch_ms": k_avg_ms, "traffic": load_traffic(wl.traffic_key)},
             "cpu_baseline": base,
+            "scaling_base_1gpu": None,
             "e2e": e2e,
             "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
+    if args.workload == "spmm" and not args.scale and not args.no_scaling_base:
+        del wl, kernel_events
+        torch.cuda.empty_cache()
+        try:
+            line["scaling_base_1gpu"] = partitioned_single_gpu_base(dev)
+        except Exception as exc:  # never lose the headline line to the extra measurement
+            line["scaling_base_1gpu"] = {"error": str(exc)[:200]}
     print(json.dumps(line))
 
 
@@ -496,6 +531,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--no-scaling-base", action="store_true",
+                    help="default workload: skip timing the N>1 workload on this one GPU")
     ap.add_argument("--no-single", action="store_true", help="partitioned: skip the 1-GPU comparison run on rank 0")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -186,8 +186,10 @@ int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indpt
 /* Fused GAT layer core: scores, LeakyReLU, edge softmax (online maximum/sum) and the weighted aggregation in
  * one pass over each row's edges — the composition sddmm_forward + spmm_forward of the reference
  * (xgnn_h/sparse.py:38-51,84-91; layer YiTu_GNN/YiTu_H/test/common/model.py:75-106) without the [nnz,H]
- * attention tensor.  Plain (unstitched) graphs, H <= 32, F a multiple of 4 with F/4 a power of two, H*F <= 512;
- * other shapes return YITU_ERR_UNSUPPORTED and the caller composes the unfused ops. */
+ * attention tensor.  Plain (unstitched) graphs, H <= 32, F a multiple of 4, H*F <= 512; other shapes return
+ * YITU_ERR_UNSUPPORTED and the caller composes the unfused ops.  The backward call recomputes the attention from
+ * query/key and chains the edge-softmax, edge-dot, transposed-SpMM and gather-sum kernels; edge_attn and edge_grad
+ * are its [nnz,H] scratch. */
 typedef struct yitu_gat_args_t {
     yitu_csr_t graph;
     int64_t n_heads, n_feats;

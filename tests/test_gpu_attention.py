@@ -81,7 +81,7 @@ def test_sddmm_large_scores_do_not_overflow(oracle):
     assert_close(attn.cpu().numpy(), oracle.sddmm_forward(indptr, indices, q, k), what="attn (large scores)")
 
 
-@pytest.mark.parametrize("H,F", [(8, 32), (1, 64), (4, 16), (2, 128), (16, 4), (3, 8), (32, 16), (1, 4)])
+@pytest.mark.parametrize("H,F", [(8, 32), (1, 64), (4, 16), (2, 128), (16, 4), (3, 8), (32, 16), (1, 4), (5, 12), (2, 200)])
 def test_fused_gat(oracle, H, F):
     from yitu_b200 import graph_ext
     rng = np.random.default_rng(H * 1000 + F)

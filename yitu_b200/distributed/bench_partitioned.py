@@ -76,6 +76,8 @@ def run(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     n, e, d = (1 << 24) >> args.scale, (1 << 29) >> args.scale, 128
+    if args.impl == "reference" and rank != 0:
+        return  # the CPU arm runs on rank 0 alone
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
 
@@ -125,7 +127,12 @@ def run(args):
 
     spmm_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "spmm"]
     fetch_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "fetch"]
-    launches_per_step = len([1 for tag, _, _ in events]) / args.steps
+    # this library's kernels per step on this rank: one gather per fetch, one SpMM (+ one hub reduction when the
+    # graph it ran on has split rows) per aggregation
+    n_fetch = len(fetch_ms) / args.steps
+    n_spmm = len(spmm_ms) / args.steps
+    has_hub = 1 if runner.graph.plan() is not None else 0
+    launches_per_step = n_fetch + n_spmm * (1 + has_hub)
     k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (one or two launches)
     k_bytes = shard.nnz * (4 * d + 8) + (shard.n_local + 1) * 8 + 4 * shard.n_local * d
     by_owner = [0.0] * world  # bytes this rank pulls from each owner per step
@@ -201,7 +208,7 @@ def run(args):
                 "cpu_baseline": None,
                 "e2e": {"value": nnz * d / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                         "h2d_bytes_per_step": int(bytes_io), "d2h_bytes_per_step": int(bytes_io)},
-                "gpu_launches": int(round(launches_per_step * 2)) * args.steps * world, "clocks": clocks}
+                "gpu_launches": int(round(launches_per_step)) * args.steps * world, "clocks": clocks}
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as O
             sh = RowShard(indptr, indices, values, partition_bounds(indptr, 16), 8)

@@ -125,8 +125,7 @@ def hfused_backward_all(spmm_values, spmm_indptr, spmm_indices, spmm_features, s
 
 # ------------------------------------------------------------------------------------------ fused GAT
 def gat_supported(indptr, indices, n_heads, n_feats):
-    return n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512 and \
-        (n_feats // 4) & (n_feats // 4 - 1) == 0 and n_feats // 4 <= 32
+    return n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
 def gat_forward(indptr, indices, query, key, features):

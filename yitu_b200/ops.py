@@ -221,11 +221,7 @@ def _gat_args(graph, query, key, x, out, row_max, row_sum, slope):
 
 
 def gat_fused_supported(graph, n_heads, n_feats, backward=True):
-    lph = n_feats // 4
-    ok = graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
-    if backward:
-        ok = ok and lph <= 32 and (lph & (lph - 1)) == 0
-    return ok
+    return graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
 def gat_fwd(graph, query, key, x, slope=0.2):
