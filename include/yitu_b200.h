@@ -89,6 +89,27 @@ int yitu_partition_rows(const yitu_csr_t *g, int32_t n_parts, int64_t *bounds, y
 int yitu_partition_rows_host(int64_t n_rows, const void *indptr_host, int32_t indptr_is64, int32_t n_parts,
                              int64_t *bounds_host);
 
+/* Edge list -> CSR by destination on the device: sorts (dst, src), drops duplicate pairs, optionally adds (i, i) for
+ * every node, columns ascending within a row.  Same structure as the scipy coo->csr the reference runs on the host
+ * (YiTu_GNN/data/dataset.py:117-129).  indices_out needs n_edges (+ n_dst with self-loops) entries; the number of stored
+ * edges comes back in *nnz_host (the call synchronises the stream). */
+int64_t yitu_coo_to_csr_workspace_bytes(int64_t n_edges, int64_t n_dst, int32_t add_self_loops);
+int yitu_coo_to_csr(int64_t n_src, int64_t n_dst, int64_t n_edges, const int32_t *src, const int32_t *dst,
+                    int32_t add_self_loops, void *indptr_out, int32_t indptr_is64, int32_t *indices_out, int64_t *nnz_host,
+                    void *workspace, int64_t workspace_bytes, yitu_stream_t stream);
+
+/* Per-node degree vector from the row pointers, d = max(in-degree, 1): mode 0 = sqrt(d), the `degrees` tensor the
+ * reference's dataset passes to its GCN kernel (YiTu_GNN/data/dataset.py:131-133); mode 1 = 1/sqrt(d) (symmetric
+ * normalisation); mode 2 = 1/d (right norm, xgnn_h/mp.py:165-167). */
+int yitu_degree_norm_f32(int64_t n_rows, const void *indptr, int32_t indptr_is64, int32_t mode, float *out,
+                         yitu_stream_t stream);
+
+/* stitch_csr on the device: block tables are DEVICE int32 arrays, the two pointer arrays and n_cols are HOST arrays.
+ * out_indices needs sum(nnz) entries; *overflow_flag (device int32) becomes 1 if a stitched column exceeds 2^24. */
+int yitu_stitch_csr(int32_t n_blocks, int64_t n_rows, const int32_t *const *indptrs_host,
+                    const int32_t *const *indices_host, const int64_t *n_cols_host, int32_t *out_indptr,
+                    int32_t *out_indices, int32_t *overflow_flag, yitu_stream_t stream);
+
 /* Neighbour-group table, on the host, bit-identical to build_part (ccsrc/kernel/YiTu_GNN.cpp:203-245):
  * float32 storage, and the terminal pointer is written only while the last node's groups are emitted. */
 int64_t yitu_build_part_count_host(int32_t part_size, const int32_t *indptr_host, int64_t n_nodes);

@@ -55,6 +55,11 @@ SYMBOLS = {
     "yitu_csr_transpose": (C.c_int, [C.POINTER(Csr), c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "yitu_partition_rows": (C.c_int, [C.POINTER(Csr), c_i32, c_vp, c_vp]),
     "yitu_partition_rows_host": (C.c_int, [c_i64, c_vp, c_i32, c_i32, c_vp]),
+    "yitu_coo_to_csr_workspace_bytes": (c_i64, [c_i64, c_i64, c_i32]),
+    "yitu_coo_to_csr": (C.c_int, [c_i64, c_i64, c_i64, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp, C.POINTER(c_i64), c_vp, c_i64,
+                                  c_vp]),
+    "yitu_degree_norm_f32": (C.c_int, [c_i64, c_vp, c_i32, c_i32, c_vp, c_vp]),
+    "yitu_stitch_csr": (C.c_int, [c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "yitu_build_part_count_host": (c_i64, [c_i32, c_vp, c_i64]),
     "yitu_build_part_host": (C.c_int, [c_i32, c_vp, c_i64, c_vp, c_vp]),
     "yitu_stitch_csr_host": (C.c_int, [c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),

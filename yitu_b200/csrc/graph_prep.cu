@@ -3,6 +3,7 @@
 // expect (build_part, stitch_csr).  Integer work only; scans and sorts use CUB from the CUDA toolkit.
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
+#include <cub/device/device_select.cuh>
 
 #include <cstdarg>
 #include <cstring>
@@ -150,6 +151,74 @@ __global__ void segment_mean_kernel(int64_t n_rows, const void *indptr, int is64
             for (int64_t i = b + lane; i < e; i += 32)
                 if ((static_cast<unsigned>(indices[i]) >> 24) == s) values[i] = w;
         }
+    }
+}
+
+
+// ------------------------------------------------------------------------------------------- COO -> CSR
+__global__ void pack_edges_kernel(int64_t n_edges, const int *src, const int *dst, int64_t n_loops, uint64_t *keys) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n_edges) {
+        keys[i] = (static_cast<uint64_t>(static_cast<uint32_t>(dst[i])) << 32) | static_cast<uint32_t>(src[i]);
+    } else if (i < n_edges + n_loops) {
+        const uint64_t v = static_cast<uint64_t>(i - n_edges);
+        keys[i] = (v << 32) | v;
+    }
+}
+
+template <typename P>
+__global__ void csr_from_keys_kernel(int64_t n_dst, const int64_t *nnz_dev, const uint64_t *keys, P *indptr, int *indices) {
+    const int64_t nnz = *nnz_dev;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < nnz) indices[i] = static_cast<int>(keys[i] & 0xffffffffu);
+    if (i <= n_dst) {  // first position whose destination >= i
+        int64_t lo = 0, hi = nnz;
+        while (lo < hi) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (static_cast<int64_t>(keys[mid] >> 32) >= i) hi = mid; else lo = mid + 1;
+        }
+        indptr[i] = static_cast<P>(lo);
+    }
+}
+
+__global__ void degree_norm_kernel(int64_t n, const void *indptr, int is64, int mode, float *out) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    const float d = fmaxf(static_cast<float>(load_ptr(indptr, is64, r + 1) - load_ptr(indptr, is64, r)), 1.0f);
+    out[r] = mode == 0 ? sqrtf(d) : (mode == 1 ? 1.0f / sqrtf(d) : 1.0f / d);
+}
+
+// ------------------------------------------------------------------------------------------- stitch (device)
+struct StitchParams {
+    const int *indptr[16];
+    const int *indices[16];
+    int shift[16];
+    int n_blocks;
+    int64_t n_rows;
+};
+
+__global__ void stitch_ptr_kernel(const __grid_constant__ StitchParams p, int *out_indptr) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r > p.n_rows) return;
+    int total = 0;
+    for (int b = 0; b < p.n_blocks; ++b) total += p.indptr[b][r];
+    out_indptr[r] = total;
+}
+
+__global__ void stitch_fill_kernel(const __grid_constant__ StitchParams p, const int *out_indptr, int *out_indices,
+                                   int *overflow) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= p.n_rows) return;
+    int w = out_indptr[row];
+    for (int b = 0; b < p.n_blocks; ++b) {
+        const int beg = p.indptr[b][row], end = p.indptr[b][row + 1];
+        for (int i = beg + lane; i < end; i += 32) {
+            const int col = p.shift[b] + p.indices[b][i];
+            if (col > (1 << 24)) *overflow = 1;
+            out_indices[w + (i - beg)] = (b << 24) + col;
+        }
+        w += end - beg;
     }
 }
 
@@ -303,6 +372,110 @@ extern "C" int yitu_segment_mean_weights_f32(const yitu_csr_t *g, float *values,
                           reinterpret_cast<cudaStream_t>(stream)>>>(g->n_rows, g->indptr, g->indptr_is64, g->indices,
                                                                     g->index_mask, values);
     YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------- COO -> CSR (device)
+static int coo_key_bits(int64_t n_dst) { return 32 + key_bits(n_dst); }
+
+static size_t coo_temp_bytes(int64_t m, int bits) {
+    size_t a = 0, b = 0;
+    cub::DeviceRadixSort::SortKeys(nullptr, a, static_cast<const uint64_t *>(nullptr), static_cast<uint64_t *>(nullptr), m, 0,
+                                   bits);
+    cub::DeviceSelect::Unique(nullptr, b, static_cast<const uint64_t *>(nullptr), static_cast<uint64_t *>(nullptr),
+                              static_cast<int64_t *>(nullptr), m);
+    return a > b ? a : b;
+}
+
+extern "C" int64_t yitu_coo_to_csr_workspace_bytes(int64_t n_edges, int64_t n_dst, int32_t add_self_loops) {
+    const int64_t m = n_edges + (add_self_loops ? n_dst : 0);
+    return 2 * align_up(m * 8 + 8, 256) + 256 + align_up(static_cast<int64_t>(coo_temp_bytes(m, coo_key_bits(n_dst))), 256);
+}
+
+extern "C" int yitu_coo_to_csr(int64_t n_src, int64_t n_dst, int64_t n_edges, const int32_t *src, const int32_t *dst,
+                               int32_t add_self_loops, void *indptr_out, int32_t indptr_is64, int32_t *indices_out,
+                               int64_t *nnz_host, void *workspace, int64_t workspace_bytes, yitu_stream_t stream) {
+    YITU_REQUIRE(n_src >= 0 && n_dst >= 0 && n_edges >= 0 && n_src < (1ll << 31) && n_dst < (1ll << 31),
+                 YITU_ERR_INVALID_ARG, "bad sizes");
+    YITU_REQUIRE(!add_self_loops || n_src == n_dst, YITU_ERR_INVALID_ARG, "self-loops need a square graph");
+    YITU_REQUIRE(indptr_out && nnz_host, YITU_ERR_INVALID_ARG, "NULL output");
+    const int64_t m = n_edges + (add_self_loops ? n_dst : 0);
+    YITU_REQUIRE(indptr_is64 || m < (1ll << 31), YITU_ERR_LIMIT, "%lld edges need int64 row pointers", (long long)m);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (m == 0) {
+        YITU_CUDA(cudaMemsetAsync(indptr_out, 0, (n_dst + 1) * (indptr_is64 ? 8 : 4), st));
+        *nnz_host = 0;
+        return YITU_OK;
+    }
+    YITU_REQUIRE((n_edges == 0 || (src && dst)) && indices_out, YITU_ERR_INVALID_ARG, "NULL edge list or indices_out");
+    YITU_REQUIRE(workspace && workspace_bytes >= yitu_coo_to_csr_workspace_bytes(n_edges, n_dst, add_self_loops),
+                 YITU_ERR_WORKSPACE, "coo_to_csr workspace needs %lld bytes",
+                 (long long)yitu_coo_to_csr_workspace_bytes(n_edges, n_dst, add_self_loops));
+    const int64_t arr = align_up(m * 8 + 8, 256);
+    char *ws = static_cast<char *>(workspace);
+    uint64_t *keys_a = reinterpret_cast<uint64_t *>(ws);
+    uint64_t *keys_b = reinterpret_cast<uint64_t *>(ws + arr);
+    int64_t *nnz_dev = reinterpret_cast<int64_t *>(ws + 2 * arr);
+    void *temp = ws + 2 * arr + 256;
+    const int bits = coo_key_bits(n_dst);
+    size_t temp_bytes = coo_temp_bytes(m, bits);
+    pack_edges_kernel<<<static_cast<unsigned>((m + 255) / 256), 256, 0, st>>>(n_edges, src, dst,
+                                                                             add_self_loops ? n_dst : 0, keys_a);
+    YITU_LAUNCH_CHECK();
+    YITU_CUDA(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, keys_a, keys_b, m, 0, bits, st));
+    YITU_CUDA(cub::DeviceSelect::Unique(temp, temp_bytes, keys_b, keys_a, nnz_dev, m, st));
+    const int64_t work = (m > n_dst + 1 ? m : n_dst + 1);
+    const unsigned blocks = static_cast<unsigned>((work + 255) / 256);
+    if (indptr_is64)
+        csr_from_keys_kernel<int64_t><<<blocks, 256, 0, st>>>(n_dst, nnz_dev, keys_a, static_cast<int64_t *>(indptr_out),
+                                                              indices_out);
+    else
+        csr_from_keys_kernel<int><<<blocks, 256, 0, st>>>(n_dst, nnz_dev, keys_a, static_cast<int *>(indptr_out),
+                                                          indices_out);
+    YITU_LAUNCH_CHECK();
+    YITU_CUDA(cudaMemcpyAsync(nnz_host, nnz_dev, 8, cudaMemcpyDeviceToHost, st));
+    YITU_CUDA(cudaStreamSynchronize(st));
+    return YITU_OK;
+}
+
+extern "C" int yitu_degree_norm_f32(int64_t n_rows, const void *indptr, int32_t indptr_is64, int32_t mode, float *out,
+                                    yitu_stream_t stream) {
+    YITU_REQUIRE(n_rows >= 0 && indptr && mode >= 0 && mode <= 2, YITU_ERR_INVALID_ARG, "bad argument");
+    if (n_rows == 0) return YITU_OK;
+    YITU_REQUIRE(out, YITU_ERR_INVALID_ARG, "out is NULL");
+    degree_norm_kernel<<<static_cast<unsigned>((n_rows + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        n_rows, indptr, indptr_is64, mode, out);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_stitch_csr(int32_t n_blocks, int64_t n_rows, const int32_t *const *indptrs_host,
+                               const int32_t *const *indices_host, const int64_t *n_cols_host, int32_t *out_indptr,
+                               int32_t *out_indices, int32_t *overflow_flag, yitu_stream_t stream) {
+    YITU_REQUIRE(n_blocks >= 0 && n_blocks <= 16, YITU_ERR_LIMIT, "stitch_csr takes at most 16 blocks, got %d", n_blocks);
+    YITU_REQUIRE(out_indptr && overflow_flag && n_rows >= 0, YITU_ERR_INVALID_ARG, "bad argument");
+    StitchParams p{};
+    p.n_blocks = n_blocks;
+    p.n_rows = n_rows;
+    int64_t shift = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+        YITU_REQUIRE(indptrs_host[b] != nullptr, YITU_ERR_INVALID_ARG, "block %d has no row pointers", b);
+        p.indptr[b] = indptrs_host[b];
+        p.indices[b] = indices_host[b];
+        YITU_REQUIRE(shift <= (1 << 24), YITU_ERR_LIMIT, "stitched column offset %lld exceeds 2^24", (long long)shift);
+        p.shift[b] = static_cast<int>(shift);
+        shift += n_cols_host[b];
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    YITU_CUDA(cudaMemsetAsync(overflow_flag, 0, 4, st));
+    stitch_ptr_kernel<<<static_cast<unsigned>((n_rows + 1 + 255) / 256), 256, 0, st>>>(p, out_indptr);
+    YITU_LAUNCH_CHECK();
+    if (n_rows > 0 && out_indices) {
+        stitch_fill_kernel<<<static_cast<unsigned>((n_rows * 32 + 255) / 256), 256, 0, st>>>(p, out_indptr, out_indices,
+                                                                                           overflow_flag);
+        YITU_LAUNCH_CHECK();
+    }
     return YITU_OK;
 }
 

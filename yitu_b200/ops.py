@@ -271,3 +271,61 @@ def partition_rows_host(indptr, n_parts):
     check(lib().yitu_partition_rows_host(indptr.numel() - 1, _ptr(indptr), int(indptr.dtype == torch.int64), n_parts,
                                          _ptr(bounds)))
     return bounds
+
+
+def coo_to_csr(src, dst, n_src, n_dst, self_loops=False, ptr_dtype=torch.int32):
+    """Edge list (int32 CUDA tensors) -> (indptr, indices) by destination on the device: duplicates dropped,
+    optional self-loops, ascending columns — what the reference builds with scipy on the host
+    (YiTu_GNN/data/dataset.py:117-129)."""
+    require_cuda(src, "src", torch.int32)
+    require_cuda(dst, "dst", torch.int32)
+    if src.numel() != dst.numel():
+        raise RuntimeError("src and dst differ in length")
+    dev = src.device
+    n_edges = src.numel()
+    L = lib()
+    cap = n_edges + (n_dst if self_loops else 0)
+    indptr = torch.empty(n_dst + 1, dtype=ptr_dtype, device=dev)
+    indices = torch.empty(max(cap, 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        ws_bytes = L.yitu_coo_to_csr_workspace_bytes(n_edges, n_dst, int(self_loops))
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        nnz = C.c_int64(0)
+        check(L.yitu_coo_to_csr(n_src, n_dst, n_edges, _ptr(src), _ptr(dst), int(self_loops), _ptr(indptr),
+                                int(ptr_dtype == torch.int64), _ptr(indices), C.byref(nnz), _ptr(ws), ws_bytes,
+                                _stream(dev)))
+    return indptr, indices[:nnz.value].clone()
+
+
+DEG_SQRT, DEG_RSQRT, DEG_INV = 0, 1, 2
+
+
+def degree_norm(indptr, mode=DEG_SQRT):
+    """float32 [n_rows] from d = max(in-degree, 1): sqrt(d) (the reference's `degrees`,
+    YiTu_GNN/data/dataset.py:131-133), 1/sqrt(d), or 1/d."""
+    n = indptr.numel() - 1
+    out = torch.empty(n, dtype=torch.float32, device=indptr.device)
+    with torch.cuda.device(indptr.device):
+        check(lib().yitu_degree_norm_f32(n, _ptr(indptr), int(indptr.dtype == torch.int64), mode, _ptr(out),
+                                         _stream(indptr.device)))
+    return out
+
+
+def stitch_csr_device(indptrs, indices, n_cols):
+    """Device stitch_csr over CUDA int32 block tables: (indptr, indices) of the segmented CSR, on the device."""
+    n_blocks = len(indptrs)
+    n_rows = indptrs[0].numel() - 1 if n_blocks else 0
+    dev = indptrs[0].device
+    total = sum(int(i.numel()) for i in indices)
+    out_ip = torch.empty(n_rows + 1, dtype=torch.int32, device=dev)
+    out_id = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    PP = C.c_void_p * max(n_blocks, 1)
+    ncols = (C.c_int64 * max(n_blocks, 1))(*[int(c) for c in n_cols])
+    with torch.cuda.device(dev):
+        check(lib().yitu_stitch_csr(n_blocks, n_rows, PP(*[t.data_ptr() for t in indptrs]),
+                                    PP(*[t.data_ptr() for t in indices]), ncols, _ptr(out_ip), _ptr(out_id), _ptr(flag),
+                                    _stream(dev)))
+    if int(flag) != 0:
+        raise AssertionError("stitched column exceeds 2**24")
+    return out_ip, out_id[:total]

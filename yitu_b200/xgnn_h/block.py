@@ -37,11 +37,19 @@ class Block:
 def stitch_csr(block_list: List[Block]):
     """Pack up to 16 blocks with equal row counts into one segmented CSR: row r = row r of every block in
     turn, index = (block id << 24) + column + columns of the blocks before.  Same result as the reference's
-    per-edge Python loop, computed by the library's host routine; the result lives on the CPU like there."""
+    per-edge Python loop, computed by the library's host routine (result on the CPU, like there) or, when the block tables are CUDA
+    tensors, by its device kernels (result on that GPU)."""
     rows = [blk.size[0] for blk in block_list]
     assert len(rows) <= 16
     assert min(rows) == max(rows)
     n_rows = rows[0]
+    if all(blk.adj_sparse[0].is_cuda and blk.adj_sparse[1].is_cuda for blk in block_list):
+        # tables already on a GPU: stitch there (the result stays on that device)
+        from .. import ops
+        ip, ix = ops.stitch_csr_device([blk.adj_sparse[0].to(torch.int32).contiguous() for blk in block_list],
+                                       [blk.adj_sparse[1].to(torch.int32).contiguous() for blk in block_list],
+                                       [blk.size[1] for blk in block_list])
+        return Block(size=[n_rows, sum(blk.size[1] for blk in block_list)], adj=[ip, ix])
     ips = [blk.adj_sparse[0].to("cpu", torch.int32).contiguous() for blk in block_list]
     ids = [blk.adj_sparse[1].to("cpu", torch.int32).contiguous() for blk in block_list]
     n_cols = torch.tensor([blk.size[1] for blk in block_list], dtype=torch.int64)
