@@ -1,4 +1,4 @@
-"""bench.py leg for the row-partitioned SpMM (R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, fp32
+"""bench.py's leg for the row-partitioned SpMM (R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, fp32
 weights 1/in-degree, 128 features), one process per GPU.  Strong scaling: the graph is fixed, each rank
 aggregates its edge-balanced row range.  Every rank builds the same graph from the same seed on its own GPU
 (integer generator, bit-identical everywhere) and keeps its shard."""
@@ -18,14 +18,14 @@ def _reference_leg(args, device, n, e, d):
     """CPU restatement on all host cores, on the rows of partition 0 of 16 (bounded sample)."""
     from oracle import oracle as O
     from yitu_b200 import graphs
-    from .partition import RowShard, partition_bounds
+    from yitu_b200.distributed.partition import RowShard, partition_bounds
     indptr, indices, values = graphs.spmm_partitioned(device=device, n=n, e=e)
     bounds = partition_bounds(indptr, 16)
     sh = RowShard(indptr, indices, values, bounds, 8)
     x = graphs.randn_features(1, n, d, device=device).cpu().numpy()
     ip, ix, vals = sh.indptr.cpu().numpy(), sh.indices.cpu().numpy(), sh.values.cpu().numpy()
-    cores = len(os.sched_getaffinity(0))
     O.build()
+    cores = O.set_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
     best = None
     for _ in range(max(1, args.steps + args.warmup)):
         t0 = time.perf_counter()
@@ -69,8 +69,8 @@ def _time_steps(runner, steps, world, events=None):
 def run(args):
     import bench  # the repo-root script: clock sampler and peak numbers
     from yitu_b200 import graphs, ops
-    from .partition import RowShard, partition_bounds
-    from .runtime import PartitionedSpmm
+    from yitu_b200.distributed.partition import RowShard, partition_bounds
+    from yitu_b200.distributed.runtime import PartitionedSpmm
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -215,6 +215,7 @@ def run(args):
             xs = graphs.randn_features(1, n, d, device=dev).cpu().numpy()
             ip, ix, vals = sh.indptr.cpu().numpy(), sh.indices.cpu().numpy(), sh.values.cpu().numpy()
             O.build()
+            O.set_threads(len(os.sched_getaffinity(0)))
             t_best = None
             for _ in range(5):
                 t0 = time.perf_counter()

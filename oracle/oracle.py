@@ -40,6 +40,12 @@ def lib():
     return _lib
 
 
+def set_threads(n):
+    """Use n OpenMP threads from now on, whatever OMP_NUM_THREADS said when the process started."""
+    lib().yo_set_threads(C.c_int(int(n)))
+    return lib().yo_max_threads()
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
