@@ -1,0 +1,140 @@
+"""Layer-level parity on the GPU: GCNConv/GINConv (YiTu_GNN/nn) and the YiTu_H layers (GCNLayer, GATLayer,
+HeteroGraphConv, and its stitched one-pass form) against dense float64 torch algebra, outputs and gradients."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from conftest import random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def _dense(indptr, indices, n_src):
+    n_dst = len(indptr) - 1
+    a = torch.zeros(n_dst, n_src, dtype=torch.float64)
+    a[np.repeat(np.arange(n_dst), np.diff(indptr)), indices] = 1.0
+    return a.cuda()
+
+
+def _block(indptr, indices, n_src):
+    from yitu_b200.xgnn_h import Block
+    return Block([len(indptr) - 1, n_src], [torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda()])
+
+
+def _close(a, b, tol=2e-5):
+    a, b = a.detach().double(), b.detach().double()
+    return float((a - b).abs().max()) <= tol * (float(b.abs().max()) + 1e-30)
+
+
+class _Info:
+    pass
+
+
+def test_gcnconv_and_ginconv_autograd():
+    from yitu_b200 import YiTu_GNN_kernel as K
+    from yitu_b200.nn import GCNConv, GINConv
+    rng = np.random.default_rng(0)
+    n = 400
+    dense = rng.random((n, n)) < 0.03
+    dense = dense | dense.T
+    np.fill_diagonal(dense, True)
+    indptr = np.concatenate([[0], np.cumsum(dense.sum(1))]).astype(np.int32)
+    indices = np.nonzero(dense)[1].astype(np.int32)
+    info = _Info()
+    info.row_pointers, info.column_index = torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda()
+    deg = torch.from_numpy(np.diff(indptr).astype(np.float32))
+    info.degrees = (1.0 / torch.sqrt(deg)).cuda()
+    pp, p2n = K.build_part(32, torch.from_numpy(indptr))
+    info.partPtr, info.part2Node = pp.int().cuda(), p2n.int().cuda()
+    info.partSize, info.dimWorker, info.warpPerBlock = 32, 32, 2
+    a = torch.from_numpy(dense.astype(np.float64)).cuda()
+    nd = info.degrees.double()
+    a_hat = nd[:, None] * a * nd[None, :]
+    x = torch.randn(n, 24, device="cuda", requires_grad=True)
+    w_out = torch.randn(n, 10, device="cuda")
+    for layer, ref in ((GCNConv(24, 10).cuda(), lambda xx, ww: a_hat @ (xx @ ww)),
+                       (GINConv(24, 10).cuda(), lambda xx, ww: (0.5 * (a @ xx)) @ ww)):
+        y = layer(x, info)
+        (y * w_out).sum().backward()
+        gx, gw = x.grad.clone(), layer.weights.grad.clone()
+        x.grad = None
+        xd = x.detach().double().requires_grad_()
+        wd = layer.weights.detach().double().requires_grad_()
+        yd = ref(xd, wd)
+        (yd * w_out.double()).sum().backward()
+        assert _close(y, yd) and _close(gx, xd.grad) and _close(gw, wd.grad, 5e-5)
+
+
+def test_gat_layer_matches_dense():
+    from yitu_b200.nn import GATLayer
+    rng = np.random.default_rng(1)
+    n, H, F = 300, 4, 16
+    indptr, indices = random_csr(rng, n, n, density=0.05, empty_rows=False)
+    blk = _block(indptr, indices, n)
+    layer = GATLayer(20, F, H).cuda()
+    x = torch.randn(n, 20, device="cuda", requires_grad=True)
+    y = layer(blk, x)
+    y.sum().backward()
+    gx = x.grad.clone()
+    grads = {k: p.grad.clone() for k, p in layer.named_parameters()}
+    # dense float64 restatement of model.py:75-106
+    ld = GATLayer(20, F, H).cuda().double()
+    ld.load_state_dict({k: v.double() for k, v in layer.state_dict().items()})
+    xd = x.detach().double().requires_grad_()
+    h = ld.linear_v(xd)
+    q, k = ld.linear_q(h), ld.linear_k(h)
+    a = _dense(indptr, indices, n)
+    e = nn.functional.leaky_relu(q.unsqueeze(1) + k.unsqueeze(0), 0.2)
+    e = torch.where(a.unsqueeze(-1) > 0, e, torch.full_like(e, -1e300)).permute(2, 0, 1)
+    attn = torch.softmax(e, dim=-1) * a.unsqueeze(0)
+    yd = torch.bmm(attn, h.view(n, H, F).transpose(0, 1)).transpose(0, 1).mean(dim=1)
+    yd.sum().backward()
+    assert _close(y, yd, 5e-5) and _close(gx, xd.grad, 1e-4)
+    for kname, p in ld.named_parameters():
+        assert _close(grads[kname], p.grad, 2e-4), kname
+
+
+def test_hetero_conv_and_stitched_form_agree():
+    from yitu_b200.nn import GCNLayer, HeteroGraphConv, StitchedRGCNConv
+    rng = np.random.default_rng(2)
+    n_dst, d_in, d_out = 250, 12, 64
+    sizes = {"a": 90, "b": 140, "c": 60}
+    hgraph, norms, xs, dense = {}, {}, {}, {}
+    for name, n_src in sizes.items():
+        indptr, indices = random_csr(rng, n_dst, n_src, density=0.08)
+        hgraph[(name, "rel_" + name, "dst")] = _block(indptr, indices, n_src)
+        deg = np.maximum(np.diff(indptr), 1).astype(np.float32)  # 1/in_degree; empty rows contribute 0 anyway
+        norms[str((name, "rel_" + name, "dst"))] = torch.from_numpy(1.0 / deg).cuda().unsqueeze(-1)
+        xs[name] = torch.randn(n_src, d_in, device="cuda", requires_grad=True)
+        dense[name] = _dense(indptr, indices, n_src)
+    xs["dst"] = torch.zeros(n_dst, d_in, device="cuda")
+    conv = HeteroGraphConv({"rel_" + n: GCNLayer(d_in, d_out) for n in sizes}).cuda()
+    y = conv(hgraph, xs, norms)["dst"]
+    w_out = torch.randn(n_dst, d_out, device="cuda")
+    (y * w_out).sum().backward()
+    g1 = {n: xs[n].grad.clone() for n in sizes}
+    gw1 = {n: conv.convs["rel_" + n].fc.weight.grad.clone() for n in sizes}
+
+    stitched = StitchedRGCNConv([("rel_" + n, hgraph[(n, "rel_" + n, "dst")]) for n in sizes], d_in, d_out).cuda()
+    for n in sizes:
+        stitched.fcs["rel_" + n].load_state_dict(conv.convs["rel_" + n].fc.state_dict())
+        xs[n].grad = None
+    y2 = stitched({"rel_" + n: xs[n] for n in sizes})
+    (y2 * w_out).sum().backward()
+    assert _close(y2, y, 3e-5)
+    for n in sizes:
+        assert _close(xs[n].grad, g1[n], 5e-5)
+        assert _close(stitched.fcs["rel_" + n].weight.grad, gw1[n], 1e-4)
+
+    # dense float64: mean over relations of (1/in_degree) * A_r (x_r W_r^T + b_r)
+    ref = 0
+    for n in sizes:
+        fc = conv.convs["rel_" + n].fc
+        h = xs[n].detach().double() @ fc.weight.detach().double().T + fc.bias.detach().double()
+        ref = ref + norms[str((n, "rel_" + n, "dst"))].double() * (dense[n] @ h)
+    assert _close(y, ref / 3, 3e-5)
+    summed = StitchedRGCNConv([("rel_" + n, hgraph[(n, "rel_" + n, "dst")]) for n in sizes], d_in, d_out,
+                              reduce="sum").cuda()
+    summed.load_state_dict(stitched.state_dict())
+    assert _close(summed({"rel_" + n: xs[n] for n in sizes}), ref, 3e-5)
