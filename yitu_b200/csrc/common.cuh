@@ -47,16 +47,21 @@ __device__ __forceinline__ float leaky_relu(float v, float slope) {
     return fmaxf(0.0f, v) + slope * fminf(0.0f, v);
 }
 
-// Read-only 128-bit / 32-bit loads of data that is streamed once (indices, edge values):
-// keep them out of L1 so the gathered feature rows own it.
+// Loads of data that is streamed once (indices, edge values): kept out of L1, and marked evict-first in L2 through
+// a cache-hint policy, so that they do not push the gathered feature rows out of the 126 MB L2.
+__device__ __forceinline__ uint64_t stream_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ int ld_stream(const int *p) {
     int v;
-    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(v) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(stream_policy()));
     return v;
 }
 __device__ __forceinline__ float ld_stream(const float *p) {
     float v;
-    asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(stream_policy()));
     return v;
 }
 

@@ -56,10 +56,11 @@ __device__ __forceinline__ void load_vec(float (&r)[VEC], const float *p) {
 
 template <int VEC>
 __device__ __forceinline__ void store_vec(float *p, const float (&r)[VEC]) {
+    // output rows are written once and not read again by this kernel: streaming stores (evict-first)
     if constexpr (VEC == 4) {
-        *reinterpret_cast<float4 *>(p) = make_float4(r[0], r[1], r[2], r[3]);
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(r[0], r[1], r[2], r[3]));
     } else {
-        *p = r[0];
+        __stcs(p, r[0]);
     }
 }
 
