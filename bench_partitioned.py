@@ -98,12 +98,12 @@ def run(args):
     torch.cuda.empty_cache()
     x_shard = graphs.randn_features(1, shard.n_local, d, device=dev, row_begin=shard.row_begin)
 
-    candidates = [("local", False)] if world == 1 else [("peer", True), ("peer", False), ("allgather", False)]
+    candidates = [("local", False, 1)] if world == 1 else [("peer", False, 1), ("peer", True, 1), ("allgather", False, 1)]
     runners, trial = {}, {}
-    for mode, overlap in candidates:
-        r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap)
+    for mode, overlap, blocks in candidates:
+        r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap, row_blocks=blocks)
         r.x_local.copy_(x_shard)
-        key = mode + ("+overlap" if overlap else "")
+        key = mode + ("+overlap" if overlap else "") + ("+rowblocks%d" % blocks if blocks > 1 else "")
         runners[key] = r
         for _ in range(3):
             r.step()
@@ -131,7 +131,7 @@ def run(args):
     # graph it ran on has split rows) per aggregation
     n_fetch = len(fetch_ms) / args.steps
     n_spmm = len(spmm_ms) / args.steps
-    has_hub = 1 if runner.graph.plan() is not None else 0
+    has_hub = 1 if runner.graph.plan() is not None else 0  # (row-block runs: counted from the whole-shard graph)
     launches_per_step = n_fetch + n_spmm * (1 + has_hub)
     k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (one or two launches)
     k_bytes = shard.nnz * (4 * d + 8) + (shard.n_local + 1) * 8 + 4 * shard.n_local * d

@@ -84,6 +84,24 @@ def _worker(rank, world, port, errors):
         got = O.spmm(shard.indptr.numpy(), li, xbuf, wmode=O.W_EDGE, values=shard.values.numpy())
         assert np.array_equal(got, ref), "partitioned aggregation must equal the single-graph rows"
 
+        # halo list ordered by the first row block that needs a row
+        rb = [0, shard.n_local // 3, (2 * shard.n_local) // 3, shard.n_local]
+        plan_b = HaloPlan(shard, rb)
+        assert sorted(plan_b.halo_ids.tolist()) == halo.tolist() and plan_b.chunk_offsets[-1] == plan_b.n_halo
+        lib_ = plan_b.local_indices.numpy()
+        hb = plan_b.halo_ids.numpy()
+        assert np.array_equal(np.where(lib_ < shard.n_local, lib_ + lo, hb[np.maximum(lib_ - shard.n_local, 0)]), cols)
+        ipn = shard.indptr.numpy()
+        for b in range(3):
+            used = lib_[ipn[rb[b]]:ipn[rb[b + 1]]]
+            used = used[used >= shard.n_local] - shard.n_local
+            assert used.size == 0 or used.max() < plan_b.chunk_offsets[b + 1], "block b may only use chunks 0..b"
+            seg = hb[plan_b.chunk_offsets[b]:plan_b.chunk_offsets[b + 1]]
+            assert np.all(np.diff(seg) > 0), "ascending ids inside a chunk"
+        xbuf_b = torch.cat([x[lo:hi], x[torch.from_numpy(hb).long()]]).numpy()
+        got_b = O.spmm(shard.indptr.numpy(), lib_, xbuf_b, wmode=O.W_EDGE, values=shard.values.numpy())
+        assert np.array_equal(got_b, ref)
+
         (ipo, ixo, vo), (iph, ixh, vh) = split_local_halo(shard, plan)
         assert int(ipo[-1]) + int(iph[-1]) == shard.nnz
         assert ixo.numel() == 0 or int(ixo.max()) < shard.n_local

@@ -41,14 +41,14 @@ def _worker(rank, world, port, errors):
         bounds = partition_bounds(indptr, world)
         shard = RowShard(indptr, indices, values, bounds, rank)
         lo, hi = shard.row_begin, shard.row_end
-        for mode, overlap in (("peer", False), ("peer", True), ("allgather", False)):
-            r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap)
+        for mode, overlap, blocks in (("peer", False, 1), ("peer", True, 1), ("peer", False, 4), ("allgather", False, 1)):
+            r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap, row_blocks=blocks)
             r.x_local.copy_(x[lo:hi])
             for _ in range(2):
                 out = r.step()
             torch.cuda.synchronize(dev)
             err = float((out - ref[lo:hi]).abs().max())
-            assert err <= 1e-5 * float(ref.abs().max()), "%s overlap=%s: max err %g" % (mode, overlap, err)
+            assert err <= 1e-5 * float(ref.abs().max()), "%s overlap=%s blocks=%d: max err %g" % (mode, overlap, blocks, err)
             if mode == "peer":
                 assert r.plan.n_halo > 0
                 assert torch.equal(r.x_halo, x[r.plan.halo_ids.long()]), "halo rows must be the owners' rows"

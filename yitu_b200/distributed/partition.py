@@ -34,20 +34,45 @@ class RowShard:
 
 class HaloPlan:
     """Which remote source rows a shard needs, and its column ids renumbered for the buffer
-    [own rows | halo rows]: own source id s -> s - row_begin, remote id -> n_local + position in halo_ids."""
+    [own rows | halo rows]: own source id s -> s - row_begin, remote id -> n_local + position in halo_ids.
 
-    def __init__(self, shard):
+    With row_bounds (K+1 row offsets inside the shard) the halo list is ordered by the first row block that uses a
+    row, ascending ids within a block: halo_ids[chunk_offsets[b]:chunk_offsets[b+1]] are the rows block b needs in
+    addition to those of the blocks before it, so block b can be aggregated as soon as chunks 0..b have arrived."""
+
+    def __init__(self, shard, row_bounds=None):
         lo, hi = shard.row_begin, shard.row_end
         cols = shard.indices
         own = (cols >= lo) & (cols < hi)
-        self.halo_ids = torch.unique(cols[~own])  # sorted ascending, int32
-        self.n_halo = self.halo_ids.numel()
-        pos = torch.searchsorted(self.halo_ids, cols)
+        halo_sorted = torch.unique(cols[~own])  # sorted ascending, int32
+        self.n_halo = halo_sorted.numel()
+        pos = torch.searchsorted(halo_sorted, cols)
+        bounds_t = torch.tensor(shard.bounds, dtype=halo_sorted.dtype, device=cols.device)
+        # halo rows [owner_offsets[p], owner_offsets[p+1]) of the id-sorted list live on rank p
+        self.owner_offsets = torch.searchsorted(halo_sorted, bounds_t).tolist()
+        self.chunk_offsets = [0, self.n_halo]
+        self.row_bounds = None
+        if row_bounds is not None and len(row_bounds) > 2 and self.n_halo > 0:
+            k = len(row_bounds) - 1
+            edge_bounds = shard.indptr.long()[torch.tensor(row_bounds, device=cols.device)]
+            edge_ids = torch.arange(cols.numel(), device=cols.device)
+            block_of_edge = torch.searchsorted(edge_bounds, edge_ids, right=True) - 1
+            del edge_ids
+            first = torch.full((self.n_halo,), k, dtype=torch.int64, device=cols.device)
+            first.scatter_reduce_(0, pos[~own], block_of_edge[~own], reduce="amin")
+            del block_of_edge
+            first_sorted, perm = torch.sort(first, stable=True)  # new position j holds old position perm[j]
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(self.n_halo, device=cols.device)
+            self.halo_ids = halo_sorted[perm].contiguous()
+            pos = inv[pos.clamp(max=self.n_halo - 1)]
+            counts = torch.bincount(first_sorted, minlength=k + 1)[:k]
+            self.chunk_offsets = [0] + torch.cumsum(counts, 0).tolist()
+            self.row_bounds = list(row_bounds)
+        else:
+            self.halo_ids = halo_sorted
         self.local_indices = torch.where(own, cols - lo, pos.to(cols.dtype) + shard.n_local).to(torch.int32)
         self.own_mask = own
-        bounds_t = torch.tensor(shard.bounds, dtype=self.halo_ids.dtype, device=cols.device)
-        # halo_ids[owner_offsets[p]:owner_offsets[p+1]] live on rank p
-        self.owner_offsets = torch.searchsorted(self.halo_ids, bounds_t).tolist()
 
 
 def split_local_halo(shard, plan):

@@ -57,12 +57,13 @@ class SharedBuffer:
 
 
 class PartitionedSpmm:
-    def __init__(self, shard, d, device, group=None, mode="peer", overlap=True, weight_mode=ops.W_EDGE):
+    def __init__(self, shard, d, device, group=None, mode="peer", overlap=True, weight_mode=ops.W_EDGE, row_blocks=1):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
         self.rank = shard.rank
         self.mode = mode if self.world > 1 else "local"  # "local": the shard is the whole graph, no exchange
-        self.overlap = overlap and self.mode == "peer"
+        self.row_blocks = int(row_blocks) if self.mode == "peer" else 1
+        self.overlap = overlap and self.mode == "peer" and self.row_blocks <= 1
         self.weight_mode = weight_mode
         n_local = shard.n_local
         self.out = torch.empty(n_local, d, dtype=torch.float32, device=self.device)
@@ -78,7 +79,13 @@ class PartitionedSpmm:
             self.plan = None
             self.halo_bytes = (self.world - 1) * self.max_rows * d * 4
             return
-        self.plan = HaloPlan(shard)
+        row_bounds = None
+        if self.row_blocks > 1:
+            # edge-balanced row blocks inside the shard: block b is aggregated while the halo rows that only later
+            # blocks need are still in flight
+            probe = ops.PreparedGraph(shard.indptr, torch.empty(0, dtype=torch.int32, device=self.device), 0)
+            row_bounds = ops.partition_rows(probe, self.row_blocks).tolist()
+        self.plan = HaloPlan(shard, row_bounds)
         n_halo = self.plan.n_halo
         self.shared = SharedBuffer((n_local + n_halo) * d, self.device)
         self.xbuf = self.shared.tensor().view(n_local + n_halo, d)
@@ -93,6 +100,18 @@ class PartitionedSpmm:
             self._ptrs = (C.c_void_p * self.world)(*ptrs)
             self._bounds = (C.c_int64 * (self.world + 1))(*shard.bounds)
             self.side = torch.cuda.Stream(device=self.device, priority=-1)
+            if self.plan.row_bounds is not None:
+                self.blocks = []
+                rb = self.plan.row_bounds
+                ip_all = shard.indptr
+                for b in range(len(rb) - 1):
+                    e0, e1 = int(ip_all[rb[b]]), int(ip_all[rb[b + 1]])
+                    g_b = ops.PreparedGraph((ip_all[rb[b]:rb[b + 1] + 1] - e0).contiguous(),
+                                            self.plan.local_indices[e0:e1].contiguous(), n_local + n_halo)
+                    v_b = None if shard.values is None else shard.values[e0:e1].contiguous()
+                    self.blocks.append((g_b, v_b, self.out[rb[b]:rb[b + 1]], torch.cuda.Event()))
+            else:
+                self.row_blocks = 1
             if self.overlap:
                 (ipo, ixo, vo), (iph, ixh, vh) = split_local_halo(shard, self.plan)
                 self.g_own = ops.PreparedGraph(ipo, ixo, n_local)
@@ -121,11 +140,16 @@ class PartitionedSpmm:
         if events is not None:
             events.append(("fetch", a, self._mark(events, "fetch")))
 
-    def _fetch_halo(self):
+    def _fetch_halo(self, first=0, last=None):
+        """Gather halo rows [first, last) of the plan's list into their slots of the halo buffer."""
+        last = self.plan.n_halo if last is None else last
+        if last <= first:
+            return
         st = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
-            check(lib().yitu_halo_gather_f32(self.world, self._ptrs, self._bounds, C.c_void_p(self.plan.halo_ids.data_ptr()),
-                                             self.plan.n_halo, self.d, C.c_void_p(self.x_halo.data_ptr()),
+            check(lib().yitu_halo_gather_f32(self.world, self._ptrs, self._bounds,
+                                             C.c_void_p(self.plan.halo_ids.data_ptr() + 4 * first), last - first, self.d,
+                                             C.c_void_p(self.x_halo.data_ptr() + 4 * self.d * first),
                                              C.c_void_p(st.cuda_stream)))
 
     def _spmm(self, g, x, vals, accumulate=False, events=None):
@@ -146,6 +170,25 @@ class PartitionedSpmm:
         if self.mode == "allgather":
             dist.all_gather_into_tensor(self.rep, self._slot, group=self.group)
             return self._spmm(self.graph, self.rep, sh.values, events=events)
+        if self.row_blocks > 1:
+            main = torch.cuda.current_stream(self.device)
+            self.side.wait_stream(main)
+            off = self.plan.chunk_offsets
+            with torch.cuda.stream(self.side):
+                for b, (_, _, _, ready) in enumerate(self.blocks):
+                    a = self._mark(events, "fetch")
+                    self._fetch_halo(off[b], off[b + 1])
+                    if events is not None:
+                        events.append(("fetch", a, self._mark(events, "fetch")))
+                    ready.record(self.side)
+            for g_b, v_b, out_b, ready in self.blocks:
+                main.wait_event(ready)
+                a = self._mark(events, "spmm")
+                ops.spmm(g_b, self.xbuf, mode=self.weight_mode if v_b is not None else ops.W_NONE, edge_values=v_b,
+                         out=out_b)
+                if events is not None:
+                    events.append(("spmm", a, self._mark(events, "spmm")))
+            return self.out
         if not self.overlap:
             self.fetch_halo(events)
             return self._spmm(self.graph, self.xbuf, sh.values, events=events)
