@@ -161,6 +161,48 @@ class SpmmWorkload:
         self.h_out.copy_(out, non_blocking=True)
         self.h_gout.copy_(gout, non_blocking=True)
 
+    def e2e_run(self, steps):
+        """Pipelined end-to-end loop: the step's two feature matrices are copied in from pinned host memory on a copy-in
+        stream, aggregated on the compute stream through the public ops.spmm call, and the two results copied back to
+        pinned host memory on a copy-out stream; buffers are double-buffered so that the copy-in of step k+1 and the
+        copy-out of step k-1 (PCIe is full duplex) run beside the compute of step k.  Returns ms per step, with every
+        step's H2D and D2H inside the timed region."""
+        t, ops, dev = self.torch, self.ops, self.x.device
+        main = t.cuda.current_stream(dev)
+        s_in, s_out = t.cuda.Stream(device=dev), t.cuda.Stream(device=dev)
+        bufs = [{k: t.empty_like(self.x) for k in ("x", "g", "out", "gout")} for _ in range(2)]
+        in_done = [None, None]
+        comp_done = [None, None]
+        out_done = [None, None]
+        start, stop = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        t.cuda.synchronize(dev)
+        start.record(main)
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        for k in range(steps):
+            b = bufs[k % 2]
+            with t.cuda.stream(s_in):
+                if comp_done[k % 2] is not None:
+                    s_in.wait_event(comp_done[k % 2])  # the compute that read this input buffer two steps ago
+                b["x"].copy_(self.h_x, non_blocking=True)
+                b["g"].copy_(self.h_g, non_blocking=True)
+                in_done[k % 2] = s_in.record_event()
+            main.wait_event(in_done[k % 2])
+            if out_done[k % 2] is not None:
+                main.wait_event(out_done[k % 2])  # the copy-out that read this output buffer two steps ago
+            ops.spmm(self.g, b["x"], mode=ops.W_EDGE, edge_values=self.values, out=b["out"])
+            ops.spmm(self.gt, b["g"], mode=ops.W_EDGE, edge_values=self.values_t, out=b["gout"])
+            comp_done[k % 2] = main.record_event()
+            with t.cuda.stream(s_out):
+                s_out.wait_event(comp_done[k % 2])
+                self.h_out.copy_(b["out"], non_blocking=True)
+                self.h_gout.copy_(b["gout"], non_blocking=True)
+                out_done[k % 2] = s_out.record_event()
+        main.wait_stream(s_out)
+        stop.record(main)
+        t.cuda.synchronize(dev)
+        return start.elapsed_time(stop) / steps
+
     def verify(self):
         """A*1 equals the in-degree exactly; cheap, size-independent."""
         t, ops = self.torch, self.ops
@@ -497,8 +539,16 @@ def run_single(args):
             wl.e2e_step()
         e1.record()
         torch.cuda.synchronize()
-        e2e = {"value": wl.units_per_step / (e0.elapsed_time(e1) / e_steps * 1e-3) / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
+        e2e_ms = e0.elapsed_time(e1) / e_steps
+        e2e = {"value": wl.units_per_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms, "mode": "serial"}
+        if hasattr(wl, "e2e_run"):
+            # the same bytes per step with copy-in / compute / copy-out of neighbouring steps overlapped
+            piped_ms = wl.e2e_run(max(8, e_steps))
+            e2e["serial_value"] = e2e["value"]
+            if piped_ms < e2e_ms:
+                e2e.update(value=wl.units_per_step / (piped_ms * 1e-3) / 1e9, ms_per_step=piped_ms,
+                           mode="pipelined (double-buffered copy-in / compute / copy-out streams)")
 
     base = None if args.no_cpu_baseline else cpu_baseline(wl.cpu_sample())
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
