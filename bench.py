@@ -104,7 +104,7 @@ class ClockSampler:
 class SpmmWorkload:
     """configs[1]: forward and transposed sum-aggregation SpMM."""
     name = "spmm_rmat_n2097152_e67108864_d256_fwd_bwd"
-    dominant_kernel = "spmm_kernel<32,2,4,8,false,true>"
+    dominant_kernel = "spmm_kernel<32,1,8,4,false,true>"
 
     def __init__(self, device, n=1 << 21, e=1 << 26, d=256):
         import torch
