@@ -293,7 +293,7 @@ class GatWorkload:
 class RgcnWorkload:
     """configs[3]: hetero RGCN aggregation: per destination type one pass over the stitched relations."""
     name = "rgcn_4types_8rel_x4M_d64"
-    dominant_kernel = "spmm_kernel<16,1,4,4,false,true>"
+    dominant_kernel = "spmm_wide_kernel<8,1,true>"
 
     def __init__(self, device, d=64):
         import torch
