@@ -170,3 +170,64 @@ def test_graph_generators_are_reproducible_and_canonical():
     assert len(rels) == 8 and {r[1] for r in rels} == {0, 1, 2, 3}
     for st, dt, ipr, ixr in rels:
         assert ipr.numel() == (500, 300, 200, 100)[dt] + 1 and int(ixr.max()) < (500, 300, 200, 100)[st]
+
+
+# ------------------------------------------------------------------------------------------- properties
+from hypothesis import given, settings, strategies as st
+
+
+@settings(max_examples=60, deadline=None)
+@given(degs=st.lists(st.integers(0, 70), min_size=0, max_size=40), part_size=st.sampled_from([1, 2, 3, 8, 32]))
+def test_build_part_matches_checker_on_random_degrees(degs, part_size):
+    from oracle import oracle as O
+    from yitu_b200 import YiTu_GNN_kernel as K
+    indptr = np.concatenate([[0], np.cumsum(degs)]).astype(np.int32)
+    pp, p2n = K.build_part(part_size, torch.from_numpy(indptr))
+    opp, op2n = O.build_part(part_size, indptr)
+    assert pp.tolist() == opp.tolist() and p2n.tolist() == op2n.tolist()
+    # group table invariants (when the last node has edges): monotone pointers that tile every row
+    if len(degs) and degs[-1] > 0:
+        ptr = pp.numpy().astype(np.int64)
+        assert ptr[0] == 0 and ptr[-1] == indptr[-1] and np.all(np.diff(ptr) >= 1) and np.all(np.diff(ptr) <= part_size)
+        assert np.array_equal(np.bincount(p2n.numpy().astype(np.int64), minlength=len(degs)),
+                              -(-np.asarray(degs) // part_size))
+
+
+@settings(max_examples=40, deadline=None)
+@given(data=st.data())
+def test_stitch_csr_matches_checker_on_random_blocks(data):
+    from oracle import oracle as O
+    from yitu_b200.xgnn_h import Block, stitch_csr
+    n_rows = data.draw(st.integers(0, 12))
+    blocks = []
+    for _ in range(data.draw(st.integers(1, 5))):
+        n_cols = data.draw(st.integers(1, 9))
+        rows = [sorted(data.draw(st.sets(st.integers(0, n_cols - 1), max_size=n_cols))) for _ in range(n_rows)]
+        indptr = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int32)
+        indices = np.asarray([c for r in rows for c in r], dtype=np.int32)
+        blocks.append((indptr, indices, n_cols))
+    st_blk = stitch_csr([Block([n_rows, c], [torch.from_numpy(a), torch.from_numpy(b)]) for a, b, c in blocks])
+    o_ip, o_ix, o_cols = O.stitch_csr(blocks)
+    assert st_blk.adj_sparse[0].tolist() == o_ip.tolist() and st_blk.adj_sparse[1].tolist() == o_ix.tolist()
+    assert st_blk.size == [n_rows, o_cols]
+    # every stitched index decodes to (block, column) of exactly one input edge, in block order within a row
+    ix = st_blk.adj_sparse[1].numpy().astype(np.int64)
+    seg = ix >> 24
+    ip = st_blk.adj_sparse[0].numpy()
+    for r in range(n_rows):
+        assert np.all(np.diff(seg[ip[r]:ip[r + 1]]) >= 0)
+
+
+@settings(max_examples=60, deadline=None)
+@given(degs=st.lists(st.integers(0, 500), min_size=1, max_size=60), parts=st.integers(1, 9))
+def test_partition_rows_properties(degs, parts):
+    from oracle import oracle as O
+    from yitu_b200 import ops
+    indptr = np.concatenate([[0], np.cumsum(degs)]).astype(np.int64)
+    b = ops.partition_rows_host(torch.from_numpy(indptr), parts).numpy()
+    assert b.tolist() == O.partition_rows(indptr, parts).tolist()
+    assert b[0] == 0 and b[-1] == len(degs) and np.all(np.diff(b) >= 0)
+    nnz = int(indptr[-1])
+    for p in range(1, parts):
+        target = -(-p * nnz // parts)
+        assert indptr[b[p]] >= target and (b[p] == 0 or indptr[b[p] - 1] < target)
