@@ -306,3 +306,27 @@ def test_reference_check_bundle():
     assert torch.allclose(y1, y3, atol=1e-4) and torch.allclose(y2, y4, atol=1e-4)
     assert torch.allclose(gx, x.grad, atol=1e-4)
     assert torch.allclose(g1, fc1.weight.grad, atol=1e-3) and torch.allclose(g2, fc2.weight.grad, atol=1e-3)
+
+
+def test_full_size_gat_sampled_rows_against_float64():
+    """Benchmark-size GAT layer core (2^20 nodes, 34.6 M edges, 8 heads x 32): sampled destination rows of the fused
+    forward against a float64 softmax-weighted sum; softmax weights of every row sum to one (aggregating ones)."""
+    from yitu_b200 import graphs, ops
+    n, H, F = 1 << 20, 8, 32
+    indptr, indices = graphs.gat_uniform(device="cuda", n=n, e=1 << 25)
+    g = ops.PreparedGraph(indptr, indices, n)
+    x = graphs.randn_features(1, n, H * F, device="cuda").view(n, H, F)
+    q = graphs.uniform_values(2, (n, H), -2, 2, device="cuda")
+    k = graphs.uniform_values(3, (n, H), -2, 2, device="cuda")
+    out, rmax, rsum = ops.gat_fwd(g, q, k, x)
+    ones_out, _, _ = ops.gat_fwd(g, q, k, torch.ones_like(x))
+    assert float((ones_out - 1.0).abs().max()) < 1e-5
+    gen = torch.Generator().manual_seed(1)
+    for r in torch.randint(0, n, (200,), generator=gen).tolist():
+        b, e = int(indptr[r]), int(indptr[r + 1])
+        cols = indices[b:e].long()
+        s = torch.nn.functional.leaky_relu(q[r].double()[None, :] + k[cols].double(), 0.2)      # [deg, H]
+        a = torch.softmax(s, dim=0)
+        truth = (a[:, :, None] * x[cols].double()).sum(0)                                       # [H, F]
+        err = (out[r].double() - truth).abs().max()
+        assert float(err) <= 1e-5 * (float(truth.abs().max()) + 1e-30) * 2, "row %d off by %g" % (r, float(err))

@@ -186,3 +186,42 @@ def test_full_size_properties():
     lhs = float((y1.double() * yv.double()).sum())
     rhs = float((x1.double() * aty.double()).sum())
     assert abs(lhs - rhs) <= 1e-5 * max(abs(lhs), abs(rhs), 1.0) + 1e-2
+
+
+def _rows_truth_f64(indptr, indices, values, x, rows):
+    """float64 aggregation of a few destination rows, straight from the definition."""
+    out = []
+    for r in rows.tolist():
+        b, e = int(indptr[r]), int(indptr[r + 1])
+        cols = indices[b:e].long()
+        w = values[b:e].double() if values is not None else torch.ones(e - b, dtype=torch.float64, device=x.device)
+        out.append((w[:, None] * x[cols].double()).sum(0))
+    return torch.stack(out)
+
+
+def test_full_size_sampled_rows_against_float64():
+    """Benchmark-size SpMM (2^21 nodes, 63.5 M edges, 256 features): 300 sampled destination rows, among them the
+    longest hub rows, forward and transposed, against float64 sums at the 1e-5 bar."""
+    from yitu_b200 import graphs, ops
+    n = 1 << 21
+    indptr, indices, values = graphs.spmm_rmat(device="cuda", n=n, e=1 << 26)
+    g = ops.PreparedGraph(indptr, indices, n)
+    x = graphs.randn_features(1, n, 256, device="cuda")
+    y = ops.spmm(g, x, mode=ops.W_EDGE, edge_values=values)
+    deg = indptr[1:] - indptr[:-1]
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    rows = torch.cat([torch.topk(deg, 20).indices.cpu(), torch.randint(0, n, (280,), generator=gen)])
+    truth = _rows_truth_f64(indptr, indices, values, x, rows)
+    scale = float(truth.abs().max())
+    err = (y[rows.cuda()].double() - truth).abs()
+    assert float((err - 1e-5 * (truth.abs() + scale)).max()) <= 0, "forward rows off by %g" % float(err.max())
+    # transposed product over the CSC built on the device
+    gt = g.t_prepared()
+    t_indptr, t_rows, t_perm = g.transpose()
+    yt = ops.spmm(gt, x, mode=ops.W_EDGE, edge_values=values, edge_perm=t_perm)
+    out_deg = t_indptr[1:] - t_indptr[:-1]
+    cols = torch.cat([torch.topk(out_deg, 20).indices.cpu(), torch.randint(0, n, (280,), generator=gen)])
+    truth_t = _rows_truth_f64(t_indptr, t_rows, values[t_perm.long()], x, cols)
+    scale_t = float(truth_t.abs().max())
+    err_t = (yt[cols.cuda()].double() - truth_t).abs()
+    assert float((err_t - 1e-5 * (truth_t.abs() + scale_t)).max()) <= 0, "transposed rows off by %g" % float(err_t.max())
