@@ -133,8 +133,17 @@ edge_gather_sum_kernel(int64_t n_cols, const void *t_indptr, int is64, const int
     for (int hc = 0; hc < H; hc += HB) {
         const int h = hc + hs;
         float a = 0.0f;
-        if (h < H)
-            for (int64_t j = b + slot; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
+        if (h < H) {
+            int64_t j = b + slot;
+            for (; j + 3 * ES < e; j += 4 * ES) {  // four permutation loads, then four value loads, in flight together
+                const int p0 = __ldg(perm + j), p1 = __ldg(perm + j + ES), p2 = __ldg(perm + j + 2 * ES),
+                          p3 = __ldg(perm + j + 3 * ES);
+                const float v0 = __ldg(vals + static_cast<int64_t>(p0) * H + h), v1 = __ldg(vals + static_cast<int64_t>(p1) * H + h),
+                            v2 = __ldg(vals + static_cast<int64_t>(p2) * H + h), v3 = __ldg(vals + static_cast<int64_t>(p3) * H + h);
+                a += v0; a += v1; a += v2; a += v3;
+            }
+            for (; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
+        }
         for (int o = HB; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
         if (slot == 0 && h < H) out[c * H + h] = a;
     }
