@@ -138,3 +138,39 @@ def test_hetero_conv_and_stitched_form_agree():
                               reduce="sum").cuda()
     summed.load_state_dict(stitched.state_dict())
     assert _close(summed({"rel_" + n: xs[n] for n in sizes}), ref, 3e-5)
+
+
+def test_two_layer_gcn_replays_from_a_cuda_graph():
+    """The operators take the current stream and allocate only through torch, so a whole forward pass can be captured
+    once and replayed (the small 2-layer GCN configuration is launch-bound when run eagerly)."""
+    from yitu_b200 import YiTu_GNN_kernel as K, graphs
+    from yitu_b200.nn import GCNConv
+    n = 16384
+    indptr, indices, norm = graphs.gcn_small()
+    info = _Info()
+    info.row_pointers, info.column_index, info.degrees = indptr.cuda(), indices.cuda(), norm.cuda()
+    pp, p2n = K.build_part(32, indptr)
+    info.partPtr, info.part2Node = pp.int().cuda(), p2n.int().cuda()
+    info.partSize, info.dimWorker, info.warpPerBlock = 32, 32, 2
+    l1, l2 = GCNConv(128, 64).cuda(), GCNConv(64, 16).cuda()
+    x = graphs.randn_features(0, n, 128, device="cuda")
+
+    def forward():
+        with torch.no_grad():
+            return l2(torch.relu(l1(x, info)), info)
+
+    eager = forward()  # also builds the cached graph schedule, which synchronises and must precede the capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            forward()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = forward()
+    x.copy_(graphs.randn_features(5, n, 128, device="cuda"))  # new input in the captured buffer
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, forward()), "replay must reproduce the eager result for the new input"
+    assert not torch.equal(captured, eager)
