@@ -330,3 +330,21 @@ def test_full_size_gat_sampled_rows_against_float64():
         truth = (a[:, :, None] * x[cols].double()).sum(0)                                       # [H, F]
         err = (out[r].double() - truth).abs().max()
         assert float(err) <= 1e-5 * (float(truth.abs().max()) + 1e-30) * 2, "row %d off by %g" % (r, float(err))
+
+
+def test_gspmm_without_edge_values_is_the_plain_sum(oracle):
+    from yitu_b200 import xgnn_h
+    from yitu_b200.xgnn_h import sparse
+    rng = np.random.default_rng(12)
+    indptr, indices = random_csr(rng, 120, 90, density=0.1)
+    blk = xgnn_h.Block([120, 90], [_dev(indptr), _dev(indices)])
+    x = torch.randn(90, 2, 24, device="cuda", requires_grad=True)
+    w = torch.randn(120, 2, 24, device="cuda")
+    y = sparse.gspmm(blk, None, x)
+    (y * w).sum().backward()
+    assert_close(y.detach().cpu().numpy(), oracle.spmm(indptr, indices, x.detach().cpu().numpy()), what="sum")
+    ones = torch.ones(indices.shape[0], 2, device="cuda")
+    x2 = x.detach().clone().requires_grad_()
+    y2 = sparse.gspmm(blk, ones, x2)
+    (y2 * w).sum().backward()
+    assert_close(x.grad.cpu().numpy(), x2.grad.cpu().numpy(), what="grad of the sum")

@@ -3,7 +3,7 @@ operator the reference lowers to two calls (fused_gsddmm then gspmm)."""
 import torch
 from torch import autograd
 
-from .. import graph_ext
+from .. import graph_ext, ops
 from . import block
 
 
@@ -25,10 +25,25 @@ class GSPMMFunction(autograd.Function):
         return None, grad_a, grad_x
 
 
+class GSPMMSumFunction(autograd.Function):
+    """gspmm with edge=None: the reference materialises a [E,H] tensor of ones and multiplies by it
+    (xgnn_h/sparse.py:43-48); the same sum is taken here with the unweighted kernel, forward and transposed."""
+
+    @staticmethod
+    def forward(ctx, adj_sparse, x):
+        g = ops.prepared(adj_sparse[0], adj_sparse[1], x.size(0), ops.STITCH_MASK)
+        ctx.graph = g
+        return ops.spmm(g, x.contiguous(), n_heads=x.size(1), mode=ops.W_NONE)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return None, ops.spmm(ctx.graph.t_prepared(), grad_out.contiguous(), n_heads=grad_out.size(1), mode=ops.W_NONE)
+
+
 def gspmm(block: block.Block, edge: torch.Tensor, x: torch.Tensor):
     assert x.dim() == 3
     if edge is None:
-        edge = torch.ones(size=[block.adj_sparse[1].size(0), x.size(1)], device=x.device)
+        return GSPMMSumFunction.apply(block.adj_sparse, x)
     return GSPMMFunction.apply(block.adj_sparse, edge, x)
 
 
