@@ -348,3 +348,30 @@ def test_gspmm_without_edge_values_is_the_plain_sum(oracle):
     y2 = sparse.gspmm(blk, ones, x2)
     (y2 * w).sum().backward()
     assert_close(x.grad.cpu().numpy(), x2.grad.cpu().numpy(), what="grad of the sum")
+
+
+def test_attention_ops_with_int64_row_pointers(oracle):
+    """Row pointers may be int64 (graphs beyond 2^31 edges need them); same results as with int32."""
+    from yitu_b200 import ops
+    rng = np.random.default_rng(31)
+    n_dst, n_src, H, F = 140, 110, 4, 16
+    indptr, indices = random_csr(rng, n_dst, n_src, density=0.1, hubs=1, hub_deg=90)
+    q = rng.standard_normal((n_dst, H)).astype(np.float32)
+    k = rng.standard_normal((n_src, H)).astype(np.float32)
+    x = rng.standard_normal((n_src, H, F)).astype(np.float32)
+    g = rng.standard_normal((n_dst, H, F)).astype(np.float32)
+    graph = ops.PreparedGraph(_dev(indptr.astype(np.int64)), _dev(indices), n_src)
+    out, rmax, rsum = ops.gat_fwd(graph, _dev(q), _dev(k), _dev(x))
+    ref_out, ref_attn = oracle.gat_forward(indptr, indices, q, k, x)
+    assert_close(out.cpu().numpy(), ref_out, what="gat out (int64 indptr)")
+    gq, gk, gx = ops.gat_bwd(graph, _dev(q), _dev(k), _dev(x), out, rmax, rsum, _dev(g))
+    rgq, rgk, rgx = oracle.gat_backward(indptr, indices, q, k, x, ref_attn, g)
+    assert_close(gq.cpu().numpy(), rgq, rtol=2e-5, what="grad_query (int64 indptr)")
+    assert_close(gk.cpu().numpy(), rgk, rtol=2e-5, what="grad_key (int64 indptr)")
+    assert_close(gx.cpu().numpy(), rgx, rtol=2e-5, what="grad_x (int64 indptr)")
+    attn = ops.edge_softmax_fwd(graph, _dev(q[None]), _dev(k))
+    assert_close(attn.cpu().numpy(), ref_attn, what="attn (int64 indptr)")
+    t_ip, t_rows, t_perm = graph.transpose()
+    assert t_ip.dtype == torch.int64
+    r_ip, r_rows, r_perm = oracle.csr_transpose(indptr, indices, n_src)
+    assert np.array_equal(t_ip.cpu().numpy(), r_ip) and np.array_equal(t_perm.cpu().numpy(), r_perm)
