@@ -586,6 +586,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
     ap.add_argument("--no-scaling-base", action="store_true",
                     help="default workload: skip timing the N>1 workload on this one GPU")
+    ap.add_argument("--row-cost", type=int, default=0,
+                    help="partitioned: balance edges + ROW_COST * rows instead of edges alone (not the prescribed split)")
     ap.add_argument("--no-single", action="store_true", help="partitioned: skip the 1-GPU comparison run on rank 0")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

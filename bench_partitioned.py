@@ -91,7 +91,7 @@ def run(args):
 
     indptr, indices, values = graphs.spmm_partitioned(device=dev, n=n, e=e)
     nnz = indices.numel()
-    bounds = partition_bounds(indptr, world)
+    bounds = partition_bounds(indptr, world, row_cost=args.row_cost)
     shard = RowShard(indptr, indices, values, bounds, rank)
     if rank != 0:
         del indptr, indices, values
@@ -188,7 +188,9 @@ def run(args):
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
                 "config": {"workload": "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d), "nnz": nnz,
-                           "parallelism": "row_partition_%d" % world, "halo": best, "trial_ms": trial,
+                           "parallelism": "row_partition_%d" % world,
+                           "balance": "edges" if not args.row_cost else "edges + %d * rows" % args.row_cost,
+                           "halo": best, "trial_ms": trial,
                            "l2": "inputs_larger_than_l2", "rows_per_rank": [int(s[4]) for s in per_rank],
                            "edges_per_rank": [int(s[3]) for s in per_rank],
                            "halo_bytes_per_rank": [int(s[2]) for s in per_rank],

@@ -5,11 +5,15 @@ import torch
 from .. import ops
 
 
-def partition_bounds(indptr, n_parts):
+def partition_bounds(indptr, n_parts, row_cost=0):
     """Edge-balanced contiguous row ranges: bounds[p] = min{ r : indptr[r] >= ceil(p*nnz/P) } as a Python list.
 
     The reference's own range partition balances node counts (YiTu_GNN/mmap/partition.py:12-22); balancing
-    edges balances the gather work instead."""
+    edges balances the gather work instead.  row_cost > 0 balances edges + row_cost * rows (a destination row costs
+    about as much as row_cost edges: its output write and per-row latency), which evens out both the aggregation
+    time and the size of the feature shards on skewed graphs."""
+    if row_cost:
+        indptr = indptr.long() + int(row_cost) * torch.arange(indptr.numel(), dtype=torch.int64, device=indptr.device)
     if indptr.is_cuda:
         g = ops.PreparedGraph(indptr, torch.empty(0, dtype=torch.int32, device=indptr.device), 0)
         return ops.partition_rows(g, n_parts).tolist()
