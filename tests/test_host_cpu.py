@@ -231,3 +231,20 @@ def test_partition_rows_properties(degs, parts):
     for p in range(1, parts):
         target = -(-p * nnz // parts)
         assert indptr[b[p]] >= target and (b[p] == 0 or indptr[b[p] - 1] < target)
+
+
+def test_cost_aware_partition_balances_edges_plus_rows():
+    from yitu_b200.distributed import partition_bounds
+    rng = np.random.default_rng(6)
+    deg = np.concatenate([rng.integers(200, 400, size=50), rng.integers(0, 3, size=5000)])  # hubs first, then a long tail
+    indptr = torch.from_numpy(np.concatenate([[0], np.cumsum(deg)]).astype(np.int64))
+    plain = partition_bounds(indptr, 4)
+    aware = partition_bounds(indptr, 4, row_cost=7)
+    assert plain[0] == aware[0] == 0 and plain[-1] == aware[-1] == len(deg)
+    cost = indptr.numpy() + 7 * np.arange(len(deg) + 1)
+    for p in range(1, 4):
+        target = -(-p * int(cost[-1]) // 4)
+        assert cost[aware[p]] >= target and cost[aware[p] - 1] < target
+    rows_plain = np.diff(plain)
+    rows_aware = np.diff(aware)
+    assert rows_aware.max() < rows_plain.max(), "weighing rows must shrink the largest shard of a skewed graph"
