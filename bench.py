@@ -224,7 +224,7 @@ class SpmmWorkload:
 class GatWorkload:
     """configs[2]: fused GAT layer core forward + backward."""
     name = "gat_uniform_n1048576_e33554432_h8_f32_fwd_bwd"
-    dominant_kernel = "gat_fwd_kernel<2>"
+    dominant_kernel = "gat_fwd_kernel_r64<2,false>"
 
     def __init__(self, device, n=1 << 20, e=1 << 25, H=8, F=32):
         import torch
@@ -450,6 +450,90 @@ def run_reference_gpu_comparison(args):
     print(json.dumps(out))
 
 
+def run_layer_fusion(args):
+    """Layer-level effect of the fused epilogues on the benchmark graphs: the GCN layer tail (norm * aggregate, ReLU)
+    and the GAT layer tail (mean over heads, ELU), forward and forward+backward, fused into the aggregation kernels
+    against the same kernels followed by separate element-wise torch operators (the reference's formulation).
+    Prints one JSON line; not the headline benchmark."""
+    import torch
+    from yitu_b200 import graphs, ops
+    from yitu_b200.nn.layers import aggregate
+    from yitu_b200.xgnn_h import Block, sparse
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    reps = max(3, args.steps)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    out = {"workload": "layer_epilogue_fusion", "unit": "ms", "reps": reps, "rows": []}
+    shift = args.scale
+    # GCN layer tail on the D=256 R-MAT graph: relu(norm * (A h))
+    n, e, d = (1 << 21) >> shift, (1 << 26) >> shift, 256
+    indptr, indices, _ = graphs.spmm_rmat(device=dev, n=n, e=e)
+    blk = Block([n, n], [indptr, indices])
+    norm = ops.degree_norm(indptr, ops.DEG_INV)
+    h = graphs.randn_features(1, n, d, device=dev).requires_grad_()
+    gy = graphs.randn_features(2, n, d, device=dev)
+
+    def gcn(fused, backward):
+        if fused:
+            y = aggregate(blk, h, row_scale=norm, activation="relu")
+        else:
+            y = torch.relu(norm.view(-1, 1) * aggregate(blk, h))
+        if backward:
+            y.backward(gy)
+            h.grad = None
+
+    err = float((aggregate(blk, h, row_scale=norm, activation="relu") -
+                 torch.relu(norm.view(-1, 1) * aggregate(blk, h))).abs().max())
+    row = {"layer": "GCN tail relu(norm*A h)", "n": n, "nnz": indices.numel(), "d": d, "max_abs_diff": err}
+    for backward in (False, True):
+        key = "fwd_bwd" if backward else "fwd"
+        row["unfused_%s_ms" % key] = timed(lambda: gcn(False, backward))
+        row["fused_%s_ms" % key] = timed(lambda: gcn(True, backward))
+    out["rows"].append(row)
+    del blk, h, gy, indptr, indices, norm
+    torch.cuda.empty_cache()
+    # GAT layer tail on the 8x32 uniform graph: elu(mean_h(softmax-weighted aggregation))
+    n, e, H, F = (1 << 20) >> shift, (1 << 25) >> shift, 8, 32
+    indptr, indices = graphs.gat_uniform(device=dev, n=n, e=e)
+    blk = Block([n, n], [indptr, indices])
+    x = graphs.randn_features(1, n, H * F, device=dev).view(n, H, F).requires_grad_()
+    q = graphs.uniform_values(5, (n, H), -1, 1, device=dev).requires_grad_()
+    k = graphs.uniform_values(6, (n, H), -1, 1, device=dev).requires_grad_()
+    gy = graphs.randn_features(2, n, F, device=dev)
+
+    def gat(fused, backward):
+        if fused:
+            y = sparse.fused_gat(blk, q, k, x, head_mean=True, activation="elu")
+        else:
+            y = torch.nn.functional.elu(torch.mean(sparse.fused_gat(blk, q, k, x), dim=1))
+        if backward:
+            y.backward(gy)
+            x.grad = q.grad = k.grad = None
+
+    err = float((sparse.fused_gat(blk, q, k, x, head_mean=True, activation="elu") -
+                 torch.nn.functional.elu(torch.mean(sparse.fused_gat(blk, q, k, x), dim=1))).abs().max())
+    row = {"layer": "GAT tail elu(mean_heads(attention aggregation))", "n": n, "nnz": indices.numel(), "heads": H,
+           "feats": F, "max_abs_diff": err}
+    for backward in (False, True):
+        key = "fwd_bwd" if backward else "fwd"
+        row["unfused_%s_ms" % key] = timed(lambda: gat(False, backward))
+        row["fused_%s_ms" % key] = timed(lambda: gat(True, backward))
+    out["rows"].append(row)
+    print(json.dumps(out))
+
+
 def partitioned_single_gpu_base(dev, steps=5):
     """The N>1 workload (row-partitioned SpMM graph) on this one GPU, so that a scaling series that starts from the
     default N=1 line has its like-for-like base: returns Gedge*feat/s and ms per step."""
@@ -580,7 +664,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu"])
+    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu", "layers"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
@@ -601,6 +685,9 @@ def main():
         return  # single-GPU workloads: extra ranks have nothing to do
     if args.workload == "refgpu":
         run_reference_gpu_comparison(args)
+        return
+    if args.workload == "layers":
+        run_layer_fusion(args)
         return
     run_single(args)
 

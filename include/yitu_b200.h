@@ -131,7 +131,16 @@ enum {
     YITU_W_EDGE_HEAD = 3  /* w = values[e*H + h]         graph_ext.spmm_forward       */
 };
 
-/* out[r,h,k] = alpha * row_scale[r] * sum_{e in row r} w(e,h) * x[col_e,h,k]   (+ out[r,h,k] if accumulate)
+/* Epilogue activations fused into the aggregation kernels (the layers apply them right after the aggregation:
+ * ReLU in the GCN models, ELU in the GAT models — YiTu_GNN/YiTu_H/test/common/model.py:46-49,126-129). */
+enum {
+    YITU_ACT_NONE = 0,
+    YITU_ACT_RELU = 1,
+    YITU_ACT_ELU = 2 /* v > 0 ? v : exp(v) - 1 */
+};
+
+/* out[r,h,k] = act( alpha * row_scale[r] * sum_{e in row r} w(e,h) * x[col_e,h,k]  (+ out[r,h,k] if accumulate)
+ *                   + bias[h*F+k] )
  *
  * Replaces the aggregation kernels of
  *   ccsrc/kernel/YiTu_GNN_kernel.cu:179-257 (SAG), :319-415 / :477-556 (GCN fwd / bwd),
@@ -150,14 +159,18 @@ typedef struct yitu_spmm_args_t {
     const float *norm_src;    /* W_NODE: [n_cols] */
     const float *row_scale;   /* optional [n_rows] */
     float alpha;              /* scalar epilogue (GIN epsilon; 1/#relations) */
-    int32_t reserved;
+    int32_t activation;       /* YITU_ACT_*, applied last */
     const float *x;           /* [n_cols, x_stride] source features */
-    int64_t x_stride;         /* floats between feature rows (>= H*F) */
+    int64_t x_stride;         /* floats between feature rows (>= H*F; >= F with x_shared_heads) */
     float *out;               /* [n_rows, out_stride] */
     int64_t out_stride;
     const yitu_hub_plan_t *plan; /* optional hub-row schedule (host struct, device tables) */
     float *scratch;              /* plan != NULL: >= plan->n_chunks * H*F floats */
     int64_t scratch_bytes;
+    const float *bias;           /* optional [H*F], added before the activation */
+    int32_t x_shared_heads;      /* W_EDGE_HEAD only: a source row holds F floats that every head reads (the gradient
+                                    of a mean over heads) instead of H*F */
+    int32_t reserved;
 } yitu_spmm_args_t;
 
 int yitu_spmm_csr_f32(const yitu_spmm_args_t *args, yitu_stream_t stream);
@@ -173,6 +186,13 @@ int yitu_spmm_csr_f32(const yitu_spmm_args_t *args, yitu_stream_t stream);
  * Inputs, outputs and the hub plan are still the caller's. */
 int64_t yitu_static_scratch_bytes(void);
 int yitu_spmm_csr_f32_static(const yitu_spmm_args_t *args, yitu_stream_t stream);
+
+/* Backward of the fused epilogue y = act(row_scale[r] * agg + bias):
+ *   grad_agg[r,d] = grad_y[r,d] * act'(y[r,d]) * row_scale[r]     (row_scale NULL = 1)
+ * with act' taken from the OUTPUT y (ReLU: y > 0; ELU: y > 0 ? 1 : y + 1).  One pass; grad_agg may alias grad_y.
+ * The reference runs these as separate torch element-wise kernels around the aggregation. */
+int yitu_epilogue_grad_f32(int64_t n_rows, int64_t n_feats, int32_t activation, const float *y, const float *grad_y,
+                           const float *row_scale, float *grad_agg, yitu_stream_t stream);
 
 /* values[e] = 1 / (number of edges of e's row that carry e's segment id): with YITU_W_EDGE over a stitched
  * graph this turns the SpMM into "mean per relation, then sum over relations" in ONE pass and one output
@@ -215,19 +235,22 @@ typedef struct yitu_gat_args_t {
     yitu_csr_t graph;
     int64_t n_heads, n_feats;
     float slope;
-    int32_t reserved;
+    int32_t head_mean;  /* 1: out[r,k] = act(mean_h out[r,h,k]) — the layer's torch.mean(v, dim=1), model.py:106 */
     const float *query; /* [n_rows,H] */
     const float *key;   /* [n_cols,H] */
     const float *x;     /* [n_cols,H,F] */
-    float *out;         /* [n_rows,H,F] */
-    float *row_max;     /* [n_rows,H] softmax statistics kept for the backward pass */
+    float *out;         /* [n_rows,H,F], or [n_rows,F] with head_mean */
+    float *row_max;     /* [n_rows,H] softmax statistics */
     float *row_sum;     /* [n_rows,H] */
+    int32_t activation; /* YITU_ACT_* on out (forward only; the backward call expects the gradient with respect
+                           to the pre-activation values) */
+    int32_t reserved;
 } yitu_gat_args_t;
 int yitu_gat_fwd_f32(const yitu_gat_args_t *args, yitu_stream_t stream);
 
 typedef struct yitu_gat_bwd_args_t {
     yitu_gat_args_t fwd;       /* same tensors as the forward call (out, row_max, row_sum now inputs) */
-    const float *grad_out;     /* [n_rows,H,F] */
+    const float *grad_out;     /* [n_rows,H,F], or [n_rows,F] with fwd.head_mean */
     const void *t_indptr;      /* transposed graph from yitu_csr_transpose */
     const int32_t *t_rows;
     const int32_t *t_perm;

@@ -33,15 +33,29 @@ def test_library_exports_every_declared_symbol():
     assert L.yitu_static_scratch_bytes() == 16 << 20
 
 
-def test_struct_layouts_match_the_header():
-    """Sizes the C compiler gives the argument structs (LP64) — guards the ctypes mirrors."""
+def test_struct_layouts_match_the_header(tmp_path):
+    """Sizes and field offsets the C compiler gives the argument structs of the header, against the ctypes
+    mirrors: a moved or missing field in either place fails here."""
     import ctypes as C
+    import subprocess
     from yitu_b200 import _lib
-    assert C.sizeof(_lib.Csr) == 48
-    assert C.sizeof(_lib.HubPlan) == 32
-    assert C.sizeof(_lib.SpmmArgs) == 48 + 8 * 2 + 4 * 2 + 8 * 5 + 4 * 2 + 8 * 4 + 8 * 3
-    assert C.sizeof(_lib.GatArgs) == 48 + 16 + 8 + 48
-    assert C.sizeof(_lib.GatBwdArgs) == C.sizeof(_lib.GatArgs) + 9 * 8
+    mirrors = {"yitu_csr_t": _lib.Csr, "yitu_hub_plan_t": _lib.HubPlan, "yitu_spmm_args_t": _lib.SpmmArgs,
+               "yitu_gat_args_t": _lib.GatArgs, "yitu_gat_bwd_args_t": _lib.GatBwdArgs}
+    lines = []
+    for cname, cls in mirrors.items():
+        lines.append('printf("%s %%zu\\n", sizeof(%s));' % (cname, cname))
+        for fname, _ in cls._fields_:
+            lines.append('printf("%s.%s %%zu\\n", offsetof(%s, %s));' % (cname, fname, cname, fname))
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "yitu_b200.h"\nint main(void) {\n%s\nreturn 0; }\n'
+                   % "\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    got = dict(l.split() for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, cls in mirrors.items():
+        assert int(got[cname]) == C.sizeof(cls), cname
+        for fname, _ in cls._fields_:
+            assert int(got["%s.%s" % (cname, fname)]) == getattr(cls, fname).offset, (cname, fname)
 
 
 def test_build_part_bit_identical_to_reference():

@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libyitu_b200.so")
 
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_LIMIT = range(6)
 W_NONE, W_NODE, W_EDGE, W_EDGE_HEAD = range(4)
+ACT_NONE, ACT_RELU, ACT_ELU = range(3)
 
 c_i64, c_i32, c_f32, c_vp = C.c_int64, C.c_int32, C.c_float, C.c_void_p
 
@@ -28,14 +29,15 @@ class HubPlan(C.Structure):
 class SpmmArgs(C.Structure):
     _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("weight_mode", c_i32), ("accumulate", c_i32),
                 ("edge_values", c_vp), ("edge_perm", c_vp), ("norm_dst", c_vp), ("norm_src", c_vp),
-                ("row_scale", c_vp), ("alpha", c_f32), ("reserved", c_i32), ("x", c_vp), ("x_stride", c_i64),
+                ("row_scale", c_vp), ("alpha", c_f32), ("activation", c_i32), ("x", c_vp), ("x_stride", c_i64),
                 ("out", c_vp), ("out_stride", c_i64), ("plan", C.POINTER(HubPlan)), ("scratch", c_vp),
-                ("scratch_bytes", c_i64)]
+                ("scratch_bytes", c_i64), ("bias", c_vp), ("x_shared_heads", c_i32), ("reserved", c_i32)]
 
 
 class GatArgs(C.Structure):
-    _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("slope", c_f32), ("reserved", c_i32),
-                ("query", c_vp), ("key", c_vp), ("x", c_vp), ("out", c_vp), ("row_max", c_vp), ("row_sum", c_vp)]
+    _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("slope", c_f32), ("head_mean", c_i32),
+                ("query", c_vp), ("key", c_vp), ("x", c_vp), ("out", c_vp), ("row_max", c_vp), ("row_sum", c_vp),
+                ("activation", c_i32), ("reserved", c_i32)]
 
 
 class GatBwdArgs(C.Structure):
@@ -66,6 +68,7 @@ SYMBOLS = {
     "yitu_spmm_csr_f32": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
     "yitu_static_scratch_bytes": (c_i64, []),
     "yitu_spmm_csr_f32_static": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
+    "yitu_epilogue_grad_f32": (C.c_int, [c_i64, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "yitu_segment_mean_weights_f32": (C.c_int, [C.POINTER(Csr), c_vp, c_vp]),
     "yitu_edge_dot_f32": (C.c_int, [C.POINTER(Csr), c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "yitu_edge_softmax_fwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp]),

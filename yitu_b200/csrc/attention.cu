@@ -152,7 +152,7 @@ edge_gather_sum_kernel(int64_t n_cols, const void *t_indptr, int is64, const int
 // grad_a[e,h] = <g[row,h,:], x[col,h,:]>.  A group of LP = pow2 >= min(F,32) lanes owns one (edge, head) pair.
 __global__ void __launch_bounds__(256)
 edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices, int mask, int H, int F, int LP,
-                const float *g, const float *x, float *grad_a) {
+                const float *g, int g_shared, float g_scale, const float *x, float *grad_a) {
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (row >= n_rows) return;
     const int lane = threadIdx.x & 31;
@@ -162,7 +162,7 @@ edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices
     const int64_t eb = load_ptr(indptr, is64, row), ee = load_ptr(indptr, is64, row + 1);
     const int64_t D = static_cast<int64_t>(H) * F;
     const int64_t pairs = (ee - eb) * H;
-    const float *gr = g + row * D;
+    const float *gr = g + row * (g_shared ? F : D);  // g_shared: one F-wide gradient row serves every head
     for (int64_t pb = 0; pb < pairs; pb += G) {  // uniform trip count: every lane joins the shuffles
         const int64_t pi = pb + grp;
         float a = 0.0f;
@@ -174,11 +174,11 @@ edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices
             const int raw = __ldg(indices + e);
             const int col = mask ? (raw & mask) : raw;
             const float *xr = x + static_cast<int64_t>(col) * D + static_cast<int64_t>(h) * F;
-            const float *gh = gr + static_cast<int64_t>(h) * F;
+            const float *gh = g_shared ? gr : gr + static_cast<int64_t>(h) * F;
             for (int k = gl; k < F; k += LP) a = fmaf(__ldg(gh + k), __ldg(xr + k), a);
         }
         for (int o = LP >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (pi < pairs && gl == 0) grad_a[e * H + h] = a;
+        if (pi < pairs && gl == 0) grad_a[e * H + h] = a * g_scale;
     }
 }
 
@@ -188,7 +188,7 @@ edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices
 template <int NV>
 __global__ void __launch_bounds__(256)
 edge_dot_rows_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices, int mask, int H, int F,
-                     const float *g, const float *x, float *grad_a) {
+                     const float *g, int g_shared, float g_scale, const float *x, float *grad_a) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
@@ -207,7 +207,12 @@ edge_dot_rows_kernel(int64_t n_rows, const void *indptr, int is64, const int *in
         off[i] = static_cast<int64_t>(i * 32 + lane) * 4;
         valid[i] = off[i] < D;
         hd[i] = valid[i] ? static_cast<int>(off[i] / F) : 0;
-        gr[i] = valid[i] ? __ldg(reinterpret_cast<const float4 *>(g + row * D + off[i])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        gr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid[i]) {
+            const float *gp = g_shared ? g + row * F + (off[i] - static_cast<int64_t>(hd[i]) * F) : g + row * D + off[i];
+            gr[i] = __ldg(reinterpret_cast<const float4 *>(gp));
+            gr[i].x *= g_scale; gr[i].y *= g_scale; gr[i].z *= g_scale; gr[i].w *= g_scale;
+        }
     }
     const int64_t eb = load_ptr(indptr, is64, row), ee = load_ptr(indptr, is64, row + 1);
     for (int64_t e0 = eb; e0 < ee; e0 += 32) {
@@ -259,18 +264,19 @@ struct GatParams {
     float slope;
     const float *q, *k, *x;
     float *out, *row_max, *row_sum;
+    int head_mean, act, stage;  // stage = floats of per-warp staging for the head mean (H*F or 0)
 };
 
-__device__ __forceinline__ int warp_smem_floats_fwd(int H) { return 32 + 32 * H + 4 * 32; }
+__device__ __forceinline__ int warp_smem_floats_fwd(int H, int stage) { return 32 + 32 * H + 4 * 32 + stage; }
 
-template <int NV>
-__global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ GatParams p) {
+template <int NV, bool MEAN>
+__device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
     if (row >= p.n_rows) return;
     const int H = p.H;
-    float *base = smem + wib * warp_smem_floats_fwd(H);
+    float *base = smem + wib * warp_smem_floats_fwd(H, p.stage);
     int *s_col = reinterpret_cast<int *>(base);
     float *s_p = base + 32;
     float *s_scale = s_p + 32 * H;
@@ -373,14 +379,48 @@ __global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ Ga
         p.row_sum[row * H + lane] = l_run;
     }
     __syncwarp();
+    if constexpr (MEAN) {
+        // the layer's mean over heads: stage the H*F results, then lane f adds the H values of feature f in head
+        // order (fixed order: deterministic) — the [n_rows,H,F] tensor is never written
+        float *s_o = s_l + 32;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (!valid[i]) continue;
+            const float l = s_l[hd[i]];
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            *reinterpret_cast<float4 *>(s_o + off[i]) =
+                make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+        }
+        __syncwarp();
+        const float inv_h = 1.0f / static_cast<float>(H);
+        for (int f = lane; f < p.F; f += 32) {
+            float a = 0.0f;
+            for (int h = 0; h < H; ++h) a += s_o[h * p.F + f];
+            p.out[row * p.F + f] = activate(a * inv_h, p.act);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         if (!valid[i]) continue;
         const float l = s_l[hd[i]];
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         *reinterpret_cast<float4 *>(p.out + row * D + off[i]) =
-            make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+            make_float4(activate(acc[i][0] * inv, p.act), activate(acc[i][1] * inv, p.act),
+                        activate(acc[i][2] * inv, p.act), activate(acc[i][3] * inv, p.act));
     }
+}
+
+template <int NV, bool MEAN>
+__global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ GatParams p) {
+    gat_fwd_body<NV, MEAN>(p);
+}
+
+// The same body held to 64 registers (four 256-thread CTAs per SM).  Left to itself the compiler settles on 48
+// registers for the two-slice head-mean variant and serialises the gathers: 7.2 ms against 6.5 ms on the 8x32 layer.
+template <int NV, bool MEAN>
+__global__ void __launch_bounds__(256, 4) gat_fwd_kernel_r64(const __grid_constant__ GatParams p) {
+    gat_fwd_body<NV, MEAN>(p);
 }
 
 static int head_block(int64_t H) {
@@ -448,8 +488,10 @@ extern "C" int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, in
     return YITU_OK;
 }
 
-extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out,
-                                 const float *x, float *grad_a, yitu_stream_t stream) {
+// grad_shared: grad_out is [n_rows,F] and stands for every head (scaled by grad_scale) — the gradient of a mean
+// over heads.
+static int edge_dot_impl(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out, int grad_shared,
+                         float grad_scale, const float *x, float *grad_a, yitu_stream_t stream) {
     if (int rc = validate_csr(g)) return rc;
     YITU_REQUIRE(n_heads >= 1 && n_feats >= 1, YITU_ERR_INVALID_ARG, "bad shape");
     if (g->n_rows == 0 || g->nnz == 0) return YITU_OK;
@@ -466,7 +508,7 @@ extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n
             if (smem > 48 * 1024)
                 YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             kernel<<<blocks, 256, smem, st>>>(g->n_rows, g->indptr, g->indptr_is64, g->indices, g->index_mask, H, F,
-                                              grad_out, x, grad_a);
+                                              grad_out, grad_shared, grad_scale, x, grad_a);
             YITU_LAUNCH_CHECK();
             return YITU_OK;
         };
@@ -476,9 +518,14 @@ extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n
     }
     edge_dot_kernel<<<blocks, 256, 0, st>>>(g->n_rows, g->indptr, g->indptr_is64, g->indices, g->index_mask,
                                             static_cast<int>(n_heads), static_cast<int>(n_feats), head_block(n_feats),
-                                            grad_out, x, grad_a);
+                                            grad_out, grad_shared, grad_scale, x, grad_a);
     YITU_LAUNCH_CHECK();
     return YITU_OK;
+}
+
+extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out,
+                                 const float *x, float *grad_a, yitu_stream_t stream) {
+    return edge_dot_impl(g, n_heads, n_feats, grad_out, 0, 1.0f, x, grad_a, stream);
 }
 
 static int check_gat(const yitu_gat_args_t *a, bool backward) {
@@ -490,6 +537,8 @@ static int check_gat(const yitu_gat_args_t *a, bool backward) {
     YITU_REQUIRE(H <= 32 && F % 4 == 0 && H * F <= 512, YITU_ERR_UNSUPPORTED,
                  "fused GAT needs H <= 32, F %% 4 == 0, H*F <= 512 (H=%lld F=%lld)", (long long)H, (long long)F);
     (void)backward;
+    YITU_REQUIRE(a->activation >= YITU_ACT_NONE && a->activation <= YITU_ACT_ELU, YITU_ERR_INVALID_ARG,
+                 "unknown activation %d", a->activation);
     YITU_REQUIRE(a->graph.n_rows == 0 || (a->query && a->out && a->row_max && a->row_sum), YITU_ERR_INVALID_ARG,
                  "NULL tensor");
     YITU_REQUIRE(a->graph.nnz == 0 || (a->key && a->x), YITU_ERR_INVALID_ARG, "NULL tensor");
@@ -503,6 +552,8 @@ static void fill_gat(GatParams &p, const yitu_gat_args_t *a) {
     p.hshift = (p.H & (p.H - 1)) == 0 ? 31 - __builtin_clz(p.H) : -1;
     p.slope = a->slope; p.q = a->query; p.k = a->key; p.x = a->x;
     p.out = a->out; p.row_max = a->row_max; p.row_sum = a->row_sum;
+    p.head_mean = a->head_mean ? 1 : 0; p.act = a->activation;
+    p.stage = p.head_mean ? p.H * p.F : 0;
 }
 
 template <typename K>
@@ -523,10 +574,15 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     fill_gat(p, a);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int64_t D = a->n_heads * a->n_feats;
-    const int sm = 32 + 32 * p.H + 4 * 32;
-    if (D <= 128) return launch_rows(gat_fwd_kernel<1>, p, sm, st);
-    if (D <= 256) return launch_rows(gat_fwd_kernel<2>, p, sm, st);
-    return launch_rows(gat_fwd_kernel<4>, p, sm, st);
+    const int sm = 32 + 32 * p.H + 4 * 32 + p.stage;
+    if (p.head_mean) {
+        if (D <= 128) return launch_rows(gat_fwd_kernel<1, true>, p, sm, st);
+        if (D <= 256) return launch_rows(gat_fwd_kernel_r64<2, true>, p, sm, st);
+        return launch_rows(gat_fwd_kernel<4, true>, p, sm, st);
+    }
+    if (D <= 128) return launch_rows(gat_fwd_kernel<1, false>, p, sm, st);
+    if (D <= 256) return launch_rows(gat_fwd_kernel_r64<2, false>, p, sm, st);
+    return launch_rows(gat_fwd_kernel<4, false>, p, sm, st);
 }
 
 extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
@@ -549,7 +605,10 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     //   d attn[e,h] = <grad_out[row,h,:], x[col,h,:]>         -> edge_grad
     //   softmax + LeakyReLU derivatives in place              -> edge_grad = d score, grad_query
     if (int rc = yitu_edge_softmax_fwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, stream)) return rc;
-    if (int rc = yitu_edge_dot_f32(&g, H, F, b->grad_out, a->x, b->edge_grad, stream)) return rc;
+    // with head_mean the upstream gradient is [n_rows,F]: every head sees grad_out[r,:] / H
+    const int shared = a->head_mean ? 1 : 0;
+    const float gscale = shared ? 1.0f / static_cast<float>(H) : 1.0f;
+    if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream)) return rc;
     if (int rc = yitu_edge_softmax_bwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, b->edge_grad,
                                            b->grad_query, b->edge_grad, stream))
         return rc;
@@ -559,8 +618,8 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     s.graph.indptr = b->t_indptr; s.graph.indptr_is64 = g.indptr_is64; s.graph.index_mask = 0;
     s.graph.indices = b->t_rows;
     s.n_heads = H; s.n_feats = F; s.weight_mode = YITU_W_EDGE_HEAD;
-    s.edge_values = b->edge_attn; s.edge_perm = b->t_perm; s.alpha = 1.0f;
-    s.x = b->grad_out; s.x_stride = D; s.out = b->grad_x; s.out_stride = D;
+    s.edge_values = b->edge_attn; s.edge_perm = b->t_perm; s.alpha = gscale;
+    s.x = b->grad_out; s.x_stride = shared ? F : D; s.x_shared_heads = shared; s.out = b->grad_x; s.out_stride = D;
     if (int rc = yitu_spmm_csr_f32(&s, stream)) return rc;
     return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
                                     stream);

@@ -47,6 +47,12 @@ __device__ __forceinline__ float leaky_relu(float v, float slope) {
     return fmaxf(0.0f, v) + slope * fminf(0.0f, v);
 }
 
+__device__ __forceinline__ float activate(float v, int act) {
+    if (act == YITU_ACT_RELU) return fmaxf(v, 0.0f);
+    if (act == YITU_ACT_ELU) return v > 0.0f ? v : expm1f(v);
+    return v;
+}
+
 // Loads of data that is streamed once (indices, edge values): kept out of L1, and marked evict-first in L2 through
 // a cache-hint policy, so that they do not push the gathered feature rows out of the 126 MB L2.
 __device__ __forceinline__ uint64_t stream_policy() {

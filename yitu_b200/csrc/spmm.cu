@@ -1,4 +1,4 @@
-// CSR pull SpMM for sm_100a:  out[r,:] = alpha*row_scale[r] * sum_{e in row r} w(e) * x[col_e,:]
+// CSR pull SpMM for sm_100a:  out[r,:] = act(alpha*row_scale[r] * sum_{e in row r} w(e) * x[col_e,:] + bias)
 //
 // Work decomposition
 //   * a group of LPR lanes (4..32, one warp for rows of >= 128 floats) owns one destination row, or one
@@ -42,7 +42,22 @@ struct SpmmParams {
     const int *chunk_row;
     const int64_t *chunk_begin;
     float *scratch;
+    const float *bias;
+    int act, xshared;
 };
+
+// Last step of every output row: bias, then activation (both optional).
+template <int VEC>
+__device__ __forceinline__ void finish_vec(float (&r)[VEC], const SpmmParams &p, int64_t d) {
+    if (p.bias) {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) r[q] += __ldg(p.bias + d + q);
+    }
+    if (p.act) {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) r[q] = activate(r[q], p.act);
+    }
+}
 
 template <int VEC>
 __device__ __forceinline__ void load_vec(float (&r)[VEC], const float *p) {
@@ -104,11 +119,13 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
     int64_t off[NV];
     bool valid[NV];
     int hd[NV];
+    int64_t xo[NV];  // offset of the lane's slice inside a source row (differs from off[] when heads share x)
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         off[i] = d0 + static_cast<int64_t>(i * LPR + l) * VEC;
         valid[i] = off[i] < p.D;
         hd[i] = PER_HEAD ? static_cast<int>(off[i] / p.F) : 0;
+        xo[i] = (PER_HEAD && p.xshared) ? off[i] - static_cast<int64_t>(hd[i]) * p.F : off[i];
     }
 
     float acc[NV][VEC];
@@ -171,8 +188,8 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     if (valid[i]) {
-                        if constexpr (IDX32) load_vec<VEC>(v[u][i], p.x + (xr32 + static_cast<uint32_t>(off[i])));
-                        else load_vec<VEC>(v[u][i], xr + off[i]);
+                        if constexpr (IDX32) load_vec<VEC>(v[u][i], p.x + (xr32 + static_cast<uint32_t>(xo[i])));
+                        else load_vec<VEC>(v[u][i], xr + xo[i]);
                         if constexpr (PER_HEAD)
                             wh[u][i] = (j + u < n) ? __ldg(p.values + static_cast<int64_t>(vi[u]) * p.H + hd[i]) : 0.0f;
                     } else {
@@ -211,6 +228,7 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
 #pragma unroll
                 for (int q = 0; q < VEC; ++q) r[q] = s * acc[i][q];
             }
+            finish_vec<VEC>(r, p, off[i]);
             store_vec<VEC>(dst + off[i], r);
         }
     }
@@ -320,6 +338,7 @@ __global__ void __launch_bounds__(256) spmm_wide_kernel(const __grid_constant__ 
 #pragma unroll
             for (int q = 0; q < 8; ++q) r[q] = s * acc[q];
         }
+        finish_vec<8>(r, p, off);
         store_vec<8>(dst + off, r);
     }
 }
@@ -337,7 +356,9 @@ __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__
         float a = 0.0f;
         for (int64_t k = 0; k < nch; ++k) a += p.scratch[(chunk + k) * p.D + d];
         float *o = p.out + row * p.os + d;
-        *o = p.accumulate ? fmaf(s, a, *o) : s * a;
+        float r = p.accumulate ? fmaf(s, a, *o) : s * a;
+        if (p.bias) r += __ldg(p.bias + d);
+        *o = activate(r, p.act);
     }
 }
 
@@ -401,9 +422,14 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     YITU_REQUIRE(a->n_heads >= 1 && a->n_feats >= 1, YITU_ERR_INVALID_ARG, "n_heads=%lld n_feats=%lld",
                  (long long)a->n_heads, (long long)a->n_feats);
     const int64_t D = a->n_heads * a->n_feats;
-    YITU_REQUIRE(a->x_stride >= D && a->out_stride >= D, YITU_ERR_INVALID_ARG,
-                 "row strides (%lld, %lld) smaller than H*F=%lld", (long long)a->x_stride,
-                 (long long)a->out_stride, (long long)D);
+    YITU_REQUIRE(a->x_shared_heads == 0 || a->weight_mode == YITU_W_EDGE_HEAD, YITU_ERR_INVALID_ARG,
+                 "x_shared_heads needs per-head edge values (YITU_W_EDGE_HEAD)");
+    const int64_t x_width = a->x_shared_heads ? a->n_feats : D;
+    YITU_REQUIRE(a->x_stride >= x_width && a->out_stride >= D, YITU_ERR_INVALID_ARG,
+                 "row strides (%lld, %lld) smaller than the rows (%lld, %lld)", (long long)a->x_stride,
+                 (long long)a->out_stride, (long long)x_width, (long long)D);
+    YITU_REQUIRE(a->activation >= YITU_ACT_NONE && a->activation <= YITU_ACT_ELU, YITU_ERR_INVALID_ARG,
+                 "unknown activation %d", a->activation);
     YITU_REQUIRE(g.n_rows == 0 || a->out != nullptr, YITU_ERR_INVALID_ARG, "out is NULL");
     YITU_REQUIRE(g.nnz == 0 || a->x != nullptr, YITU_ERR_INVALID_ARG, "x is NULL");
     YITU_REQUIRE(a->weight_mode >= YITU_W_NONE && a->weight_mode <= YITU_W_EDGE_HEAD, YITU_ERR_INVALID_ARG,
@@ -423,6 +449,7 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     p.values = a->edge_values; p.perm = a->edge_perm;
     p.norm_dst = a->norm_dst; p.norm_src = a->norm_src; p.row_scale = a->row_scale; p.alpha = a->alpha;
     p.x = a->x; p.xs = a->x_stride; p.out = a->out; p.os = a->out_stride;
+    p.bias = a->bias; p.act = a->activation; p.xshared = a->x_shared_heads ? 1 : 0;
     if (a->plan && a->plan->n_chunks > 0) {
         YITU_REQUIRE(a->plan->chunk_edges >= 32, YITU_ERR_INVALID_ARG, "plan.chunk_edges must be >= 32");
         YITU_REQUIRE(a->plan->chunk_row && a->plan->chunk_begin, YITU_ERR_INVALID_ARG, "plan tables are NULL");

@@ -128,22 +128,24 @@ def gat_supported(indptr, indices, n_heads, n_feats):
     return n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
-def gat_forward(indptr, indices, query, key, features):
+def gat_forward(indptr, indices, query, key, features, head_mean=False, activation=None):
     """[out [n_dst,H,F], row_max [n_dst,H], row_sum [n_dst,H]]: sddmm_forward + spmm_forward in one pass, for an
-    unstitched graph (every segment id 0).  query [n_dst,H], key [n_src,H], features [n_src,H,F]."""
+    unstitched graph (every segment id 0).  query [n_dst,H], key [n_src,H], features [n_src,H,F].
+    head_mean / activation fuse the layer's mean over heads (out [n_dst,F]) and the model's ReLU / ELU."""
     ops.require_cuda(indptr, "indptr", _I32)
     ops.require_cuda(indices, "indices", _I32)
     for t, n in ((query, "query"), (key, "key"), (features, "features")):
         ops.require_cuda(t, n, _F32)
     _need(query.dim() == 2 and key.dim() == 2 and features.dim() == 3, "gat_forward: bad ranks")
     g = ops.prepared(indptr, indices, features.size(0), 0)
-    return list(ops.gat_fwd(g, query, key, features, SLOPE))
+    return list(ops.gat_fwd(g, query, key, features, SLOPE, head_mean, activation))
 
 
-def gat_backward(indptr, indices, query, key, features, out, row_max, row_sum, grad_out):
-    """[grad_query, grad_key, grad_features] of gat_forward."""
+def gat_backward(indptr, indices, query, key, features, out, row_max, row_sum, grad_out, head_mean=False):
+    """[grad_query, grad_key, grad_features] of gat_forward; grad_out is taken with respect to the values before
+    the activation."""
     for t, n in ((query, "query"), (key, "key"), (features, "features"), (out, "out"), (row_max, "row_max"),
                  (row_sum, "row_sum"), (grad_out, "grad_out")):
         ops.require_cuda(t, n, _F32)
     g = ops.prepared(indptr, indices, features.size(0), 0)
-    return list(ops.gat_bwd(g, query, key, features, out, row_max, row_sum, grad_out, SLOPE))
+    return list(ops.gat_bwd(g, query, key, features, out, row_max, row_sum, grad_out, SLOPE, head_mean))

@@ -19,50 +19,82 @@ def _block_of(graph):
 
 
 class _AggregateFunction(autograd.Function):
-    """y = A x with fixed per-edge weights (or none): forward SpMM, backward the transposed SpMM."""
+    """y = act(row_scale * (A x) + bias) with fixed per-edge weights (or none): one SpMM with a fused epilogue
+    forward; backward one element-wise pass (activation derivative and row scale) and the transposed SpMM."""
 
     @staticmethod
-    def forward(ctx, x, graph, weights):
-        ctx.graph, ctx.weights = graph, weights
+    def forward(ctx, x, graph, weights, row_scale=None, bias=None, activation=None):
+        ctx.graph, ctx.weights, ctx.row_scale, ctx.activation = graph, weights, row_scale, activation
+        ctx.has_bias = bias is not None
         mode = ops.W_NONE if weights is None else ops.W_EDGE
-        return ops.spmm(graph, x.contiguous(), mode=mode, edge_values=weights)
+        y = ops.spmm(graph, x.contiguous(), mode=mode, edge_values=weights, row_scale=row_scale,
+                     bias=None if bias is None else bias.detach().contiguous(), activation=activation)
+        if activation is not None:
+            ctx.save_for_backward(y)
+        return y
 
     @staticmethod
     def backward(ctx, grad_out):
         g, w = ctx.graph, ctx.weights
+        grad_out = grad_out.contiguous()
+        if ctx.activation is not None or ctx.row_scale is not None:
+            y = ctx.saved_tensors[0] if ctx.activation is not None else None
+            grad_bias = None
+            if ctx.has_bias:  # the bias sits inside the row scale's reach only through the activation
+                grad_pre = ops.epilogue_grad(y, grad_out, None, ctx.activation) if y is not None else grad_out
+                grad_bias = grad_pre.reshape(-1, grad_pre.size(-1)).sum(0)
+                grad_agg = ops.epilogue_grad(None, grad_pre, ctx.row_scale, None) if ctx.row_scale is not None else grad_pre
+            else:
+                grad_agg = ops.epilogue_grad(y, grad_out, ctx.row_scale, ctx.activation)
+        else:
+            grad_agg = grad_out
+            grad_bias = grad_out.reshape(-1, grad_out.size(-1)).sum(0) if ctx.has_bias else None
         gt = g.t_prepared()
         if w is None:
-            return ops.spmm(gt, grad_out.contiguous(), mode=ops.W_NONE), None, None
-        return ops.spmm(gt, grad_out.contiguous(), mode=ops.W_EDGE, edge_values=w, edge_perm=g.transpose()[2]), None, None
+            grad_x = ops.spmm(gt, grad_agg, mode=ops.W_NONE)
+        else:
+            grad_x = ops.spmm(gt, grad_agg, mode=ops.W_EDGE, edge_values=w, edge_perm=g.transpose()[2])
+        return grad_x, None, None, None, grad_bias, None
 
 
-def aggregate(block, x, weights=None, index_mask=0):
-    """Differentiable sum (or fixed-weight sum) of source rows per destination row; x is [n_src, D]."""
+def aggregate(block, x, weights=None, index_mask=0, row_scale=None, bias=None, activation=None):
+    """Differentiable sum (or fixed-weight sum) of source rows per destination row; x is [n_src, D].  row_scale
+    [n_dst], bias [D] and activation (None / "relu" / "elu") are applied in the kernel's epilogue:
+    act(row_scale * sum + bias)."""
     g = ops.prepared(block.adj_sparse[0], block.adj_sparse[1], x.size(0), index_mask)
-    return _AggregateFunction.apply(x, g, weights)
+    return _AggregateFunction.apply(x, g, weights, row_scale, bias, activation)
 
 
 class GCNLayer(nn.Module):
-    """norm * (A (x W^T + b)) — model.py:7-30; `norm` is the per-destination 1/in_degree column (mp.py:165-167)."""
+    """norm * (A (x W^T + b)) — model.py:7-30; `norm` is the per-destination 1/in_degree column (mp.py:165-167).
+    The multiplication by norm runs in the aggregation kernel's epilogue, and so does `activation` (the ReLU the
+    reference's GCNModel applies between layers, model.py:46-49) when one is given."""
 
-    def __init__(self, in_features: int, out_features: int):
+    def __init__(self, in_features: int, out_features: int, activation: str = None):
         nn.Module.__init__(self)
         self.fc = nn.Linear(in_features, out_features)
+        self.activation = activation
 
     def forward(self, graph, norm, x):
         if isinstance(x, (list, tuple)):
             assert len(x) == 2
             x = x[0]
-        h = aggregate(_block_of(graph), self.fc(x))
-        return torch.multiply(norm, h)
+        blk = _block_of(graph)
+        h = self.fc(x)
+        n_dst = blk.adj_sparse[0].numel() - 1
+        if norm.numel() == n_dst and norm.dtype == torch.float32 and not norm.requires_grad:
+            return aggregate(blk, h, row_scale=norm.reshape(-1).contiguous(), activation=self.activation)
+        out = torch.multiply(norm, aggregate(blk, h))
+        return sparse._TORCH_ACT[self.activation](out)
 
 
 class GATLayer(nn.Module):
-    """mean over heads of softmax-weighted aggregation — model.py:61-106."""
+    """mean over heads of softmax-weighted aggregation — model.py:61-106; `activation` fuses the ELU the
+    reference's GATModel applies between layers (model.py:126-129)."""
 
-    def __init__(self, in_features: int, out_features: int, n_heads: int):
+    def __init__(self, in_features: int, out_features: int, n_heads: int, activation: str = None):
         nn.Module.__init__(self)
-        self.n_heads, self.n_features = n_heads, out_features
+        self.n_heads, self.n_features, self.activation = n_heads, out_features, activation
         self.linear_q = nn.Linear(n_heads * out_features, n_heads)
         self.linear_k = nn.Linear(n_heads * out_features, n_heads)
         self.linear_v = nn.Linear(in_features, n_heads * out_features)
@@ -78,8 +110,8 @@ class GATLayer(nn.Module):
         q = self.linear_q(h_dst)
         k = self.linear_k(h_src)
         h_src = h_src.view(-1, self.n_heads, self.n_features)
-        out = sparse.fused_gat(_block_of(graph), q, k, h_src)
-        return torch.mean(out, dim=1)
+        # mean over heads (and the optional activation) inside the aggregation kernel
+        return sparse.fused_gat(_block_of(graph), q, k, h_src, head_mean=True, activation=self.activation)
 
 
 class HeteroGraphConv(nn.Module):

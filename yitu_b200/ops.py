@@ -8,10 +8,21 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import Csr, GatArgs, GatBwdArgs, HubPlan, SpmmArgs, W_EDGE, W_EDGE_HEAD, W_NODE, W_NONE, check, lib
+from ._lib import (ACT_ELU, ACT_NONE, ACT_RELU, Csr, GatArgs, GatBwdArgs, HubPlan, SpmmArgs, W_EDGE, W_EDGE_HEAD,
+                   W_NODE, W_NONE, check, lib)
 
 DEFAULT_CHUNK_EDGES = 512
 STITCH_MASK = 0xFFFFFF
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "relu": ACT_RELU, "elu": ACT_ELU}
+
+
+def activation_code(activation):
+    if isinstance(activation, int):
+        return activation
+    try:
+        return ACTIVATIONS[activation]
+    except KeyError:
+        raise RuntimeError("activation must be None, 'relu' or 'elu', got %r" % (activation,))
 
 
 def _ptr(t):
@@ -136,20 +147,27 @@ def prepared(indptr, indices, n_cols, index_mask=0):
 
 
 def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, norm_dst=None, norm_src=None,
-         row_scale=None, alpha=1.0, out=None, accumulate=False, chunk_edges=DEFAULT_CHUNK_EDGES):
-    """out[r,h,k] = alpha*row_scale[r] * sum_e w(e,h) * x[col_e,h,k] through yitu_spmm_csr_f32.
+         row_scale=None, alpha=1.0, out=None, accumulate=False, chunk_edges=DEFAULT_CHUNK_EDGES, bias=None,
+         activation=None, x_shared_heads=False):
+    """out[r,h,k] = act(alpha*row_scale[r] * sum_e w(e,h) * x[col_e,h,k] + bias[h,k]) through yitu_spmm_csr_f32.
 
-    x: [n_cols, H*F] or [n_cols, H, F] float32 CUDA; returns a tensor shaped like x with n_rows rows."""
+    x: [n_cols, H*F] or [n_cols, H, F] float32 CUDA; returns a tensor shaped like x with n_rows rows.
+    x_shared_heads (per-head edge values only): x is [n_cols, F] and every head reads the same row; the result is
+    [n_rows, H, F]."""
     if x.dtype != torch.float32:
         raise RuntimeError("features must be float32, got %s" % x.dtype)
     if x.size(0) != graph.n_cols:
         raise RuntimeError("features have %d rows, the graph has %d source nodes" % (x.size(0), graph.n_cols))
     x2 = x.reshape(x.size(0), -1)
-    D = x2.size(1)
+    x_width = x2.size(1)
+    D = x_width * n_heads if x_shared_heads else x_width
     if D % n_heads:
         raise RuntimeError("feature width %d is not a multiple of n_heads=%d" % (D, n_heads))
+    if bias is not None and (bias.numel() != D or bias.dtype != torch.float32 or not bias.is_contiguous()):
+        raise RuntimeError("bias must be a contiguous float32 tensor of %d values" % D)
     if out is None:
-        out = torch.empty((graph.n_rows,) + tuple(x.shape[1:]), dtype=torch.float32, device=x.device)
+        shape = (graph.n_rows, n_heads, x_width) if x_shared_heads else (graph.n_rows,) + tuple(x.shape[1:])
+        out = torch.empty(shape, dtype=torch.float32, device=x.device)
         accumulate = False
     a = SpmmArgs()
     a.graph = graph.csr
@@ -158,7 +176,9 @@ def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, 
     a.edge_values, a.edge_perm = _ptr(edge_values), _ptr(edge_perm)
     a.norm_dst, a.norm_src, a.row_scale = _ptr(norm_dst), _ptr(norm_src), _ptr(row_scale)
     a.alpha = float(alpha)
-    a.x, a.x_stride = _ptr(x2), D
+    a.activation = activation_code(activation)
+    a.bias, a.x_shared_heads = _ptr(bias), int(bool(x_shared_heads))
+    a.x, a.x_stride = _ptr(x2), x_width
     a.out, a.out_stride = _ptr(out), D
     keep = None
     if chunk_edges:
@@ -171,6 +191,19 @@ def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, 
     with torch.cuda.device(x.device):
         check(lib().yitu_spmm_csr_f32(C.byref(a), _stream(x.device)))
     del keep
+    return out
+
+
+def epilogue_grad(y, grad_y, row_scale=None, activation=None):
+    """grad_y * act'(y) * row_scale[r] in one pass (yitu_epilogue_grad_f32); y, grad_y are [n_rows, ...] float32."""
+    n_rows = grad_y.size(0)
+    width = grad_y.numel() // max(n_rows, 1)
+    grad_y = grad_y.contiguous()
+    out = torch.empty_like(grad_y)
+    code = activation_code(activation)
+    with torch.cuda.device(grad_y.device):
+        check(lib().yitu_epilogue_grad_f32(n_rows, max(width, 1), code, _ptr(y) if code else None, _ptr(grad_y),
+                                           _ptr(row_scale), _ptr(out), _stream(grad_y.device)))
     return out
 
 
@@ -211,10 +244,11 @@ def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2):
     return grad_q, grad_k
 
 
-def _gat_args(graph, query, key, x, out, row_max, row_sum, slope):
+def _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean=False, activation=None):
     a = GatArgs()
     a.graph = graph.csr
     a.n_heads, a.n_feats, a.slope = x.size(1), x.size(2), slope
+    a.head_mean, a.activation = int(bool(head_mean)), activation_code(activation)
     a.query, a.key, a.x = _ptr(query), _ptr(key), _ptr(x)
     a.out, a.row_max, a.row_sum = _ptr(out), _ptr(row_max), _ptr(row_sum)
     return a
@@ -224,24 +258,30 @@ def gat_fused_supported(graph, n_heads, n_feats, backward=True):
     return graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
-def gat_fwd(graph, query, key, x, slope=0.2):
-    """Fused scores + edge softmax + aggregation: (out [n_rows,H,F], row_max [n_rows,H], row_sum [n_rows,H])."""
+def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None):
+    """Fused scores + edge softmax + aggregation: (out [n_rows,H,F], row_max [n_rows,H], row_sum [n_rows,H]).
+    head_mean: out is act(mean over heads), [n_rows,F], and the per-head tensor is never written."""
     H, F = x.size(1), x.size(2)
-    out = torch.empty((graph.n_rows, H, F), dtype=torch.float32, device=x.device)
+    shape = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
+    out = torch.empty(shape, dtype=torch.float32, device=x.device)
     row_max = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
     row_sum = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
-    a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope)
+    a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, activation)
     with torch.cuda.device(x.device):
         check(lib().yitu_gat_fwd_f32(C.byref(a), _stream(x.device)))
     return out, row_max, row_sum
 
 
-def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2):
-    """(grad_query, grad_key, grad_x) of gat_fwd."""
+def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, head_mean=False):
+    """(grad_query, grad_key, grad_x) of gat_fwd; grad_out is the gradient of the pre-activation output
+    ([n_rows,F] with head_mean)."""
     H = x.size(1)
+    expect = (graph.n_rows, x.size(2)) if head_mean else (graph.n_rows, H, x.size(2))
+    if tuple(grad_out.shape) != expect or not grad_out.is_contiguous():
+        raise RuntimeError("grad_out must be contiguous with shape %s, got %s" % (expect, tuple(grad_out.shape)))
     t_indptr, t_rows, t_perm = graph.transpose()
     b = GatBwdArgs()
-    b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope)
+    b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean)
     grad_q = torch.empty_like(query)
     grad_k = torch.empty_like(key)
     grad_x = torch.empty_like(x)

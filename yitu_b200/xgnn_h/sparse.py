@@ -94,28 +94,45 @@ def hfused_spddmm(spmm_block: block.Block, spmm_values, spmm_x, sddmm_block: blo
 
 
 class FusedGATFunction(autograd.Function):
-    """gspmm(fused_gsddmm(q, k), x) as one kernel per direction; no [E,H] attention tensor is kept."""
+    """gspmm(fused_gsddmm(q, k), x) as one kernel per direction; no [E,H] attention tensor is kept.  With
+    head_mean the layer's mean over heads (and an optional ReLU / ELU) is part of the same kernel, and the backward
+    kernels read the [n_dst,F] gradient directly."""
 
     @staticmethod
-    def forward(ctx, adj_sparse, query, key, x):
-        out, row_max, row_sum = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x)
-        ctx.adj_sparse = adj_sparse
+    def forward(ctx, adj_sparse, query, key, x, head_mean=False, activation=None):
+        out, row_max, row_sum = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x, head_mean,
+                                                      activation)
+        ctx.adj_sparse, ctx.head_mean, ctx.activation = adj_sparse, head_mean, activation
         ctx.save_for_backward(query, key, x, out, row_max, row_sum)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         query, key, x, out, row_max, row_sum = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        if ctx.activation is not None:
+            grad_out = ops.epilogue_grad(out, grad_out, None, ctx.activation)
         gq, gk, gx = graph_ext.gat_backward(ctx.adj_sparse[0], ctx.adj_sparse[1], query, key, x, out, row_max,
-                                            row_sum, grad_out.contiguous())
-        return None, gq, gk, gx
+                                            row_sum, grad_out, ctx.head_mean)
+        return None, gq, gk, gx, None, None
 
 
-def fused_gat(block: block.Block, query: torch.Tensor, key: torch.Tensor, x: torch.Tensor):
+_TORCH_ACT = {None: lambda t: t, "relu": torch.relu, "elu": torch.nn.functional.elu}
+
+
+def fused_gat(block: block.Block, query: torch.Tensor, key: torch.Tensor, x: torch.Tensor, head_mean: bool = False,
+              activation: str = None):
     """Attention + aggregation of a GAT layer (YiTu_GNN/YiTu_H/test/common/model.py:96-105) for an unstitched
-    block: query [n_dst,H], key [n_src,H], x [n_src,H,F] -> [n_dst,H,F].  Shapes the fused kernels do not
-    cover take the two-operator route."""
+    block: query [n_dst,H], key [n_src,H], x [n_src,H,F] -> [n_dst,H,F]; with head_mean the layer's
+    torch.mean(dim=1) (model.py:106) and the model's activation (model.py:126-129) are fused: -> [n_dst,F].
+    Shapes the fused kernels do not cover take the two-operator route."""
     assert x.dim() == 3 and query.dim() == 2
+    if activation not in _TORCH_ACT:
+        raise RuntimeError("activation must be None, 'relu' or 'elu', got %r" % (activation,))
     if graph_ext.gat_supported(block.adj_sparse[0], block.adj_sparse[1], x.size(1), x.size(2)):
-        return FusedGATFunction.apply(block.adj_sparse, query.contiguous(), key.contiguous(), x.contiguous())
-    return gspmm(block, fused_gsddmm(block, query, key), x)
+        return FusedGATFunction.apply(block.adj_sparse, query.contiguous(), key.contiguous(), x.contiguous(),
+                                      head_mean, activation)
+    out = gspmm(block, fused_gsddmm(block, query, key), x)
+    if head_mean:
+        out = torch.mean(out, dim=1)
+    return _TORCH_ACT[activation](out)
