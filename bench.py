@@ -534,6 +534,65 @@ def run_layer_fusion(args):
     print(json.dumps(out))
 
 
+def run_reorder(args):
+    """Locality reordering (yitu_b200.rabbit) measured by what it is for: the D=256 aggregation before and after the
+    renumbering, on a graph with planted communities behind shuffled ids and on the R-MAT benchmark graph, plus the
+    time of the reordering itself.  Prints one JSON line; not the headline benchmark."""
+    import torch
+    from yitu_b200 import graphs, ops, rabbit
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    reps = max(3, args.steps)
+    n, e, d = (1 << 21) >> args.scale, (1 << 26) >> args.scale, 256
+
+    def timed(fn, reps=reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    def spmm_ms(ei):
+        ip, ix = ops.coo_to_csr(ei[0].contiguous(), ei[1].contiguous(), n, n, self_loops=True)
+        g = ops.PreparedGraph(ip, ix, n)
+        g.plan()
+        x = graphs.randn_features(1, n, d, device=dev)
+        ms = timed(lambda: ops.spmm(g, x))
+        return ms, ix.numel()
+
+    out = {"workload": "locality_reordering", "n": n, "d": d, "unit": "ms", "rows": []}
+    cases = (("planted communities of 1024 nodes, 90% of edges inside, ids shuffled",
+              lambda: graphs.planted_community_edges(7, n, 1024, e, 0.9, device=dev)),
+             ("R-MAT (0.57,0.19,0.19,0.05)", lambda: graphs.rmat_edges(1, n, n, e, device=dev)))
+    for name, make in cases:
+        src, dst = make()
+        ei = torch.stack([src, dst]).to(torch.int32)
+        del src, dst
+        before_ms, nnz = spmm_ms(ei)
+        span_before = rabbit.avg_edge_span(ei)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        new_id, levels, top = rabbit.reorder_ids(ei, n)
+        torch.cuda.synchronize()
+        reorder_s = time.perf_counter() - t0
+        ei2 = rabbit.relabel(ei, new_id)
+        del ei
+        after_ms, _ = spmm_ms(ei2)
+        out["rows"].append({"graph": name, "nnz": nnz, "levels": levels, "top_communities": top,
+                            "reorder_seconds": reorder_s, "avg_edge_span_before": span_before,
+                            "avg_edge_span_after": rabbit.avg_edge_span(ei2),
+                            "decider_says_reorder": bool(span_before ** 0.5 > n ** 0.5 / 100),
+                            "spmm_before_ms": before_ms, "spmm_after_ms": after_ms, "speedup": before_ms / after_ms})
+        del ei2, new_id
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+
+
 def partitioned_single_gpu_base(dev, steps=5):
     """The N>1 workload (row-partitioned SpMM graph) on this one GPU, so that a scaling series that starts from the
     default N=1 line has its like-for-like base: returns Gedge*feat/s and ms per step."""
@@ -664,7 +723,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu", "layers"])
+    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu", "layers", "reorder"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
@@ -688,6 +747,9 @@ def main():
         return
     if args.workload == "layers":
         run_layer_fusion(args)
+        return
+    if args.workload == "reorder":
+        run_reorder(args)
         return
     run_single(args)
 

@@ -123,6 +123,28 @@ int yitu_stitch_csr_host(int32_t n_blocks, int64_t n_rows, const int32_t *const 
                          const int32_t *const *indices_host, const int64_t *n_cols_host, int32_t *out_indptr_host,
                          int32_t *out_indices_host);
 
+/* ------------------------------------------------------------------------------------ locality reordering */
+/* new_id[v] = position of node v in an order that keeps communities contiguous: hierarchical aggregation with
+ * Rabbit Order's merge criterion (largest positive modularity gain, ccsrc/reorder/rabbit_order.hpp:455-530) run
+ * as synchronous data-parallel rounds on the device — the role of rabbit.reorder (ccsrc/reorder/reorder.cpp:235-290,
+ * called from YiTu_GNN/data/dataset.py:149-170), which runs on the host cores there.  Deterministic: integer
+ * arithmetic throughout.  The edge list is treated as undirected; self-loops and repeated edges are accepted.
+ * Fewer than 2^30 edges.  Synchronises the stream (one small read-back per level).
+ * n_levels_host / n_top_host (optional): levels built, communities at the coarsest level. */
+int64_t yitu_reorder_workspace_bytes(int64_t n_nodes, int64_t n_edges, int32_t max_levels);
+int yitu_reorder_communities(int64_t n_nodes, int64_t n_edges, const int32_t *src, const int32_t *dst,
+                             int32_t max_levels, int32_t *new_id, int32_t *n_levels_host, int64_t *n_top_host,
+                             void *workspace, int64_t workspace_bytes, yitu_stream_t stream);
+
+/* out_src[i] = new_id[src[i]], out_dst[i] = new_id[dst[i]] — the edge list rabbit.reorder returns. */
+int yitu_relabel_edges(int64_t n_edges, const int32_t *src, const int32_t *dst, const int32_t *new_id,
+                       int32_t *out_src, int32_t *out_dst, yitu_stream_t stream);
+
+/* *sum_device = sum_i |src[i] - dst[i]|: numerator of the reference's avg_edgeSpan (YiTu_GNN/data/dataset.py:109),
+ * which its decider compares with sqrt(n)/100 to decide whether to reorder (YiTu_GNN/utils/input_info.py:131-140). */
+int yitu_edge_span_sum(int64_t n_edges, const int32_t *src, const int32_t *dst, uint64_t *sum_device,
+                       yitu_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------- SpMM */
 enum {
     YITU_W_NONE = 0,      /* w = 1                       SAG, GIN, gspmm(edge=None)  */

@@ -263,3 +263,69 @@ def gat_backward(indptr, indices, q, k, x, attn, grad_out):
     grad_a, grad_x = spmm_backward(attn, indptr, indices, x, grad_out)
     grad_q, grad_k = sddmm_backward(indptr, indices, q, k, attn, grad_a)
     return (grad_q[0] if squeeze else grad_q), grad_k, grad_x
+
+
+# ----------------------------------------------------------------------------------------------
+# Locality reordering (numpy; integer arithmetic, so the device result must match bit for bit)
+# ----------------------------------------------------------------------------------------------
+def reorder_communities(n, src, dst, max_levels=32):
+    """new_id int32[n], levels built, communities at the coarsest level.
+
+    Community aggregation with Rabbit Order's merge criterion — join the neighbour u maximising
+    w(v,u) - str(v)*str(u)/tot_wgt when that is positive (ccsrc/reorder/rabbit_order.hpp:455-470), on the
+    symmetrised edge list without self-loops and with parallel edges summed (ccsrc/reorder/reorder.cpp:32-80) — run
+    as synchronous rounds: candidates are the neighbours of higher rank (str, then id), ties go to the smaller id, and
+    v joins u only if u itself stays in place in that round; the graph is contracted between rounds.  New ids order the
+    nodes by (coarsest community, ..., finest community, old id).
+
+    Parity unpinned against the reference: its asynchronous Rabbit Order needs Boost and libnuma (absent here) and
+    its output depends on thread timing.  This restates the round-synchronous schedule the device code runs.
+    """
+    src = np.asarray(src, dtype=np.int64)
+    dst = np.asarray(dst, dtype=np.int64)
+    keep = src != dst
+    keys = np.concatenate([(src[keep] << 32) | dst[keep], (dst[keep] << 32) | src[keep]])
+    keys, w = np.unique(keys, return_counts=True)
+    w = w.astype(np.int64)
+    cu, cv = keys >> 32, keys & 0xFFFFFFFF
+    strength = np.bincount(cu, weights=w, minlength=n).astype(np.int64)
+    tot = int(strength.sum())
+    cur = np.arange(n, dtype=np.int64)
+    levels = []
+    n_cur = n
+    while len(levels) < max_levels and len(cu) > 0:
+        gain = w * tot - strength[cu] * strength[cv]
+        ok = (gain > 0) & ((strength[cv] > strength[cu]) | ((strength[cv] == strength[cu]) & (cv > cu)))
+        parent = np.arange(n_cur, dtype=np.int64)
+        idx = np.nonzero(ok)[0]
+        if len(idx):
+            order = np.lexsort((cv[idx], -gain[idx], cu[idx]))  # per cu: largest gain first, then smaller cv
+            ii = idx[order]
+            first = np.ones(len(ii), dtype=bool)
+            first[1:] = cu[ii][1:] != cu[ii][:-1]
+            parent[cu[ii][first]] = cv[ii][first]
+        stays = parent == np.arange(n_cur)
+        root = np.where(stays[parent], parent, np.arange(n_cur))
+        is_root = root == np.arange(n_cur)
+        n_next = int(is_root.sum())
+        if n_next == n_cur:
+            break
+        label = (np.cumsum(is_root) - 1)[root]
+        strength = np.bincount(label, weights=strength, minlength=n_next).astype(np.int64)
+        a, b = label[cu], label[cv]
+        m = a != b
+        if m.any():
+            keys, inv = np.unique((a[m] << 32) | b[m], return_inverse=True)
+            w = np.bincount(inv, weights=w[m], minlength=len(keys)).astype(np.int64)
+        else:
+            keys, w = np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.int64)
+        cu, cv = keys >> 32, keys & 0xFFFFFFFF
+        cur = label[cur]
+        levels.append(cur.copy())
+        n_cur = n_next
+    perm = np.arange(n, dtype=np.int64)
+    for lv in levels:
+        perm = perm[np.argsort(lv[perm], kind="stable")]
+    new_id = np.empty(n, dtype=np.int64)
+    new_id[perm] = np.arange(n)
+    return new_id.astype(np.int32), len(levels), n_cur

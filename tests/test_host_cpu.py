@@ -122,7 +122,7 @@ def test_operators_reject_cpu_tensors():
 def test_install_as_reference_modules():
     import sys
     import yitu_b200
-    saved = {k: sys.modules.get(k) for k in ("graph_ext", "YiTu_GNN", "YiTu_GNN.YiTu_GNN_kernel")}
+    saved = {k: sys.modules.get(k) for k in ("graph_ext", "YiTu_GNN", "YiTu_GNN.YiTu_GNN_kernel", "YiTu_GNN.rabbit")}
     try:
         yitu_b200.install_as_reference_modules()
         import graph_ext
@@ -132,6 +132,8 @@ def test_install_as_reference_modules():
             assert callable(getattr(graph_ext, fn))
         for fn in ("SAG", "forward", "backward", "forward_gin", "backward_gin", "build_part"):
             assert callable(getattr(YiTu_GNN_kernel, fn))
+        from YiTu_GNN import rabbit
+        assert callable(rabbit.reorder)
     finally:
         for k, v in saved.items():
             if v is None:

@@ -65,6 +65,11 @@ SYMBOLS = {
     "yitu_build_part_count_host": (c_i64, [c_i32, c_vp, c_i64]),
     "yitu_build_part_host": (C.c_int, [c_i32, c_vp, c_i64, c_vp, c_vp]),
     "yitu_stitch_csr_host": (C.c_int, [c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "yitu_reorder_workspace_bytes": (c_i64, [c_i64, c_i64, c_i32]),
+    "yitu_reorder_communities": (C.c_int, [c_i64, c_i64, c_vp, c_vp, c_i32, c_vp, C.POINTER(c_i32), C.POINTER(c_i64), c_vp,
+                                           c_i64, c_vp]),
+    "yitu_relabel_edges": (C.c_int, [c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "yitu_edge_span_sum": (C.c_int, [c_i64, c_vp, c_vp, c_vp, c_vp]),
     "yitu_spmm_csr_f32": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
     "yitu_static_scratch_bytes": (c_i64, []),
     "yitu_spmm_csr_f32_static": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libyitu_b200.so")
-SOURCES = ["spmm.cu", "attention.cu", "graph_prep.cu", "halo.cu", "no_alloc.cu", "epilogue.cu"]
+SOURCES = ["spmm.cu", "attention.cu", "graph_prep.cu", "halo.cu", "no_alloc.cu", "epilogue.cu", "reorder.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE]
 

@@ -93,6 +93,35 @@ def uniform_edges(seed, n_src, n_dst, n_edges, device="cpu", chunk=1 << 26):
     return torch.cat(srcs), torch.cat(dsts)
 
 
+def planted_community_edges(seed, n, community, n_edges, p_intra=0.9, device="cpu", shuffle=True, chunk=1 << 26):
+    """Edges mostly inside blocks of `community` consecutive nodes (probability p_intra, otherwise a uniform
+    destination), with node ids then passed through a pseudo-random bijection of [0, n) when shuffle is set — a graph
+    that has locality to find but whose numbering hides it, as crawled real-world graphs do.  n must be a power of
+    two (the bijection is an odd-multiplier / xor-shift permutation of log2(n)-bit words)."""
+    assert n & (n - 1) == 0 and community <= n
+    bits_n = n.bit_length() - 1
+    t_intra = int(round(p_intra * 65536))
+    srcs, dsts = [], []
+    for e0 in range(0, n_edges, chunk):
+        idx = torch.arange(e0, min(e0 + chunk, n_edges), dtype=torch.int64, device=device)
+        a, b = _draw(seed, idx, 0), _draw(seed, idx, 1)
+        src = ((a & 0xFFFFFFFF) * n) >> 32
+        inside = ((b >> 48) & 0xFFFF) < t_intra
+        local = (((a >> 32) & 0xFFFFFFFF) * community) >> 32
+        anywhere = ((b & 0xFFFFFFFF) * n) >> 32
+        dst = torch.where(inside, torch.div(src, community, rounding_mode="floor") * community + local, anywhere)
+        srcs.append(src)
+        dsts.append(dst)
+    src, dst = torch.cat(srcs), torch.cat(dsts)
+    if shuffle:
+        def scramble(v):
+            v = (v * 0x9E3779B1 + 0x7F4A7C15) & (n - 1)          # odd multiplier: a bijection modulo 2^k
+            v = v ^ (v >> max(1, bits_n // 2))                     # xor-shift: a bijection
+            return (v * 0x85EBCA6B + 0x165667B1) & (n - 1)
+        src, dst = scramble(src), scramble(dst)
+    return src, dst
+
+
 def csr_by_destination(src, dst, n_src, n_dst, self_loops=False, index_dtype=torch.int32,
                        ptr_dtype=torch.int32):
     """Deduplicate (src, dst) pairs, optionally add (i, i) for every i, and return
