@@ -15,7 +15,9 @@
 // at best, only at the same occupancy); sub-warp groups narrower than the row (lose coalescing); a persistent
 // grid with software-pipelined row pointers / index tiles (1.7x slower than letting the CTA scheduler
 // balance short CTAs); batches of 8 consecutive rows per warp with the next row's index tile prefetched
-// (1.1-1.4x slower: fewer, longer warps hide less latency than many short ones).
+// (1.1-1.4x slower: fewer, longer warps hide less latency than many short ones); for heads that share one source
+// row (x_shared_heads), a lane-per-feature layout with the H edge weights broadcast by shuffle (5.4 ms against 3.7 ms
+// for the per-head layout below on the 8x32 layer: ten shuffles per edge cost more than the replicated loads).
 //
 // The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
 // values), per row = 4*D written + one row pointer.
