@@ -1,6 +1,6 @@
 """Generates tests/golden/*.json from the REFERENCE's own CPU-executable code for this path.
 
-Run where the reference checkout is mounted (default /root/reference):
+Run where the reference checkout is mounted (its path in $YITU_REFERENCE):
 
     make -C oracle ref            # compiles ccsrc/kernel/YiTu_GNN.cpp as it lies into oracle/_ref/
     python tests/golden/make_golden.py
