@@ -54,6 +54,23 @@ def _worker(rank, world, port, errors):
                 assert torch.equal(r.x_halo, x[r.plan.halo_ids.long()]), "halo rows must be the owners' rows"
             dist.barrier()
             r.close()
+        # differentiable form: forward over this rank's rows of A, backward over the same rows of A^T
+        from yitu_b200.distributed import PartitionedAggregate
+        whole = ops.PreparedGraph(indptr, indices, n)
+        w_out = graphs.randn_features(9, n, d, device=dev)
+        ref_grad = ops.spmm(whole.t_prepared(), w_out, mode=ops.W_EDGE, edge_values=values, edge_perm=whole.transpose()[2])
+        agg = PartitionedAggregate(indptr, indices, values, d, dev)
+        assert (agg.row_begin, agg.row_end) == (lo, hi)
+        xl = x[lo:hi].clone().requires_grad_()
+        for _ in range(2):  # twice: the shared shards are overwritten between steps
+            xl.grad = None
+            y = agg(xl)
+            (y * w_out[lo:hi]).sum().backward()
+        torch.cuda.synchronize(dev)
+        assert float((y - ref[lo:hi]).abs().max()) <= 1e-5 * float(ref.abs().max())
+        assert float((xl.grad - ref_grad[lo:hi]).abs().max()) <= 1e-5 * float(ref_grad.abs().max())
+        dist.barrier()
+        agg.close()
         dist.destroy_process_group()
     except Exception:
         errors.put("rank %d:\n%s" % (rank, traceback.format_exc()))
@@ -80,3 +97,30 @@ def test_partitioned_spmm_two_gpus():
             p.terminate()
             msgs.append("a rank did not finish")
     assert not msgs and all(p.exitcode == 0 for p in procs), "\n".join(msgs)
+
+
+def test_partitioned_aggregate_single_gpu_autograd():
+    """World size 1: the differentiable partitioned aggregation degenerates to the local SpMM and its transpose."""
+    sys.path.insert(0, ROOT)
+    from yitu_b200 import graphs, ops
+    from yitu_b200.distributed import PartitionedAggregate
+    dev = torch.device("cuda", 0)
+    n, d = 1 << 14, 64
+    src, dst = graphs.rmat_edges(5, n, n, 1 << 18, device=dev)
+    indptr, indices = graphs.csr_by_destination(src, dst, n, n)
+    values = torch.rand(indices.numel(), device=dev)
+    whole = ops.PreparedGraph(indptr, indices, n)
+    x = graphs.randn_features(1, n, d, device=dev).requires_grad_()
+    w_out = graphs.randn_features(2, n, d, device=dev)
+    for vals in (values, None):
+        mode = ops.W_EDGE if vals is not None else ops.W_NONE
+        agg = PartitionedAggregate(indptr, indices, vals, d, dev)
+        x.grad = None
+        y = agg(x)
+        (y * w_out).sum().backward()
+        ref = ops.spmm(whole, x.detach(), mode=mode, edge_values=vals)
+        ref_grad = ops.spmm(whole.t_prepared(), w_out, mode=mode, edge_values=vals,
+                            edge_perm=whole.transpose()[2] if vals is not None else None)
+        assert float((y.detach() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+        assert float((x.grad - ref_grad).abs().max()) <= 1e-5 * float(ref_grad.abs().max())
+        agg.close()

@@ -160,9 +160,11 @@ class PartitionedSpmm:
             events.append(("spmm", a, self._mark(events, "spmm")))
         return out
 
-    def step(self, events=None):
+    def step(self, events=None, fence=False):
         """One aggregation over this rank's rows; returns the [n_local, d] output (reused between steps).
-        `events`, if a list, receives (tag, start, end) CUDA-event triples around every SpMM and halo fetch."""
+        `events`, if a list, receives (tag, start, end) CUDA-event triples around every SpMM and halo fetch.
+        fence=True adds a second handshake once this rank's halo has arrived, so that no rank's later work (which may
+        overwrite its feature shard, as a training step does) starts before every peer has finished reading it."""
         sh = self.shard
         if self.mode == "local":
             return self._spmm(self.graph, self.x_local, sh.values, events=events)
@@ -170,6 +172,10 @@ class PartitionedSpmm:
         if self.mode == "allgather":
             dist.all_gather_into_tensor(self.rep, self._slot, group=self.group)
             return self._spmm(self.graph, self.rep, sh.values, events=events)
+        if fence:
+            self.fetch_halo(events)
+            self.handshake()
+            return self._spmm(self.graph, self.xbuf, sh.values, events=events)
         if self.row_blocks > 1:
             main = torch.cuda.current_stream(self.device)
             self.side.wait_stream(main)
@@ -203,3 +209,51 @@ class PartitionedSpmm:
     def close(self):
         if getattr(self, "shared", None) is not None:
             self.shared.close()
+
+
+class _PartitionedAggregateFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, owner):
+        ctx.owner = owner
+        owner.fwd.x_local.copy_(x_local)
+        return owner.fwd.step(fence=True).clone()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        owner = ctx.owner
+        owner.bwd.x_local.copy_(grad_out)
+        return owner.bwd.step(fence=True).clone(), None
+
+
+class PartitionedAggregate:
+    """Differentiable y = A x over a row-partitioned square graph: rank p holds rows [bounds[p], bounds[p+1]) of x and
+    of y.  Forward runs the partitioned SpMM over this rank's rows of A; backward runs it over the same row range of
+    A^T (pull-style, no atomics, no reduction across ranks), fetching the halo rows of the upstream gradient from the
+    peers' shards.  The reference's multi-GPU layers reduce partial results across ranks instead
+    (YiTu_GNN/distributed/communication.py:230-264).
+
+    Built from the whole graph on every rank (indptr / indices / values are the global CSR, as in the reference's
+    partitioning step, which also starts from the full graph)."""
+
+    def __init__(self, indptr, indices, values, d, device, group=None, bounds=None, mode="peer"):
+        from .partition import RowShard, partition_bounds
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        n = indptr.numel() - 1
+        self.bounds = list(bounds) if bounds is not None else partition_bounds(indptr, world)
+        self.row_begin, self.row_end = self.bounds[rank], self.bounds[rank + 1]
+        whole = ops.PreparedGraph(indptr, indices, n)
+        t_indptr, t_rows, t_perm = whole.transpose()
+        t_values = None if values is None else values[t_perm.long()]
+        wm = ops.W_EDGE if values is not None else ops.W_NONE
+        self.fwd = PartitionedSpmm(RowShard(indptr, indices, values, self.bounds, rank), d, device, group, mode,
+                                   overlap=False, weight_mode=wm)
+        self.bwd = PartitionedSpmm(RowShard(t_indptr, t_rows, t_values, self.bounds, rank), d, device, group, mode,
+                                   overlap=False, weight_mode=wm)
+
+    def __call__(self, x_local):
+        return _PartitionedAggregateFunction.apply(x_local, self)
+
+    def close(self):
+        self.fwd.close()
+        self.bwd.close()
