@@ -243,7 +243,7 @@ class GatWorkload:
         self.q = (self.x * a_dst).sum(-1).contiguous()
         self.grad = graphs.randn_features(2, n, H * F, device=device).view(n, H, F)
         self.units_per_step = 2 * self.nnz * self.d
-        self.launches_per_step = 1 + 5  # fused forward; backward = softmax, edge dot, softmax bwd, SpMM, gather sum
+        self.launches_per_step = 1 + 3  # fused forward; backward = edge kernel, transposed SpMM, per-source sum
         self.kernel_launches_per_step = 1
         self.kernel_bytes = self.nnz * (4 + 4 * H + 4 * H * F) + n * (4 + 4 * H + 4 * H * F + 8 * H)
         self.traffic_key = "gat_fwd_h8_f32"

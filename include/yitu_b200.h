@@ -250,9 +250,10 @@ int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indpt
  * one pass over each row's edges — the composition sddmm_forward + spmm_forward of the reference
  * (xgnn_h/sparse.py:38-51,84-91; layer YiTu_GNN/YiTu_H/test/common/model.py:75-106) without the [nnz,H]
  * attention tensor.  Plain (unstitched) graphs, H <= 32, F a multiple of 4, H*F <= 512; other shapes return
- * YITU_ERR_UNSUPPORTED and the caller composes the unfused ops.  The backward call recomputes the attention from
- * query/key and chains the edge-softmax, edge-dot, transposed-SpMM and gather-sum kernels; edge_attn and edge_grad
- * are its [nnz,H] scratch. */
+ * YITU_ERR_UNSUPPORTED and the caller composes the unfused ops.  The backward call is edge-parallel: with the row
+ * statistics of the forward pass and D[r,h] = <grad_out[r,h,:], out[r,h,:]> (= sum_e attn_e * d attn_e) every edge's
+ * attention, its gradient and the score gradient follow without a second pass over the row; one kernel writes them
+ * (edge_attn, edge_grad: [nnz,H] scratch) and grad_query, the transposed SpMM gives grad_x, a per-source sum grad_key. */
 typedef struct yitu_gat_args_t {
     yitu_csr_t graph;
     int64_t n_heads, n_feats;
@@ -267,7 +268,14 @@ typedef struct yitu_gat_args_t {
     int32_t activation; /* YITU_ACT_* on out (forward only; the backward call expects the gradient with respect
                            to the pre-activation values) */
     int32_t reserved;
+    float *out_heads;   /* head_mean only: the per-head result [n_rows,H,F] before the mean; optional in the forward
+                           call, required by the backward call (which reads it instead of `out`) */
+    const yitu_hub_plan_t *plan; /* optional hub-row schedule of `graph`: rows longer than plan->chunk_edges are cut
+                                    into chunks that separate warps process (power-law graphs) */
+    float *scratch;     /* plan != NULL: forward needs yitu_gat_fwd_scratch_bytes(plan->n_chunks, H, F) */
+    int64_t scratch_bytes;
 } yitu_gat_args_t;
+int64_t yitu_gat_fwd_scratch_bytes(int64_t n_chunks, int64_t n_heads, int64_t n_feats);
 int yitu_gat_fwd_f32(const yitu_gat_args_t *args, yitu_stream_t stream);
 
 typedef struct yitu_gat_bwd_args_t {
@@ -281,7 +289,11 @@ typedef struct yitu_gat_bwd_args_t {
     float *grad_x;             /* [n_cols,H,F] */
     float *edge_attn;          /* scratch [nnz,H] */
     float *edge_grad;          /* scratch [nnz,H] */
+    const yitu_hub_plan_t *t_plan; /* optional hub-row schedule of the transposed graph (fwd.plan is that of the graph) */
+    float *scratch;            /* a plan is given: yitu_gat_bwd_scratch_bytes(fwd.plan chunks, t_plan chunks, H, F) */
+    int64_t scratch_bytes;
 } yitu_gat_bwd_args_t;
+int64_t yitu_gat_bwd_scratch_bytes(int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads, int64_t n_feats);
 int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *args, yitu_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------- multi-GPU */

@@ -375,3 +375,53 @@ def test_attention_ops_with_int64_row_pointers(oracle):
     assert t_ip.dtype == torch.int64
     r_ip, r_rows, r_perm = oracle.csr_transpose(indptr, indices, n_src)
     assert np.array_equal(t_ip.cpu().numpy(), r_ip) and np.array_equal(t_perm.cpu().numpy(), r_perm)
+
+
+def _hub_graph(rng, n, hubs, hub_deg, density=0.01):
+    """CSR with a few destination rows AND a few source columns of degree ~hub_deg (power-law-like tails on both
+    sides, so the graph and its transpose both have rows to split)."""
+    a = rng.random((n, n)) < density
+    for h in rng.choice(n, size=hubs, replace=False):
+        a[h, rng.choice(n, size=hub_deg, replace=False)] = True
+    for h in rng.choice(n, size=hubs, replace=False):
+        a[rng.choice(n, size=hub_deg, replace=False), h] = True
+    indptr = np.concatenate([[0], np.cumsum(a.sum(1))]).astype(np.int32)
+    return indptr, np.nonzero(a)[1].astype(np.int32)
+
+
+@pytest.mark.parametrize("H,F,head_mean", [(8, 32, False), (4, 16, True), (2, 64, False), (3, 20, False), (1, 128, True),
+                                           (16, 32, True)])
+@pytest.mark.parametrize("chunk", [64, 512])
+def test_fused_gat_splits_hub_rows(oracle, H, F, head_mean, chunk):
+    """Rows (and, in the backward, source columns) longer than the chunk size are cut into chunks handled by separate
+    warps; results must not depend on the split."""
+    from yitu_b200 import ops
+    rng = np.random.default_rng(1000 * H + F + chunk)
+    n = 2200
+    indptr, indices = _hub_graph(rng, n, hubs=3, hub_deg=1700)
+    assert np.diff(indptr).max() > 1500
+    q = rng.standard_normal((n, H)).astype(np.float32)
+    k = rng.standard_normal((n, H)).astype(np.float32)
+    x = rng.standard_normal((n, H, F)).astype(np.float32)
+    graph = ops.PreparedGraph(_dev(indptr), _dev(indices), n)
+    assert graph.plan(chunk) is not None and graph.t_prepared().plan(chunk) is not None
+    ref_out, ref_attn = oracle.gat_forward(indptr, indices, q, k, x)
+    res = ops.gat_fwd(graph, _dev(q), _dev(k), _dev(x), head_mean=head_mean, chunk_edges=chunk)
+    plain = ops.gat_fwd(graph, _dev(q), _dev(k), _dev(x), head_mean=head_mean, chunk_edges=0)
+    heads = res[3] if head_mean else res[0]
+    assert_close(heads.cpu().numpy(), ref_out, what="per-head output with hub chunks")
+    if head_mean:
+        assert_close(res[0].cpu().numpy(), ref_out.astype(np.float64).mean(axis=1), what="head mean with hub chunks")
+    assert_close(res[1].cpu().numpy(), plain[1].cpu().numpy(), what="row maxima")
+    assert_close(res[2].cpu().numpy(), plain[2].cpu().numpy(), what="row sums")
+    if head_mean:
+        g_in = rng.standard_normal((n, F)).astype(np.float32)
+        g_full = (np.repeat(g_in[:, None, :], H, axis=1) / np.float32(H)).astype(np.float32)
+    else:
+        g_in = g_full = rng.standard_normal((n, H, F)).astype(np.float32)
+    rgq, rgk, rgx = oracle.gat_backward(indptr, indices, q, k, x, ref_attn, g_full)
+    gq, gk, gx = ops.gat_bwd(graph, _dev(q), _dev(k), _dev(x), res[0], res[1], res[2], _dev(g_in), head_mean=head_mean,
+                             out_heads=res[3] if head_mean else None, chunk_edges=chunk)
+    assert_close(gq.cpu().numpy(), np.asarray(rgq).reshape(gq.shape), rtol=3e-5, what="grad_query with hub chunks")
+    assert_close(gk.cpu().numpy(), rgk, rtol=3e-5, what="grad_key with hub chunks")
+    assert_close(gx.cpu().numpy(), rgx, rtol=3e-5, what="grad_x with hub chunks")

@@ -119,9 +119,10 @@ def test_gat_head_mean_forward_matches_oracle(oracle, H, F, act):
     ref_full, _ = oracle.gat_forward(indptr, indices, q, k, x)
     ref = _act64(ref_full.astype(np.float64).mean(axis=1), act)
     g = _graph(indptr, indices, n)
-    out, rmax, rsum = ops.gat_fwd(g, torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(x).cuda(),
-                                  head_mean=True, activation=act)
-    assert out.shape == (n, F)
+    out, rmax, rsum, heads = ops.gat_fwd(g, torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
+                                         torch.from_numpy(x).cuda(), head_mean=True, activation=act)
+    assert out.shape == (n, F) and heads.shape == (n, H, F)
+    assert_close(heads.cpu().numpy(), ref_full, what="per-head result kept for the backward")
     assert_close(out.cpu().numpy(), ref, what="gat head mean H=%d F=%d act=%s" % (H, F, act))
     full, rmax2, rsum2 = ops.gat_fwd(g, torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
                                      torch.from_numpy(x).cuda())
@@ -160,13 +161,16 @@ def test_gat_head_mean_backward_matches_oracle(oracle, H, F):
     ref_q, ref_k, ref_x = oracle.gat_backward(indptr, indices, q, k, x, attn, g_full.astype(np.float32))
     gr = _graph(indptr, indices, n)
     tq, tk, tx = (torch.from_numpy(a).cuda() for a in (q, k, x))
-    out, rmax, rsum = ops.gat_fwd(gr, tq, tk, tx, head_mean=True)
-    gq, gk, gx = ops.gat_bwd(gr, tq, tk, tx, out, rmax, rsum, torch.from_numpy(g_mean).cuda(), head_mean=True)
+    out, rmax, rsum, heads = ops.gat_fwd(gr, tq, tk, tx, head_mean=True)
+    gq, gk, gx = ops.gat_bwd(gr, tq, tk, tx, out, rmax, rsum, torch.from_numpy(g_mean).cuda(), head_mean=True,
+                             out_heads=heads)
     assert_close(gq.cpu().numpy(), np.asarray(ref_q).reshape(gq.shape), rtol=2e-5, what="grad_query")
     assert_close(gk.cpu().numpy(), ref_k, rtol=2e-5, what="grad_key")
     assert_close(gx.cpu().numpy(), ref_x, rtol=2e-5, what="grad_x")
     with pytest.raises(RuntimeError):  # the per-head gradient shape is refused in head-mean mode
-        ops.gat_bwd(gr, tq, tk, tx, out, rmax, rsum, torch.from_numpy(g_full).cuda(), head_mean=True)
+        ops.gat_bwd(gr, tq, tk, tx, out, rmax, rsum, torch.from_numpy(g_full).cuda(), head_mean=True, out_heads=heads)
+    with pytest.raises(RuntimeError):  # and so is a head-mean backward without the per-head forward result
+        ops.gat_bwd(gr, tq, tk, tx, out, rmax, rsum, torch.from_numpy(g_mean).cuda(), head_mean=True)
 
 
 def _block(indptr, indices, n_src):

@@ -37,12 +37,14 @@ class SpmmArgs(C.Structure):
 class GatArgs(C.Structure):
     _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("slope", c_f32), ("head_mean", c_i32),
                 ("query", c_vp), ("key", c_vp), ("x", c_vp), ("out", c_vp), ("row_max", c_vp), ("row_sum", c_vp),
-                ("activation", c_i32), ("reserved", c_i32)]
+                ("activation", c_i32), ("reserved", c_i32), ("out_heads", c_vp), ("plan", C.POINTER(HubPlan)),
+                ("scratch", c_vp), ("scratch_bytes", c_i64)]
 
 
 class GatBwdArgs(C.Structure):
     _fields_ = [("fwd", GatArgs), ("grad_out", c_vp), ("t_indptr", c_vp), ("t_rows", c_vp), ("t_perm", c_vp),
-                ("grad_query", c_vp), ("grad_key", c_vp), ("grad_x", c_vp), ("edge_attn", c_vp), ("edge_grad", c_vp)]
+                ("grad_query", c_vp), ("grad_key", c_vp), ("grad_x", c_vp), ("edge_attn", c_vp), ("edge_grad", c_vp),
+                ("t_plan", C.POINTER(HubPlan)), ("scratch", c_vp), ("scratch_bytes", c_i64)]
 
 
 # every symbol include/yitu_b200.h declares: name -> (restype, argtypes)
@@ -80,6 +82,8 @@ SYMBOLS = {
     "yitu_edge_softmax_bwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                                             c_vp]),
     "yitu_edge_gather_sum_f32": (C.c_int, [c_i64, c_vp, c_i32, c_vp, c_i64, c_vp, c_vp, c_vp]),
+    "yitu_gat_fwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64]),
+    "yitu_gat_bwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64, c_i64]),
     "yitu_gat_fwd_f32": (C.c_int, [C.POINTER(GatArgs), c_vp]),
     "yitu_gat_bwd_f32": (C.c_int, [C.POINTER(GatBwdArgs), c_vp]),
     "yitu_shared_alloc": (C.c_int, [c_i64, C.POINTER(c_vp), c_vp]),

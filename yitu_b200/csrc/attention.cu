@@ -265,16 +265,39 @@ struct GatParams {
     const float *q, *k, *x;
     float *out, *row_max, *row_sum;
     int head_mean, act, stage;  // stage = floats of per-warp staging for the head mean (H*F or 0)
+    float *out_heads;           // head_mean: optional per-head result [n_rows,H,F]
+    // hub rows: chunk c covers edges [chunk_begin[c], +chunk_edges) of row chunk_row[c]; its unnormalised sums, running
+    // maxima and sums go to partial[c] = {H*F, H, H} floats and gat_fwd_merge_kernel finishes the row
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+    float *partial;
 };
 
 __device__ __forceinline__ int warp_smem_floats_fwd(int H, int stage) { return 32 + 32 * H + 4 * 32 + stage; }
+
+// floats of one hub chunk's partial result: H*F sums, then H maxima and H sums (padded so that chunks stay 16-byte aligned)
+__host__ __device__ __forceinline__ int64_t fwd_partial_stride(int64_t H, int64_t F) { return H * F + ((2 * H + 3) & ~3ll); }
 
 template <int NV, bool MEAN>
 __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
-    if (row >= p.n_rows) return;
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+    int64_t row, eb, ee;
+    const bool chunk = gid < p.n_chunks;
+    if (chunk) {
+        row = __ldg(p.chunk_row + gid);
+        eb = __ldg(p.chunk_begin + gid);
+        ee = min(eb + static_cast<int64_t>(p.chunk_edges), load_ptr(p.indptr, p.is64, row + 1));
+    } else {
+        row = gid - p.n_chunks;
+        if (row >= p.n_rows) return;
+        eb = load_ptr(p.indptr, p.is64, row);
+        ee = load_ptr(p.indptr, p.is64, row + 1);
+        if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;  // hub row: done by its chunks
+    }
     const int H = p.H;
     float *base = smem + wib * warp_smem_floats_fwd(H, p.stage);
     int *s_col = reinterpret_cast<int *>(base);
@@ -300,7 +323,6 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
 
     if (lane < H) s_q[lane] = __ldg(p.q + row * H + lane);
     float m_run = -CUDART_INF_F, l_run = 0.0f;  // lane h owns head h
-    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
     __syncwarp();
 
     for (int64_t e0 = eb; e0 < ee; e0 += 32) {
@@ -373,6 +395,18 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
         }
         __syncwarp();
     }
+    if (chunk) {
+        float *part = p.partial + gid * fwd_partial_stride(H, p.F);
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (valid[i])
+                *reinterpret_cast<float4 *>(part + off[i]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        if (lane < H) {
+            part[D + lane] = m_run;
+            part[D + H + lane] = l_run;
+        }
+        return;
+    }
     if (lane < H) {
         s_l[lane] = l_run;
         p.row_max[row * H + lane] = m_run;
@@ -388,8 +422,9 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
             if (!valid[i]) continue;
             const float l = s_l[hd[i]];
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            *reinterpret_cast<float4 *>(s_o + off[i]) =
-                make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+            const float4 r = make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+            *reinterpret_cast<float4 *>(s_o + off[i]) = r;
+            if (p.out_heads) *reinterpret_cast<float4 *>(p.out_heads + row * D + off[i]) = r;
         }
         __syncwarp();
         const float inv_h = 1.0f / static_cast<float>(H);
@@ -398,16 +433,16 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
             for (int h = 0; h < H; ++h) a += s_o[h * p.F + f];
             p.out[row * p.F + f] = activate(a * inv_h, p.act);
         }
-        return;
-    }
+    } else {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (!valid[i]) continue;
-        const float l = s_l[hd[i]];
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        *reinterpret_cast<float4 *>(p.out + row * D + off[i]) =
-            make_float4(activate(acc[i][0] * inv, p.act), activate(acc[i][1] * inv, p.act),
-                        activate(acc[i][2] * inv, p.act), activate(acc[i][3] * inv, p.act));
+        for (int i = 0; i < NV; ++i) {
+            if (!valid[i]) continue;
+            const float l = s_l[hd[i]];
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            *reinterpret_cast<float4 *>(p.out + row * D + off[i]) =
+                make_float4(activate(acc[i][0] * inv, p.act), activate(acc[i][1] * inv, p.act),
+                            activate(acc[i][2] * inv, p.act), activate(acc[i][3] * inv, p.act));
+        }
     }
 }
 
@@ -421,6 +456,236 @@ __global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ Ga
 template <int NV, bool MEAN>
 __global__ void __launch_bounds__(256, 4) gat_fwd_kernel_r64(const __grid_constant__ GatParams p) {
     gat_fwd_body<NV, MEAN>(p);
+}
+
+// Finishes the hub rows of the fused forward: combines the chunks' (maximum, sum, unnormalised aggregate) in chunk
+// order.  One CTA per chunk; only the first chunk of a row works.
+__global__ void __launch_bounds__(128) gat_fwd_merge_kernel(const __grid_constant__ GatParams p) {
+    __shared__ float s_m[32], s_inv[32], s_o[512];
+    const int64_t c0 = blockIdx.x;
+    const int64_t row = __ldg(p.chunk_row + c0);
+    const int64_t rb = load_ptr(p.indptr, p.is64, row);
+    if (__ldg(p.chunk_begin + c0) != rb) return;
+    const int64_t re = load_ptr(p.indptr, p.is64, row + 1);
+    const int nch = static_cast<int>((re - rb + p.chunk_edges - 1) / p.chunk_edges);
+    const int H = p.H, F = p.F, D = H * F;
+    const int64_t stride = fwd_partial_stride(H, F);
+    const float *part = p.partial + c0 * stride;
+    if (threadIdx.x < H) {
+        const int h = threadIdx.x;
+        float m = -CUDART_INF_F;
+        for (int c = 0; c < nch; ++c) m = fmaxf(m, part[c * stride + D + h]);
+        float l = 0.0f;
+        for (int c = 0; c < nch; ++c) l += part[c * stride + D + H + h] * expf(part[c * stride + D + h] - m);
+        s_m[h] = m;
+        s_inv[h] = l > 0.0f ? 1.0f / l : 0.0f;
+        p.row_max[row * H + h] = m;
+        p.row_sum[row * H + h] = l;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const int h = d / F;
+        float a = 0.0f;
+        for (int c = 0; c < nch; ++c) a = fmaf(part[c * stride + d], expf(part[c * stride + D + h] - s_m[h]), a);
+        const float v = a * s_inv[h];
+        if (p.head_mean) {
+            s_o[d] = v;
+            if (p.out_heads) p.out_heads[row * D + d] = v;
+        } else {
+            p.out[row * D + d] = activate(v, p.act);
+        }
+    }
+    if (!p.head_mean) return;
+    __syncthreads();
+    const float inv_h = 1.0f / static_cast<float>(H);
+    for (int f = threadIdx.x; f < F; f += blockDim.x) {
+        float a = 0.0f;
+        for (int h = 0; h < H; ++h) a += s_o[h * F + f];
+        p.out[row * F + f] = activate(a * inv_h, p.act);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused GAT backward, destination side.  With the forward's row statistics (max M, sum L) the attention of an edge
+// is p = exp(LeakyReLU(q+k) - M) / L on its own, and sum_e p_e * dp_e over a row equals Dv = <grad_out, out> of that
+// row, so every edge is independent:
+//   dp = <grad_out[row,h,:], x[col,h,:]>,  d score = p * (dp - Dv) * LeakyReLU'(q+k).
+// One warp per row (or hub chunk): the row of grad_out stays in registers, source rows are gathered with 128-bit loads
+// (two edges in flight), a 32-edge tile of dp lands in shared memory, then the lanes spread over (edge, head) pairs
+// and write attention and score gradient coalesced.  grad_query is the row sum of the score gradients (chunks leave
+// partial sums that chunk_sum_kernel adds in order).
+// ---------------------------------------------------------------------------------------------------------
+struct GatBwdParams {
+    int64_t n_rows;
+    const void *indptr;
+    const int *indices;
+    int is64, H, F, hshift;
+    float slope;
+    const float *q, *k, *x, *out_heads, *row_max, *row_sum;
+    const float *g;  // upstream gradient: [n_rows,H,F], or [n_rows,F] shared by the heads (g_shared), times g_scale
+    int g_shared;
+    float g_scale;
+    float *edge_attn, *edge_grad, *grad_q;
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+    float *q_partial;  // [n_chunks, H]
+};
+
+template <int NV>
+__global__ void __launch_bounds__(256) gat_bwd_edge_kernel(const __grid_constant__ GatBwdParams p) {
+    extern __shared__ float smem[];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+    int64_t row, eb, ee;
+    const bool chunk = gid < p.n_chunks;
+    if (chunk) {
+        row = __ldg(p.chunk_row + gid);
+        eb = __ldg(p.chunk_begin + gid);
+        ee = min(eb + static_cast<int64_t>(p.chunk_edges), load_ptr(p.indptr, p.is64, row + 1));
+    } else {
+        row = gid - p.n_chunks;
+        if (row >= p.n_rows) return;
+        eb = load_ptr(p.indptr, p.is64, row);
+        ee = load_ptr(p.indptr, p.is64, row + 1);
+        if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;
+    }
+    const int H = p.H, F = p.F;
+    const int64_t D = static_cast<int64_t>(H) * F;
+    const int LPH = F >> 2;  // lanes per head (a power of two)
+    float *base = smem + wib * (32 + 32 * H + 4 * 32);
+    int *s_col = reinterpret_cast<int *>(base);
+    float *s_v = base + 32;
+    float *s_q = s_v + 32 * H, *s_m = s_q + 32, *s_il = s_m + 32, *s_d = s_il + 32;
+    if (lane < H) {
+        s_q[lane] = __ldg(p.q + row * H + lane);
+        s_m[lane] = __ldg(p.row_max + row * H + lane);
+        const float l = __ldg(p.row_sum + row * H + lane);
+        s_il[lane] = l > 0.0f ? 1.0f / l : 0.0f;
+    }
+    int hd[NV];
+    bool valid[NV];
+    int64_t off[NV];
+    float4 gr[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        off[i] = static_cast<int64_t>(i * 32 + lane) * 4;
+        valid[i] = off[i] < D;
+        hd[i] = valid[i] ? static_cast<int>(off[i] / F) : 0;
+        gr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float d = 0.0f;
+        if (valid[i]) {
+            const float *gp = p.g_shared ? p.g + row * F + (off[i] - static_cast<int64_t>(hd[i]) * F) : p.g + row * D + off[i];
+            gr[i] = __ldg(reinterpret_cast<const float4 *>(gp));
+            gr[i].x *= p.g_scale; gr[i].y *= p.g_scale; gr[i].z *= p.g_scale; gr[i].w *= p.g_scale;
+            const float4 o = __ldg(reinterpret_cast<const float4 *>(p.out_heads + row * D + off[i]));
+            d = gr[i].x * o.x + gr[i].y * o.y + gr[i].z * o.z + gr[i].w * o.w;
+        }
+        for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+        if (valid[i] && (lane & (LPH - 1)) == 0) s_d[hd[i]] = d;
+    }
+    __syncwarp();
+    float gq = 0.0f;  // lane h owns head h
+    for (int64_t e0 = eb; e0 < ee; e0 += 32) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
+        const int my_col = lane < n ? ld_stream(p.indices + e0 + lane) : 0;
+        const int c_first = __shfl_sync(0xffffffffu, my_col, 0);
+        s_col[lane] = lane < n ? my_col : c_first;
+        __syncwarp();
+        const int n2 = (n + 1) & ~1;
+        for (int j = 0; j < n2; j += 2) {
+            float4 v[2][NV];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float *xr = p.x + static_cast<int64_t>(s_col[j + u]) * D;
+#pragma unroll
+                for (int i = 0; i < NV; ++i)
+                    v[u][i] = valid[i] ? __ldg(reinterpret_cast<const float4 *>(xr + off[i]))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    float d = gr[i].x * v[u][i].x + gr[i].y * v[u][i].y + gr[i].z * v[u][i].z + gr[i].w * v[u][i].w;
+                    for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
+                    if (valid[i] && (lane & (LPH - 1)) == 0 && j + u < n) s_v[(j + u) * H + hd[i]] = d;
+                }
+        }
+        __syncwarp();
+        const int npairs = n * H;
+        for (int idx = lane; idx < npairs; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            const float sc = s_q[h] + __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + h);
+            const float pr = expf(leaky_relu(sc, p.slope) - s_m[h]) * s_il[h];
+            const float ds = pr * (s_v[idx] - s_d[h]) * (sc < 0.0f ? p.slope : 1.0f);
+            p.edge_attn[e0 * H + idx] = pr;
+            p.edge_grad[e0 * H + idx] = ds;
+            s_v[idx] = ds;
+        }
+        __syncwarp();
+        if (lane < H)
+            for (int e = 0; e < n; ++e) gq += s_v[e * H + lane];
+        __syncwarp();
+    }
+    if (lane < H) {
+        if (chunk) p.q_partial[gid * H + lane] = gq;
+        else p.grad_q[row * H + lane] = gq;
+    }
+}
+
+// out[row, :W] = sum of the row's chunk partials, in chunk order (one CTA per chunk, the row's first chunk works)
+__global__ void __launch_bounds__(128)
+chunk_sum_kernel(const void *indptr, int is64, int chunk_edges, const int *chunk_row, const int64_t *chunk_begin, int W,
+                 const float *partial, float *out) {
+    const int64_t c0 = blockIdx.x;
+    const int64_t row = __ldg(chunk_row + c0);
+    const int64_t rb = load_ptr(indptr, is64, row);
+    if (__ldg(chunk_begin + c0) != rb) return;
+    const int64_t nch = (load_ptr(indptr, is64, row + 1) - rb + chunk_edges - 1) / chunk_edges;
+    for (int d = threadIdx.x; d < W; d += blockDim.x) {
+        float a = 0.0f;
+        for (int64_t c = 0; c < nch; ++c) a += partial[(c0 + c) * W + d];
+        out[row * W + d] = a;
+    }
+}
+
+// edge_gather_sum over a transposed graph with hub sources: chunks leave partial sums
+__global__ void __launch_bounds__(256)
+edge_gather_sum_plan_kernel(int64_t n_cols, const void *t_indptr, int is64, const int *perm, int H, int HB,
+                            const float *vals, float *out, int64_t n_chunks, int chunk_edges, const int *chunk_row,
+                            const int64_t *chunk_begin, float *partial) {
+    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    int64_t c, b, e;
+    const bool chunk = gid < n_chunks;
+    if (chunk) {
+        c = __ldg(chunk_row + gid);
+        b = __ldg(chunk_begin + gid);
+        e = min(b + static_cast<int64_t>(chunk_edges), load_ptr(t_indptr, is64, c + 1));
+    } else {
+        c = gid - n_chunks;
+        if (c >= n_cols) return;
+        b = load_ptr(t_indptr, is64, c);
+        e = load_ptr(t_indptr, is64, c + 1);
+        if (e - b > chunk_edges) return;
+    }
+    const int lane = threadIdx.x & 31;
+    const int hs = lane & (HB - 1);
+    const int slot = lane >> pow2_shift(HB);
+    const int ES = 32 / HB;
+    for (int hc = 0; hc < H; hc += HB) {
+        const int h = hc + hs;
+        float a = 0.0f;
+        if (h < H)
+            for (int64_t j = b + slot; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
+        for (int o = HB; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (slot == 0 && h < H) {
+            if (chunk) partial[gid * H + h] = a;
+            else out[c * H + h] = a;
+        }
+    }
 }
 
 static int head_block(int64_t H) {
@@ -546,6 +811,22 @@ static int check_gat(const yitu_gat_args_t *a, bool backward) {
     return YITU_OK;
 }
 
+static int fill_plan(const yitu_hub_plan_t *plan, int64_t *n_chunks, int *chunk_edges, const int **chunk_row,
+                     const int64_t **chunk_begin) {
+    *n_chunks = 0;
+    *chunk_edges = 0;
+    *chunk_row = nullptr;
+    *chunk_begin = nullptr;
+    if (plan == nullptr || plan->n_chunks == 0) return YITU_OK;
+    YITU_REQUIRE(plan->chunk_edges >= 32 && plan->chunk_row && plan->chunk_begin, YITU_ERR_INVALID_ARG,
+                 "hub plan needs chunk_edges >= 32 and its two tables");
+    *n_chunks = plan->n_chunks;
+    *chunk_edges = plan->chunk_edges;
+    *chunk_row = plan->chunk_row;
+    *chunk_begin = plan->chunk_begin;
+    return YITU_OK;
+}
+
 static void fill_gat(GatParams &p, const yitu_gat_args_t *a) {
     p.n_rows = a->graph.n_rows; p.indptr = a->graph.indptr; p.indices = a->graph.indices;
     p.is64 = a->graph.indptr_is64; p.H = static_cast<int>(a->n_heads); p.F = static_cast<int>(a->n_feats);
@@ -554,6 +835,7 @@ static void fill_gat(GatParams &p, const yitu_gat_args_t *a) {
     p.out = a->out; p.row_max = a->row_max; p.row_sum = a->row_sum;
     p.head_mean = a->head_mean ? 1 : 0; p.act = a->activation;
     p.stage = p.head_mean ? p.H * p.F : 0;
+    p.out_heads = p.head_mean ? a->out_heads : nullptr;
 }
 
 template <typename K>
@@ -562,9 +844,23 @@ static int launch_rows(K kernel, const GatParams &p, int smem_floats_per_warp, c
     const size_t smem = static_cast<size_t>(warps) * smem_floats_per_warp * sizeof(float);
     if (smem > 48 * 1024)
         YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<static_cast<unsigned>((p.n_rows + warps - 1) / warps), warps * 32, smem, st>>>(p);
+    const int64_t groups = p.n_rows + p.n_chunks;
+    kernel<<<static_cast<unsigned>((groups + warps - 1) / warps), warps * 32, smem, st>>>(p);
     YITU_LAUNCH_CHECK();
     return YITU_OK;
+}
+
+extern "C" int64_t yitu_gat_fwd_scratch_bytes(int64_t n_chunks, int64_t n_heads, int64_t n_feats) {
+    if (n_chunks < 0 || n_heads < 1 || n_feats < 1) return -1;
+    return n_chunks * fwd_partial_stride(n_heads, n_feats) * static_cast<int64_t>(sizeof(float));
+}
+
+static inline int64_t up256f(int64_t floats) { return (floats + 63) / 64 * 64; }  // 256-byte pieces, counted in floats
+
+extern "C" int64_t yitu_gat_bwd_scratch_bytes(int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads, int64_t n_feats) {
+    if (n_chunks < 0 || t_n_chunks < 0 || n_heads < 1 || n_feats < 1) return -1;
+    return (up256f(n_chunks * n_heads) + up256f(t_n_chunks * n_heads) + up256f(t_n_chunks * n_heads * n_feats)) *
+           static_cast<int64_t>(sizeof(float));
 }
 
 extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) {
@@ -572,17 +868,46 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     if (a->graph.n_rows == 0) return YITU_OK;
     GatParams p{};
     fill_gat(p, a);
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (int rc = fill_plan(a->plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
     const int64_t D = a->n_heads * a->n_feats;
-    const int sm = 32 + 32 * p.H + 4 * 32 + p.stage;
-    if (p.head_mean) {
-        if (D <= 128) return launch_rows(gat_fwd_kernel<1, true>, p, sm, st);
-        if (D <= 256) return launch_rows(gat_fwd_kernel_r64<2, true>, p, sm, st);
-        return launch_rows(gat_fwd_kernel<4, true>, p, sm, st);
+    if (p.n_chunks > 0) {
+        const int64_t need = yitu_gat_fwd_scratch_bytes(p.n_chunks, a->n_heads, a->n_feats);
+        YITU_REQUIRE(a->scratch && a->scratch_bytes >= need && aligned16(a->scratch), YITU_ERR_WORKSPACE, "fused GAT forward with a hub plan needs %lld bytes of 16-byte aligned scratch",
+                     (long long)need);
+        p.partial = a->scratch;
     }
-    if (D <= 128) return launch_rows(gat_fwd_kernel<1, false>, p, sm, st);
-    if (D <= 256) return launch_rows(gat_fwd_kernel_r64<2, false>, p, sm, st);
-    return launch_rows(gat_fwd_kernel<4, false>, p, sm, st);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int sm = 32 + 32 * p.H + 4 * 32 + p.stage;
+    int rc;
+    if (p.head_mean) {
+        if (D <= 128) rc = launch_rows(gat_fwd_kernel<1, true>, p, sm, st);
+        else if (D <= 256) rc = launch_rows(gat_fwd_kernel_r64<2, true>, p, sm, st);
+        else rc = launch_rows(gat_fwd_kernel<4, true>, p, sm, st);
+    } else {
+        if (D <= 128) rc = launch_rows(gat_fwd_kernel<1, false>, p, sm, st);
+        else if (D <= 256) rc = launch_rows(gat_fwd_kernel_r64<2, false>, p, sm, st);
+        else rc = launch_rows(gat_fwd_kernel<4, false>, p, sm, st);
+    }
+    if (rc) return rc;
+    if (p.n_chunks > 0) {
+        gat_fwd_merge_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
+    return YITU_OK;
+}
+
+// Backward for head widths whose lanes-per-head count is not a power of two: attention recomputed per row, the three
+// destination-side passes as separate kernels (no hub schedule).
+static int gat_bwd_row_passes(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
+    const yitu_gat_args_t *a = &b->fwd;
+    const yitu_csr_t &g = a->graph;
+    const int64_t H = a->n_heads, F = a->n_feats;
+    const int shared = a->head_mean ? 1 : 0;
+    const float gscale = shared ? 1.0f / static_cast<float>(H) : 1.0f;
+    if (int rc = yitu_edge_softmax_fwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, stream)) return rc;
+    if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream)) return rc;
+    return yitu_edge_softmax_bwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, b->edge_grad, b->grad_query,
+                                     b->edge_grad, stream);
 }
 
 extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
@@ -599,20 +924,66 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
                  "grad_out / grad_x must be 16-byte aligned");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int64_t H = a->n_heads, F = a->n_feats, D = H * F;
-    // destination-side passes, each a kernel of its own (measured faster than one kernel doing all three:
-    // 1.3 + 5.5 + 1.5 ms against 9.1 ms on the 8x32 benchmark layer):
-    //   attention per edge, recomputed from query/key        -> edge_attn
-    //   d attn[e,h] = <grad_out[row,h,:], x[col,h,:]>         -> edge_grad
-    //   softmax + LeakyReLU derivatives in place              -> edge_grad = d score, grad_query
-    if (int rc = yitu_edge_softmax_fwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, stream)) return rc;
-    // with head_mean the upstream gradient is [n_rows,F]: every head sees grad_out[r,:] / H
     const int shared = a->head_mean ? 1 : 0;
     const float gscale = shared ? 1.0f / static_cast<float>(H) : 1.0f;
-    if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream)) return rc;
-    if (int rc = yitu_edge_softmax_bwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, b->edge_grad,
-                                           b->grad_query, b->edge_grad, stream))
-        return rc;
-    // source-side pass: grad_x = A^T-weighted gather of grad_out rows, grad_key = per-source sum of d score
+    const float *out_heads = shared ? a->out_heads : a->out;
+    YITU_REQUIRE(g.n_rows == 0 || out_heads, YITU_ERR_INVALID_ARG,
+                 "the backward of a head-mean forward needs fwd.out_heads (the per-head result)");
+
+    GatBwdParams p{};
+    int64_t t_chunks = 0;
+    int t_chunk_edges = 0;
+    const int *t_chunk_row = nullptr;
+    const int64_t *t_chunk_begin = nullptr;
+    if (int rc = fill_plan(a->plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
+    if (int rc = fill_plan(b->t_plan, &t_chunks, &t_chunk_edges, &t_chunk_row, &t_chunk_begin)) return rc;
+    const int64_t lph = F / 4;
+    const bool edge_parallel = lph <= 32 && (lph & (lph - 1)) == 0 && aligned16(a->x) && aligned16(out_heads);
+    if (!edge_parallel) p.n_chunks = 0;
+    float *q_partial = nullptr, *k_partial = nullptr, *spmm_scratch = nullptr;
+    if (p.n_chunks > 0 || t_chunks > 0) {
+        const int64_t need = yitu_gat_bwd_scratch_bytes(p.n_chunks, t_chunks, H, F);
+        YITU_REQUIRE(b->scratch && b->scratch_bytes >= need && aligned16(b->scratch), YITU_ERR_WORKSPACE,
+                     "fused GAT backward with hub plans needs %lld bytes of scratch", (long long)need);
+        q_partial = b->scratch;
+        k_partial = q_partial + up256f(p.n_chunks * H);
+        spmm_scratch = k_partial + up256f(t_chunks * H);
+    }
+
+    // destination side: attention, score gradient (edge_grad) and grad_query
+    if (g.n_rows > 0) {
+        if (edge_parallel) {
+            p.n_rows = g.n_rows; p.indptr = g.indptr; p.indices = g.indices; p.is64 = g.indptr_is64;
+            p.H = static_cast<int>(H); p.F = static_cast<int>(F);
+            p.hshift = (p.H & (p.H - 1)) == 0 ? 31 - __builtin_clz(p.H) : -1;
+            p.slope = a->slope; p.q = a->query; p.k = a->key; p.x = a->x; p.out_heads = out_heads;
+            p.row_max = a->row_max; p.row_sum = a->row_sum;
+            p.g = b->grad_out; p.g_shared = shared; p.g_scale = gscale;
+            p.edge_attn = b->edge_attn; p.edge_grad = b->edge_grad; p.grad_q = b->grad_query;
+            p.q_partial = q_partial;
+            const int warps = 8;
+            const size_t smem = static_cast<size_t>(warps) * (32 + 32 * p.H + 4 * 32) * sizeof(float);
+            const unsigned blocks = static_cast<unsigned>((g.n_rows + p.n_chunks + warps - 1) / warps);
+            auto run = [&](auto kernel) -> int {
+                if (smem > 48 * 1024)
+                    YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                kernel<<<blocks, warps * 32, smem, st>>>(p);
+                YITU_LAUNCH_CHECK();
+                return YITU_OK;
+            };
+            int rc = D <= 128 ? run(gat_bwd_edge_kernel<1>) : D <= 256 ? run(gat_bwd_edge_kernel<2>) : run(gat_bwd_edge_kernel<4>);
+            if (rc) return rc;
+            if (p.n_chunks > 0) {
+                chunk_sum_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(
+                    g.indptr, g.indptr_is64, p.chunk_edges, p.chunk_row, p.chunk_begin, p.H, q_partial, b->grad_query);
+                YITU_LAUNCH_CHECK();
+            }
+        } else {
+            if (int rc = gat_bwd_row_passes(b, stream)) return rc;
+        }
+    }
+    // source side: grad_x = A^T-weighted gather of grad_out rows, grad_key = per-source sum of the score gradients
+    yitu_hub_plan_t tp{};
     yitu_spmm_args_t s{};
     s.graph.n_rows = g.n_cols; s.graph.n_cols = g.n_rows; s.graph.nnz = g.nnz;
     s.graph.indptr = b->t_indptr; s.graph.indptr_is64 = g.indptr_is64; s.graph.index_mask = 0;
@@ -620,7 +991,24 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     s.n_heads = H; s.n_feats = F; s.weight_mode = YITU_W_EDGE_HEAD;
     s.edge_values = b->edge_attn; s.edge_perm = b->t_perm; s.alpha = gscale;
     s.x = b->grad_out; s.x_stride = shared ? F : D; s.x_shared_heads = shared; s.out = b->grad_x; s.out_stride = D;
+    if (t_chunks > 0) {
+        tp = *b->t_plan;
+        s.plan = &tp;
+        s.scratch = spmm_scratch;
+        s.scratch_bytes = t_chunks * D * static_cast<int64_t>(sizeof(float));
+    }
     if (int rc = yitu_spmm_csr_f32(&s, stream)) return rc;
-    return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
-                                    stream);
+    if (g.n_cols == 0) return YITU_OK;
+    if (t_chunks == 0)
+        return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
+                                        stream);
+    edge_gather_sum_plan_kernel<<<static_cast<unsigned>((g.n_cols + t_chunks + 7) / 8), 256, 0, st>>>(
+        g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, static_cast<int>(H), head_block(H), b->edge_grad, b->grad_key,
+        t_chunks, t_chunk_edges, t_chunk_row, t_chunk_begin, k_partial);
+    YITU_LAUNCH_CHECK();
+    chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(b->t_indptr, g.indptr_is64, t_chunk_edges, t_chunk_row,
+                                                                      t_chunk_begin, static_cast<int>(H), k_partial,
+                                                                      b->grad_key);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
 }

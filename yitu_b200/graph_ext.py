@@ -131,7 +131,8 @@ def gat_supported(indptr, indices, n_heads, n_feats):
 def gat_forward(indptr, indices, query, key, features, head_mean=False, activation=None):
     """[out [n_dst,H,F], row_max [n_dst,H], row_sum [n_dst,H]]: sddmm_forward + spmm_forward in one pass, for an
     unstitched graph (every segment id 0).  query [n_dst,H], key [n_src,H], features [n_src,H,F].
-    head_mean / activation fuse the layer's mean over heads (out [n_dst,F]) and the model's ReLU / ELU."""
+    head_mean / activation fuse the layer's mean over heads (out [n_dst,F]) and the model's ReLU / ELU; with
+    head_mean the list has a fourth entry, the per-head result the backward needs."""
     ops.require_cuda(indptr, "indptr", _I32)
     ops.require_cuda(indices, "indices", _I32)
     for t, n in ((query, "query"), (key, "key"), (features, "features")):
@@ -141,11 +142,12 @@ def gat_forward(indptr, indices, query, key, features, head_mean=False, activati
     return list(ops.gat_fwd(g, query, key, features, SLOPE, head_mean, activation))
 
 
-def gat_backward(indptr, indices, query, key, features, out, row_max, row_sum, grad_out, head_mean=False):
+def gat_backward(indptr, indices, query, key, features, out, row_max, row_sum, grad_out, head_mean=False,
+                 out_heads=None):
     """[grad_query, grad_key, grad_features] of gat_forward; grad_out is taken with respect to the values before
     the activation."""
     for t, n in ((query, "query"), (key, "key"), (features, "features"), (out, "out"), (row_max, "row_max"),
                  (row_sum, "row_sum"), (grad_out, "grad_out")):
         ops.require_cuda(t, n, _F32)
     g = ops.prepared(indptr, indices, features.size(0), 0)
-    return list(ops.gat_bwd(g, query, key, features, out, row_max, row_sum, grad_out, SLOPE, head_mean))
+    return list(ops.gat_bwd(g, query, key, features, out, row_max, row_sum, grad_out, SLOPE, head_mean, out_heads))

@@ -244,55 +244,91 @@ def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2):
     return grad_q, grad_k
 
 
-def _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean=False, activation=None):
+def _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean=False, activation=None, out_heads=None):
     a = GatArgs()
     a.graph = graph.csr
     a.n_heads, a.n_feats, a.slope = x.size(1), x.size(2), slope
     a.head_mean, a.activation = int(bool(head_mean)), activation_code(activation)
     a.query, a.key, a.x = _ptr(query), _ptr(key), _ptr(x)
     a.out, a.row_max, a.row_sum = _ptr(out), _ptr(row_max), _ptr(row_sum)
+    a.out_heads = _ptr(out_heads)
     return a
+
+
+def _hub_plan(graph, chunk_edges):
+    """(pointer to the HubPlan struct or None, number of chunks, objects to keep alive)."""
+    if not chunk_edges:
+        return None, 0, None
+    pl = graph.plan(chunk_edges)
+    if pl is None:
+        return None, 0, None
+    return C.pointer(pl[0]), pl[0].n_chunks, pl
 
 
 def gat_fused_supported(graph, n_heads, n_feats, backward=True):
     return graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
-def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None):
+def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None, chunk_edges=DEFAULT_CHUNK_EDGES):
     """Fused scores + edge softmax + aggregation: (out [n_rows,H,F], row_max [n_rows,H], row_sum [n_rows,H]).
-    head_mean: out is act(mean over heads), [n_rows,F], and the per-head tensor is never written."""
+    head_mean: out is act(mean over heads), [n_rows,F], and a fourth tensor comes back: the per-head result
+    [n_rows,H,F] that gat_bwd needs.  Rows longer than chunk_edges are split over several warps (0: never)."""
     H, F = x.size(1), x.size(2)
+    dev = x.device
     shape = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
-    out = torch.empty(shape, dtype=torch.float32, device=x.device)
-    row_max = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
-    row_sum = torch.empty((graph.n_rows, H), dtype=torch.float32, device=x.device)
-    a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, activation)
-    with torch.cuda.device(x.device):
-        check(lib().yitu_gat_fwd_f32(C.byref(a), _stream(x.device)))
+    out = torch.empty(shape, dtype=torch.float32, device=dev)
+    out_heads = torch.empty((graph.n_rows, H, F), dtype=torch.float32, device=dev) if head_mean else None
+    row_max = torch.empty((graph.n_rows, H), dtype=torch.float32, device=dev)
+    row_sum = torch.empty((graph.n_rows, H), dtype=torch.float32, device=dev)
+    a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, activation, out_heads)
+    plan, n_chunks, keep = _hub_plan(graph, chunk_edges)
+    L = lib()
+    if plan is not None:
+        nbytes = L.yitu_gat_fwd_scratch_bytes(n_chunks, H, F)
+        scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
+        a.plan, a.scratch, a.scratch_bytes = plan, _ptr(scratch), nbytes
+    with torch.cuda.device(dev):
+        check(L.yitu_gat_fwd_f32(C.byref(a), _stream(dev)))
+    del keep
+    if head_mean:
+        return out, row_max, row_sum, out_heads
     return out, row_max, row_sum
 
 
-def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, head_mean=False):
+def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, head_mean=False, out_heads=None,
+            chunk_edges=DEFAULT_CHUNK_EDGES):
     """(grad_query, grad_key, grad_x) of gat_fwd; grad_out is the gradient of the pre-activation output
-    ([n_rows,F] with head_mean)."""
-    H = x.size(1)
-    expect = (graph.n_rows, x.size(2)) if head_mean else (graph.n_rows, H, x.size(2))
+    ([n_rows,F] with head_mean, which also needs out_heads, the fourth result of gat_fwd)."""
+    H, F = x.size(1), x.size(2)
+    dev = x.device
+    expect = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
     if tuple(grad_out.shape) != expect or not grad_out.is_contiguous():
         raise RuntimeError("grad_out must be contiguous with shape %s, got %s" % (expect, tuple(grad_out.shape)))
+    if head_mean and out_heads is None:
+        raise RuntimeError("the backward of a head-mean forward needs out_heads (the fourth result of gat_fwd)")
     t_indptr, t_rows, t_perm = graph.transpose()
     b = GatBwdArgs()
-    b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean)
+    b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, None, out_heads)
     grad_q = torch.empty_like(query)
     grad_k = torch.empty_like(key)
     grad_x = torch.empty_like(x)
-    edge_attn = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
-    edge_grad = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
+    edge_attn = torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
+    edge_grad = torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
     b.grad_out = _ptr(grad_out)
     b.t_indptr, b.t_rows, b.t_perm = _ptr(t_indptr), _ptr(t_rows), _ptr(t_perm)
     b.grad_query, b.grad_key, b.grad_x = _ptr(grad_q), _ptr(grad_k), _ptr(grad_x)
     b.edge_attn, b.edge_grad = _ptr(edge_attn), _ptr(edge_grad)
-    with torch.cuda.device(x.device):
-        check(lib().yitu_gat_bwd_f32(C.byref(b), _stream(x.device)))
+    plan, n_chunks, keep = _hub_plan(graph, chunk_edges)
+    t_plan, t_chunks, t_keep = _hub_plan(graph.t_prepared(), chunk_edges)
+    L = lib()
+    if plan is not None or t_plan is not None:
+        nbytes = L.yitu_gat_bwd_scratch_bytes(n_chunks, t_chunks, H, F)
+        scratch = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=dev)
+        b.fwd.plan, b.t_plan = plan, t_plan
+        b.scratch, b.scratch_bytes = _ptr(scratch), nbytes
+    with torch.cuda.device(dev):
+        check(L.yitu_gat_bwd_f32(C.byref(b), _stream(dev)))
+    del keep, t_keep
     return grad_q, grad_k, grad_x
 
 

@@ -100,9 +100,10 @@ class FusedGATFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, adj_sparse, query, key, x, head_mean=False, activation=None):
-        out, row_max, row_sum = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x, head_mean,
-                                                      activation)
+        res = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x, head_mean, activation)
+        out, row_max, row_sum = res[:3]
         ctx.adj_sparse, ctx.head_mean, ctx.activation = adj_sparse, head_mean, activation
+        ctx.out_heads = res[3] if head_mean else None
         ctx.save_for_backward(query, key, x, out, row_max, row_sum)
         return out
 
@@ -113,7 +114,7 @@ class FusedGATFunction(autograd.Function):
         if ctx.activation is not None:
             grad_out = ops.epilogue_grad(out, grad_out, None, ctx.activation)
         gq, gk, gx = graph_ext.gat_backward(ctx.adj_sparse[0], ctx.adj_sparse[1], query, key, x, out, row_max,
-                                            row_sum, grad_out, ctx.head_mean)
+                                            row_sum, grad_out, ctx.head_mean, ctx.out_heads)
         return None, gq, gk, gx, None, None
 
 
