@@ -188,11 +188,24 @@ edge_dot_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices
 template <int NV>
 __global__ void __launch_bounds__(256)
 edge_dot_rows_kernel(int64_t n_rows, const void *indptr, int is64, const int *indices, int mask, int H, int F,
-                     const float *g, int g_shared, float g_scale, const float *x, float *grad_a) {
+                     const float *g, int g_shared, float g_scale, const float *x, float *grad_a, int64_t n_chunks,
+                     int chunk_edges, const int *chunk_row, const int64_t *chunk_begin) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
-    if (row >= n_rows) return;
+    // the first n_chunks warps take the chunks of the hub rows (every edge is independent: nothing to merge)
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
+    int64_t row, eb, ee;
+    if (gid < n_chunks) {
+        row = __ldg(chunk_row + gid);
+        eb = __ldg(chunk_begin + gid);
+        ee = min(eb + static_cast<int64_t>(chunk_edges), load_ptr(indptr, is64, row + 1));
+    } else {
+        row = gid - n_chunks;
+        if (row >= n_rows) return;
+        eb = load_ptr(indptr, is64, row);
+        ee = load_ptr(indptr, is64, row + 1);
+        if (n_chunks > 0 && ee - eb > chunk_edges) return;
+    }
     float *base = smem + wib * (32 + 32 * H);
     int *s_col = reinterpret_cast<int *>(base);
     float *s_out = base + 32;
@@ -214,7 +227,6 @@ edge_dot_rows_kernel(int64_t n_rows, const void *indptr, int is64, const int *in
             gr[i].x *= g_scale; gr[i].y *= g_scale; gr[i].z *= g_scale; gr[i].w *= g_scale;
         }
     }
-    const int64_t eb = load_ptr(indptr, is64, row), ee = load_ptr(indptr, is64, row + 1);
     for (int64_t e0 = eb; e0 < ee; e0 += 32) {
         const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
         int my_col = lane < n ? ld_stream(indices + e0 + lane) : 0;
@@ -509,11 +521,13 @@ __global__ void __launch_bounds__(128) gat_fwd_merge_kernel(const __grid_constan
 // Fused GAT backward, destination side.  With the forward's row statistics (max M, sum L) the attention of an edge
 // is p = exp(LeakyReLU(q+k) - M) / L on its own, and sum_e p_e * dp_e over a row equals Dv = <grad_out, out> of that
 // row, so every edge is independent:
-//   dp = <grad_out[row,h,:], x[col,h,:]>,  d score = p * (dp - Dv) * LeakyReLU'(q+k).
-// One warp per row (or hub chunk): the row of grad_out stays in registers, source rows are gathered with 128-bit loads
-// (two edges in flight), a 32-edge tile of dp lands in shared memory, then the lanes spread over (edge, head) pairs
-// and write attention and score gradient coalesced.  grad_query is the row sum of the score gradients (chunks leave
-// partial sums that chunk_sum_kernel adds in order).
+//   dp = <grad_out[row,h,:], x[col,h,:]>   (edge_dot_rows_kernel: the gather pass, at the DRAM roofline)
+//   d score = p * (dp - Dv) * LeakyReLU'(q+k)   (gat_bwd_score_kernel: streams dp, writes attention and d score in
+//                                                place, sums d score per row into grad_query)
+// A single kernel doing both passes was measured slower (9.0 ms against 5.6 + 2.2 ms on the 8x32 layer): its register
+// count costs the gather pass a fifth of its warps.  The score pass is latency bound (a short dependent chain per row),
+// so it is held to 48 registers for five CTAs per SM (2.9 ms at 64 registers).  Hub rows are processed as chunks; chunk_sum_kernel adds the
+// chunks' grad_query partials in order.
 // ---------------------------------------------------------------------------------------------------------
 struct GatBwdParams {
     int64_t n_rows;
@@ -521,11 +535,11 @@ struct GatBwdParams {
     const int *indices;
     int is64, H, F, hshift;
     float slope;
-    const float *q, *k, *x, *out_heads, *row_max, *row_sum;
+    const float *q, *k, *out_heads, *row_max, *row_sum;
     const float *g;  // upstream gradient: [n_rows,H,F], or [n_rows,F] shared by the heads (g_shared), times g_scale
     int g_shared;
     float g_scale;
-    float *edge_attn, *edge_grad, *grad_q;
+    float *edge_attn, *edge_grad, *grad_q;  // edge_grad holds dp on entry, d score on exit
     int64_t n_chunks;
     int chunk_edges;
     const int *chunk_row;
@@ -533,8 +547,7 @@ struct GatBwdParams {
     float *q_partial;  // [n_chunks, H]
 };
 
-template <int NV>
-__global__ void __launch_bounds__(256) gat_bwd_edge_kernel(const __grid_constant__ GatBwdParams p) {
+__global__ void __launch_bounds__(256, 5) gat_bwd_score_kernel(const __grid_constant__ GatBwdParams p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
@@ -553,7 +566,7 @@ __global__ void __launch_bounds__(256) gat_bwd_edge_kernel(const __grid_constant
     }
     const int H = p.H, F = p.F;
     const int64_t D = static_cast<int64_t>(H) * F;
-    const int LPH = F >> 2;  // lanes per head (a power of two)
+    const bool pow2 = p.hshift >= 0;  // then a lane always meets the same head: idx % H == lane % H
     float *base = smem + wib * (32 + 32 * H + 4 * 32);
     int *s_col = reinterpret_cast<int *>(base);
     float *s_v = base + 32;
@@ -564,72 +577,84 @@ __global__ void __launch_bounds__(256) gat_bwd_edge_kernel(const __grid_constant
         const float l = __ldg(p.row_sum + row * H + lane);
         s_il[lane] = l > 0.0f ? 1.0f / l : 0.0f;
     }
-    int hd[NV];
-    bool valid[NV];
-    int64_t off[NV];
-    float4 gr[NV];
+    // Dv[h] = <grad_out[row,h,:], out[row,h,:]>
+    const int LPH = F >> 2;
+    if ((F & 3) == 0 && LPH <= 32 && (LPH & (LPH - 1)) == 0 && D <= 512) {
+        // 128-bit slices, all requested before the first use; a head's lanes are adjacent: butterfly inside the head
+        float d[4];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        off[i] = static_cast<int64_t>(i * 32 + lane) * 4;
-        valid[i] = off[i] < D;
-        hd[i] = valid[i] ? static_cast<int>(off[i] / F) : 0;
-        gr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        float d = 0.0f;
-        if (valid[i]) {
-            const float *gp = p.g_shared ? p.g + row * F + (off[i] - static_cast<int64_t>(hd[i]) * F) : p.g + row * D + off[i];
-            gr[i] = __ldg(reinterpret_cast<const float4 *>(gp));
-            gr[i].x *= p.g_scale; gr[i].y *= p.g_scale; gr[i].z *= p.g_scale; gr[i].w *= p.g_scale;
-            const float4 o = __ldg(reinterpret_cast<const float4 *>(p.out_heads + row * D + off[i]));
-            d = gr[i].x * o.x + gr[i].y * o.y + gr[i].z * o.z + gr[i].w * o.w;
+        for (int i = 0; i < 4; ++i) {
+            const int64_t off = static_cast<int64_t>(i * 32 + lane) * 4;
+            d[i] = 0.0f;
+            if (off < D) {
+                const int64_t goff = p.g_shared ? off % F : off;
+                const float4 gv = __ldg(reinterpret_cast<const float4 *>(p.g + row * (p.g_shared ? F : D) + goff));
+                const float4 ov = __ldg(reinterpret_cast<const float4 *>(p.out_heads + row * D + off));
+                d[i] = gv.x * ov.x + gv.y * ov.y + gv.z * ov.z + gv.w * ov.w;
+            }
         }
-        for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-        if (valid[i] && (lane & (LPH - 1)) == 0) s_d[hd[i]] = d;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t off = static_cast<int64_t>(i * 32 + lane) * 4;
+            for (int o = LPH >> 1; o > 0; o >>= 1) d[i] += __shfl_xor_sync(0xffffffffu, d[i], o);
+            if (off < D && (lane & (LPH - 1)) == 0) s_d[off / F] = d[i] * p.g_scale;
+        }
+    } else {
+        for (int h = 0; h < H; ++h) {
+            const float *gp = p.g_shared ? p.g + row * F : p.g + row * D + static_cast<int64_t>(h) * F;
+            const float *op = p.out_heads + row * D + static_cast<int64_t>(h) * F;
+            float d = 0.0f;
+            for (int k = lane; k < F; k += 32) d = fmaf(__ldg(gp + k), __ldg(op + k), d);
+            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            if (lane == 0) s_d[h] = d * p.g_scale;
+        }
     }
     __syncwarp();
-    float gq = 0.0f;  // lane h owns head h
+    float gq = 0.0f;  // pow2: the lane's own pairs (head lane % H); otherwise lane h owns head h
     for (int64_t e0 = eb; e0 < ee; e0 += 32) {
         const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
-        const int my_col = lane < n ? ld_stream(p.indices + e0 + lane) : 0;
-        const int c_first = __shfl_sync(0xffffffffu, my_col, 0);
-        s_col[lane] = lane < n ? my_col : c_first;
-        __syncwarp();
-        const int n2 = (n + 1) & ~1;
-        for (int j = 0; j < n2; j += 2) {
-            float4 v[2][NV];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const float *xr = p.x + static_cast<int64_t>(s_col[j + u]) * D;
-#pragma unroll
-                for (int i = 0; i < NV; ++i)
-                    v[u][i] = valid[i] ? __ldg(reinterpret_cast<const float4 *>(xr + off[i]))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u)
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    float d = gr[i].x * v[u][i].x + gr[i].y * v[u][i].y + gr[i].z * v[u][i].z + gr[i].w * v[u][i].w;
-                    for (int s = LPH >> 1; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
-                    if (valid[i] && (lane & (LPH - 1)) == 0 && j + u < n) s_v[(j + u) * H + hd[i]] = d;
-                }
-        }
+        s_col[lane] = lane < n ? ld_stream(p.indices + e0 + lane) : 0;
         __syncwarp();
         const int npairs = n * H;
-        for (int idx = lane; idx < npairs; idx += 32) {
-            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
-            const int h = idx - e * H;
-            const float sc = s_q[h] + __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + h);
-            const float pr = expf(leaky_relu(sc, p.slope) - s_m[h]) * s_il[h];
-            const float ds = pr * (s_v[idx] - s_d[h]) * (sc < 0.0f ? p.slope : 1.0f);
-            p.edge_attn[e0 * H + idx] = pr;
-            p.edge_grad[e0 * H + idx] = ds;
-            s_v[idx] = ds;
+        // eight (edge, head) pairs per lane and step: their dp and key loads are all issued before the first result is
+        // stored (the stores go to the array the dp values come from, which would otherwise order every load behind them)
+        for (int idx0 = lane; idx0 < npairs; idx0 += 256) {
+            float dpv[8], kv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = idx0 + 32 * u;
+                dpv[u] = kv[u] = 0.0f;
+                if (idx < npairs) {
+                    const int e = pow2 ? (idx >> p.hshift) : (idx / H);
+                    dpv[u] = p.edge_grad[e0 * H + idx];
+                    kv[u] = __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + (idx - e * H));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = idx0 + 32 * u;
+                if (idx < npairs) {
+                    const int e = pow2 ? (idx >> p.hshift) : (idx / H);
+                    const int h = idx - e * H;
+                    const float sc = s_q[h] + kv[u];
+                    const float pr = expf(leaky_relu(sc, p.slope) - s_m[h]) * s_il[h];
+                    const float ds = pr * (dpv[u] - s_d[h]) * (sc < 0.0f ? p.slope : 1.0f);
+                    p.edge_attn[e0 * H + idx] = pr;
+                    p.edge_grad[e0 * H + idx] = ds;
+                    if (pow2) gq += ds;
+                    else s_v[idx] = ds;
+                }
+            }
+        }
+        if (!pow2) {
+            __syncwarp();
+            if (lane < H)
+                for (int e = 0; e < n; ++e) gq += s_v[e * H + lane];
         }
         __syncwarp();
-        if (lane < H)
-            for (int e = 0; e < n; ++e) gq += s_v[e * H + lane];
-        __syncwarp();
     }
+    if (pow2)  // lanes lane, lane + H, lane + 2H, ... hold partial sums of head lane % H
+        for (int o = H; o < 32; o <<= 1) gq += __shfl_xor_sync(0xffffffffu, gq, o);
     if (lane < H) {
         if (chunk) p.q_partial[gid * H + lane] = gq;
         else p.grad_q[row * H + lane] = gq;
@@ -756,7 +781,8 @@ extern "C" int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, in
 // grad_shared: grad_out is [n_rows,F] and stands for every head (scaled by grad_scale) — the gradient of a mean
 // over heads.
 static int edge_dot_impl(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out, int grad_shared,
-                         float grad_scale, const float *x, float *grad_a, yitu_stream_t stream) {
+                         float grad_scale, const float *x, float *grad_a, yitu_stream_t stream, int64_t n_chunks = 0,
+                         int chunk_edges = 0, const int *chunk_row = nullptr, const int64_t *chunk_begin = nullptr) {
     if (int rc = validate_csr(g)) return rc;
     YITU_REQUIRE(n_heads >= 1 && n_feats >= 1, YITU_ERR_INVALID_ARG, "bad shape");
     if (g->n_rows == 0 || g->nnz == 0) return YITU_OK;
@@ -769,11 +795,13 @@ static int edge_dot_impl(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, 
     if (fast) {
         const int H = static_cast<int>(n_heads), F = static_cast<int>(n_feats);
         const size_t smem = 8 * (32 + 32 * static_cast<size_t>(H)) * sizeof(float);
+        const unsigned blocks_plan = static_cast<unsigned>((g->n_rows + n_chunks + 7) / 8);
         auto run = [&](auto kernel) -> int {
             if (smem > 48 * 1024)
                 YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            kernel<<<blocks, 256, smem, st>>>(g->n_rows, g->indptr, g->indptr_is64, g->indices, g->index_mask, H, F,
-                                              grad_out, grad_shared, grad_scale, x, grad_a);
+            kernel<<<blocks_plan, 256, smem, st>>>(g->n_rows, g->indptr, g->indptr_is64, g->indices, g->index_mask, H, F,
+                                                   grad_out, grad_shared, grad_scale, x, grad_a, n_chunks, chunk_edges,
+                                                   chunk_row, chunk_begin);
             YITU_LAUNCH_CHECK();
             return YITU_OK;
         };
@@ -896,20 +924,6 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     return YITU_OK;
 }
 
-// Backward for head widths whose lanes-per-head count is not a power of two: attention recomputed per row, the three
-// destination-side passes as separate kernels (no hub schedule).
-static int gat_bwd_row_passes(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
-    const yitu_gat_args_t *a = &b->fwd;
-    const yitu_csr_t &g = a->graph;
-    const int64_t H = a->n_heads, F = a->n_feats;
-    const int shared = a->head_mean ? 1 : 0;
-    const float gscale = shared ? 1.0f / static_cast<float>(H) : 1.0f;
-    if (int rc = yitu_edge_softmax_fwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, stream)) return rc;
-    if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream)) return rc;
-    return yitu_edge_softmax_bwd_f32(&g, 1, H, a->slope, a->query, a->key, b->edge_attn, b->edge_grad, b->grad_query,
-                                     b->edge_grad, stream);
-}
-
 extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
     YITU_REQUIRE(b != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
     const yitu_gat_args_t *a = &b->fwd;
@@ -937,9 +951,6 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     const int64_t *t_chunk_begin = nullptr;
     if (int rc = fill_plan(a->plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
     if (int rc = fill_plan(b->t_plan, &t_chunks, &t_chunk_edges, &t_chunk_row, &t_chunk_begin)) return rc;
-    const int64_t lph = F / 4;
-    const bool edge_parallel = lph <= 32 && (lph & (lph - 1)) == 0 && aligned16(a->x) && aligned16(out_heads);
-    if (!edge_parallel) p.n_chunks = 0;
     float *q_partial = nullptr, *k_partial = nullptr, *spmm_scratch = nullptr;
     if (p.n_chunks > 0 || t_chunks > 0) {
         const int64_t need = yitu_gat_bwd_scratch_bytes(p.n_chunks, t_chunks, H, F);
@@ -950,36 +961,30 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
         spmm_scratch = k_partial + up256f(t_chunks * H);
     }
 
-    // destination side: attention, score gradient (edge_grad) and grad_query
+    // destination side: dp into edge_grad, then attention, score gradient (in place) and grad_query
     if (g.n_rows > 0) {
-        if (edge_parallel) {
-            p.n_rows = g.n_rows; p.indptr = g.indptr; p.indices = g.indices; p.is64 = g.indptr_is64;
-            p.H = static_cast<int>(H); p.F = static_cast<int>(F);
-            p.hshift = (p.H & (p.H - 1)) == 0 ? 31 - __builtin_clz(p.H) : -1;
-            p.slope = a->slope; p.q = a->query; p.k = a->key; p.x = a->x; p.out_heads = out_heads;
-            p.row_max = a->row_max; p.row_sum = a->row_sum;
-            p.g = b->grad_out; p.g_shared = shared; p.g_scale = gscale;
-            p.edge_attn = b->edge_attn; p.edge_grad = b->edge_grad; p.grad_q = b->grad_query;
-            p.q_partial = q_partial;
-            const int warps = 8;
-            const size_t smem = static_cast<size_t>(warps) * (32 + 32 * p.H + 4 * 32) * sizeof(float);
-            const unsigned blocks = static_cast<unsigned>((g.n_rows + p.n_chunks + warps - 1) / warps);
-            auto run = [&](auto kernel) -> int {
-                if (smem > 48 * 1024)
-                    YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-                kernel<<<blocks, warps * 32, smem, st>>>(p);
-                YITU_LAUNCH_CHECK();
-                return YITU_OK;
-            };
-            int rc = D <= 128 ? run(gat_bwd_edge_kernel<1>) : D <= 256 ? run(gat_bwd_edge_kernel<2>) : run(gat_bwd_edge_kernel<4>);
-            if (rc) return rc;
-            if (p.n_chunks > 0) {
-                chunk_sum_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(
-                    g.indptr, g.indptr_is64, p.chunk_edges, p.chunk_row, p.chunk_begin, p.H, q_partial, b->grad_query);
-                YITU_LAUNCH_CHECK();
-            }
-        } else {
-            if (int rc = gat_bwd_row_passes(b, stream)) return rc;
+        if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream, p.n_chunks,
+                                   p.chunk_edges, p.chunk_row, p.chunk_begin))
+            return rc;
+        p.n_rows = g.n_rows; p.indptr = g.indptr; p.indices = g.indices; p.is64 = g.indptr_is64;
+        p.H = static_cast<int>(H); p.F = static_cast<int>(F);
+        p.hshift = (p.H & (p.H - 1)) == 0 ? 31 - __builtin_clz(p.H) : -1;
+        p.slope = a->slope; p.q = a->query; p.k = a->key; p.out_heads = out_heads;
+        p.row_max = a->row_max; p.row_sum = a->row_sum;
+        p.g = b->grad_out; p.g_shared = shared; p.g_scale = gscale;
+        p.edge_attn = b->edge_attn; p.edge_grad = b->edge_grad; p.grad_q = b->grad_query;
+        p.q_partial = q_partial;
+        const int warps = 8;
+        const size_t smem = static_cast<size_t>(warps) * (32 + 32 * p.H + 4 * 32) * sizeof(float);
+        if (smem > 48 * 1024)
+            YITU_CUDA(cudaFuncSetAttribute(gat_bwd_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)));
+        gat_bwd_score_kernel<<<static_cast<unsigned>((g.n_rows + p.n_chunks + warps - 1) / warps), warps * 32, smem, st>>>(p);
+        YITU_LAUNCH_CHECK();
+        if (p.n_chunks > 0) {
+            chunk_sum_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(
+                g.indptr, g.indptr_is64, p.chunk_edges, p.chunk_row, p.chunk_begin, p.H, q_partial, b->grad_query);
+            YITU_LAUNCH_CHECK();
         }
     }
     // source side: grad_x = A^T-weighted gather of grad_out rows, grad_key = per-source sum of the score gradients
