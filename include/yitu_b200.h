@@ -226,25 +226,30 @@ int yitu_segment_mean_weights_f32(const yitu_csr_t *g, float *values, yitu_strea
 /* grad_a[e,h] = sum_k g[row_e,h,k] * x[col_e,h,k] — the edge-value half of
  * YiTu_GNN/YiTu_H/src/spmm_cuda.cu:24-42, without atomics (one owner per (e,h)). */
 int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out, const float *x,
-                      float *grad_a, yitu_stream_t stream);
+                      float *grad_a, const yitu_hub_plan_t *plan, yitu_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------- GAT */
+/* The `plan` argument of the functions below is the optional hub-row schedule of the graph they walk (the transposed
+ * graph's for yitu_edge_gather_sum_f32): with it, rows longer than plan->chunk_edges are processed by a whole CTA, or
+ * chunk by chunk, instead of by one warp.  NULL keeps one warp per row. */
 /* attn[e,h] = softmax over {edges of the same row and segment} of LeakyReLU_slope(query[seg,row,h] + key[col,h]).
  * Replaces sddmm_forward (YiTu_GNN/YiTu_H/src/sddmm_cuda.cu:5-33,69-89).  Unlike the reference the row maximum
  * is subtracted before exponentiation (same value, no overflow).  n_segments = query.size(0) (<= 16). */
 int yitu_edge_softmax_fwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
-                              const float *query, const float *key, float *attn, yitu_stream_t stream);
+                              const float *query, const float *key, float *attn, const yitu_hub_plan_t *plan,
+                              yitu_stream_t stream);
 
 /* Replaces sddmm_backward (sddmm_cuda.cu:36-67,91-118): writes grad_query[seg,row,h] (every entry, zeros
  * included) and edge_grad[e,h] = d loss / d (query+key) per edge; grad_key is then the per-source sum of
  * edge_grad, taken with yitu_edge_gather_sum_f32 over the transposed graph (no atomics). */
 int yitu_edge_softmax_bwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
                               const float *query, const float *key, const float *attn, const float *grad_attn,
-                              float *grad_query, float *edge_grad, yitu_stream_t stream);
+                              float *grad_query, float *edge_grad, const yitu_hub_plan_t *plan, yitu_stream_t stream);
 
 /* out[c,h] = sum_{j in column c of the transposed graph} edge_vals[t_perm[j], h] */
 int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indptr_is64, const int32_t *t_perm,
-                             int64_t n_heads, const float *edge_vals, float *out, yitu_stream_t stream);
+                             int64_t n_heads, const float *edge_vals, float *out, const yitu_hub_plan_t *t_plan,
+                             yitu_stream_t stream);
 
 /* Fused GAT layer core: scores, LeakyReLU, edge softmax (online maximum/sum) and the weighted aggregation in
  * one pass over each row's edges — the composition sddmm_forward + spmm_forward of the reference

@@ -77,11 +77,12 @@ SYMBOLS = {
     "yitu_spmm_csr_f32_static": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
     "yitu_epilogue_grad_f32": (C.c_int, [c_i64, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "yitu_segment_mean_weights_f32": (C.c_int, [C.POINTER(Csr), c_vp, c_vp]),
-    "yitu_edge_dot_f32": (C.c_int, [C.POINTER(Csr), c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
-    "yitu_edge_softmax_fwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp]),
-    "yitu_edge_softmax_bwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+    "yitu_edge_dot_f32": (C.c_int, [C.POINTER(Csr), c_i64, c_i64, c_vp, c_vp, c_vp, C.POINTER(HubPlan), c_vp]),
+    "yitu_edge_softmax_fwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, C.POINTER(HubPlan),
                                             c_vp]),
-    "yitu_edge_gather_sum_f32": (C.c_int, [c_i64, c_vp, c_i32, c_vp, c_i64, c_vp, c_vp, c_vp]),
+    "yitu_edge_softmax_bwd_f32": (C.c_int, [C.POINTER(Csr), c_i32, c_i64, c_f32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                            C.POINTER(HubPlan), c_vp]),
+    "yitu_edge_gather_sum_f32": (C.c_int, [c_i64, c_vp, c_i32, c_vp, c_i64, c_vp, c_vp, C.POINTER(HubPlan), c_vp]),
     "yitu_gat_fwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64]),
     "yitu_gat_bwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64, c_i64]),
     "yitu_gat_fwd_f32": (C.c_int, [C.POINTER(GatArgs), c_vp]),

@@ -30,16 +30,58 @@ struct SoftmaxParams {
     float slope;
     const float *q, *k, *attn_in, *grad_attn;
     float *attn_out, *grad_q, *edge_grad;
+    // optional hub schedule: rows longer than chunk_edges are left to the CTA-per-row variants below
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
 };
 
+// Row assignment shared by the stand-alone kernels.  CTA = false: one warp per row, hub rows skipped when a schedule
+// is given.  CTA = true: one 256-thread CTA per hub row (launched with one CTA per chunk; the CTAs of a row's later
+// chunks leave at once), its 256/HB edge slots advancing together.
+template <bool CTA>
+__device__ __forceinline__ bool softmax_row(const SoftmaxParams &p, int64_t &row, int64_t &eb, int64_t &ee) {
+    if constexpr (CTA) {
+        row = __ldg(p.chunk_row + blockIdx.x);
+        eb = load_ptr(p.indptr, p.is64, row);
+        if (__ldg(p.chunk_begin + blockIdx.x) != eb) return false;
+        ee = load_ptr(p.indptr, p.is64, row + 1);
+        return true;
+    } else {
+        row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+        if (row >= p.n_rows) return false;
+        eb = load_ptr(p.indptr, p.is64, row);
+        ee = load_ptr(p.indptr, p.is64, row + 1);
+        return !(p.n_chunks > 0 && ee - eb > p.chunk_edges);
+    }
+}
+
+// Sum over the edge slots that share a head lane: shuffles inside the warp, then (CTA) across the 8 warps through
+// shared memory, every thread adding the 8 values in the same order.
+template <bool CTA>
+__device__ __forceinline__ float slot_sum(float v, int HB, float *s_red) {
+    for (int o = HB; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if constexpr (CTA) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, hs = lane & (HB - 1);
+        __syncthreads();
+        if (lane < HB) s_red[warp * 32 + hs] = v;
+        __syncthreads();
+        v = 0.0f;
+        for (int w = 0; w < 8; ++w) v += s_red[w * 32 + hs];
+    }
+    return v;
+}
+
+template <bool CTA>
 __global__ void __launch_bounds__(256) edge_softmax_fwd_kernel(const __grid_constant__ SoftmaxParams p) {
-    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (row >= p.n_rows) return;
+    __shared__ float s_red[CTA ? 2 * 8 * 32 : 1];
+    int64_t row, eb, ee;
+    if (!softmax_row<CTA>(p, row, eb, ee)) return;
     const int lane = threadIdx.x & 31;
     const int hs = lane & (p.HB - 1);
-    const int slot = lane >> pow2_shift(p.HB);
-    const int ES = 32 / p.HB;
-    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    const int slot = (CTA ? threadIdx.x : lane) >> pow2_shift(p.HB);
+    const int ES = (CTA ? 256 : 32) / p.HB;
     for (int s = 0; s < p.B; ++s) {
         for (int hc = 0; hc < p.H; hc += p.HB) {
             const int h = hc + hs;
@@ -66,6 +108,22 @@ __global__ void __launch_bounds__(256) edge_softmax_fwd_kernel(const __grid_cons
                 if (M > -CUDART_INF_F) l = l * expf(m - M) + l2 * expf(m2 - M);
                 m = M;
             }
+            if constexpr (CTA) {
+                const int warp = threadIdx.x >> 5;
+                __syncthreads();
+                if (lane < p.HB) {
+                    s_red[warp * 32 + hs] = m;
+                    s_red[256 + warp * 32 + hs] = l;
+                }
+                __syncthreads();
+                float M = -CUDART_INF_F;
+                for (int w = 0; w < 8; ++w) M = fmaxf(M, s_red[w * 32 + hs]);
+                float L = 0.0f;
+                if (M > -CUDART_INF_F)
+                    for (int w = 0; w < 8; ++w) L += s_red[256 + w * 32 + hs] * expf(s_red[w * 32 + hs] - M);
+                m = M;
+                l = L;
+            }
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             for (int64_t e = eb + slot; e < ee; e += ES) {
                 const int raw = __ldg(p.indices + e);
@@ -79,14 +137,15 @@ __global__ void __launch_bounds__(256) edge_softmax_fwd_kernel(const __grid_cons
     }
 }
 
+template <bool CTA>
 __global__ void __launch_bounds__(256) edge_softmax_bwd_kernel(const __grid_constant__ SoftmaxParams p) {
-    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (row >= p.n_rows) return;
+    __shared__ float s_red[CTA ? 8 * 32 : 1];
+    int64_t row, eb, ee;
+    if (!softmax_row<CTA>(p, row, eb, ee)) return;
     const int lane = threadIdx.x & 31;
     const int hs = lane & (p.HB - 1);
-    const int slot = lane >> pow2_shift(p.HB);
-    const int ES = 32 / p.HB;
-    const int64_t eb = load_ptr(p.indptr, p.is64, row), ee = load_ptr(p.indptr, p.is64, row + 1);
+    const int slot = (CTA ? threadIdx.x : lane) >> pow2_shift(p.HB);
+    const int ES = (CTA ? 256 : 32) / p.HB;
     for (int s = 0; s < p.B; ++s) {
         for (int hc = 0; hc < p.H; hc += p.HB) {
             const int h = hc + hs;
@@ -99,7 +158,7 @@ __global__ void __launch_bounds__(256) edge_softmax_bwd_kernel(const __grid_cons
                 if (bid != s || !hv) continue;
                 t = fmaf(__ldg(p.attn_in + e * p.H + h), __ldg(p.grad_attn + e * p.H + h), t);
             }
-            for (int o = p.HB; o < 32; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            t = slot_sum<CTA>(t, p.HB, s_red);
             float gq = 0.0f;
             for (int64_t e = eb + slot; e < ee; e += ES) {
                 const int raw = __ldg(p.indices + e);
@@ -113,23 +172,50 @@ __global__ void __launch_bounds__(256) edge_softmax_bwd_kernel(const __grid_cons
                 p.edge_grad[e * p.H + h] = gv;
                 gq += gv;
             }
-            for (int o = p.HB; o < 32; o <<= 1) gq += __shfl_xor_sync(0xffffffffu, gq, o);
+            gq = slot_sum<CTA>(gq, p.HB, s_red);
             if (slot == 0 && hv) p.grad_q[(static_cast<int64_t>(s) * p.n_rows + row) * p.H + h] = gq;
         }
     }
 }
 
 // out[c,h] = sum over column c of the transposed graph of vals[perm[j], h]
-__global__ void __launch_bounds__(256)
-edge_gather_sum_kernel(int64_t n_cols, const void *t_indptr, int is64, const int *perm, int H, int HB,
-                       const float *vals, float *out) {
-    const int64_t c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    if (c >= n_cols) return;
+struct GatherSumParams {
+    int64_t n_cols;
+    const void *t_indptr;
+    int is64;
+    const int *perm;
+    int H, HB;
+    const float *vals;
+    float *out;
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+};
+
+template <bool CTA>
+__global__ void __launch_bounds__(256) edge_gather_sum_kernel(const __grid_constant__ GatherSumParams p) {
+    __shared__ float s_red[CTA ? 8 * 32 : 1];
+    int64_t c, b, e;
+    if constexpr (CTA) {
+        c = __ldg(p.chunk_row + blockIdx.x);
+        b = load_ptr(p.t_indptr, p.is64, c);
+        if (__ldg(p.chunk_begin + blockIdx.x) != b) return;
+        e = load_ptr(p.t_indptr, p.is64, c + 1);
+    } else {
+        c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+        if (c >= p.n_cols) return;
+        b = load_ptr(p.t_indptr, p.is64, c);
+        e = load_ptr(p.t_indptr, p.is64, c + 1);
+        if (p.n_chunks > 0 && e - b > p.chunk_edges) return;
+    }
     const int lane = threadIdx.x & 31;
+    const int H = p.H, HB = p.HB;
     const int hs = lane & (HB - 1);
-    const int slot = lane >> pow2_shift(HB);
-    const int ES = 32 / HB;
-    const int64_t b = load_ptr(t_indptr, is64, c), e = load_ptr(t_indptr, is64, c + 1);
+    const int slot = (CTA ? threadIdx.x : lane) >> pow2_shift(HB);
+    const int ES = (CTA ? 256 : 32) / HB;
+    const int *perm = p.perm;
+    const float *vals = p.vals;
     for (int hc = 0; hc < H; hc += HB) {
         const int h = hc + hs;
         float a = 0.0f;
@@ -144,8 +230,8 @@ edge_gather_sum_kernel(int64_t n_cols, const void *t_indptr, int is64, const int
             }
             for (; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
         }
-        for (int o = HB; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (slot == 0 && h < H) out[c * H + h] = a;
+        a = slot_sum<CTA>(a, HB, s_red);
+        if (slot == 0 && h < H) p.out[c * H + h] = a;
     }
 }
 
@@ -677,42 +763,6 @@ chunk_sum_kernel(const void *indptr, int is64, int chunk_edges, const int *chunk
     }
 }
 
-// edge_gather_sum over a transposed graph with hub sources: chunks leave partial sums
-__global__ void __launch_bounds__(256)
-edge_gather_sum_plan_kernel(int64_t n_cols, const void *t_indptr, int is64, const int *perm, int H, int HB,
-                            const float *vals, float *out, int64_t n_chunks, int chunk_edges, const int *chunk_row,
-                            const int64_t *chunk_begin, float *partial) {
-    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    int64_t c, b, e;
-    const bool chunk = gid < n_chunks;
-    if (chunk) {
-        c = __ldg(chunk_row + gid);
-        b = __ldg(chunk_begin + gid);
-        e = min(b + static_cast<int64_t>(chunk_edges), load_ptr(t_indptr, is64, c + 1));
-    } else {
-        c = gid - n_chunks;
-        if (c >= n_cols) return;
-        b = load_ptr(t_indptr, is64, c);
-        e = load_ptr(t_indptr, is64, c + 1);
-        if (e - b > chunk_edges) return;
-    }
-    const int lane = threadIdx.x & 31;
-    const int hs = lane & (HB - 1);
-    const int slot = lane >> pow2_shift(HB);
-    const int ES = 32 / HB;
-    for (int hc = 0; hc < H; hc += HB) {
-        const int h = hc + hs;
-        float a = 0.0f;
-        if (h < H)
-            for (int64_t j = b + slot; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
-        for (int o = HB; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (slot == 0 && h < H) {
-            if (chunk) partial[gid * H + h] = a;
-            else out[c * H + h] = a;
-        }
-    }
-}
-
 static int head_block(int64_t H) {
     int hb = 1;
     while (hb < H && hb < 32) hb <<= 1;
@@ -722,6 +772,22 @@ static int head_block(int64_t H) {
 }  // namespace yitu
 
 using namespace yitu;
+
+static int fill_plan(const yitu_hub_plan_t *plan, int64_t *n_chunks, int *chunk_edges, const int **chunk_row,
+                     const int64_t **chunk_begin) {
+    *n_chunks = 0;
+    *chunk_edges = 0;
+    *chunk_row = nullptr;
+    *chunk_begin = nullptr;
+    if (plan == nullptr || plan->n_chunks == 0) return YITU_OK;
+    YITU_REQUIRE(plan->chunk_edges >= 32 && plan->chunk_row && plan->chunk_begin, YITU_ERR_INVALID_ARG,
+                 "hub plan needs chunk_edges >= 32 and its two tables");
+    *n_chunks = plan->n_chunks;
+    *chunk_edges = plan->chunk_edges;
+    *chunk_row = plan->chunk_row;
+    *chunk_begin = plan->chunk_begin;
+    return YITU_OK;
+}
 
 static int check_softmax_args(const yitu_csr_t *g, int32_t n_segments, int64_t H) {
     if (int rc = validate_csr(g)) return rc;
@@ -733,7 +799,8 @@ static int check_softmax_args(const yitu_csr_t *g, int32_t n_segments, int64_t H
 }
 
 extern "C" int yitu_edge_softmax_fwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
-                                         const float *query, const float *key, float *attn, yitu_stream_t stream) {
+                                         const float *query, const float *key, float *attn,
+                                         const yitu_hub_plan_t *plan, yitu_stream_t stream) {
     if (int rc = check_softmax_args(g, n_segments, n_heads)) return rc;
     if (g->n_rows == 0 || g->nnz == 0) return YITU_OK;
     YITU_REQUIRE(query && key && attn, YITU_ERR_INVALID_ARG, "NULL tensor");
@@ -741,16 +808,21 @@ extern "C" int yitu_edge_softmax_fwd_f32(const yitu_csr_t *g, int32_t n_segments
     p.n_rows = g->n_rows; p.indptr = g->indptr; p.indices = g->indices; p.is64 = g->indptr_is64;
     p.mask = g->index_mask; p.B = n_segments; p.H = static_cast<int>(n_heads); p.HB = head_block(n_heads);
     p.slope = slope; p.q = query; p.k = key; p.attn_out = attn;
-    edge_softmax_fwd_kernel<<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0,
-                              reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    if (int rc = fill_plan(plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    edge_softmax_fwd_kernel<false><<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0, st>>>(p);
     YITU_LAUNCH_CHECK();
+    if (p.n_chunks > 0) {  // hub rows: one CTA each
+        edge_softmax_fwd_kernel<true><<<static_cast<unsigned>(p.n_chunks), 256, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
     return YITU_OK;
 }
 
 extern "C" int yitu_edge_softmax_bwd_f32(const yitu_csr_t *g, int32_t n_segments, int64_t n_heads, float slope,
                                          const float *query, const float *key, const float *attn,
                                          const float *grad_attn, float *grad_query, float *edge_grad,
-                                         yitu_stream_t stream) {
+                                         const yitu_hub_plan_t *plan, yitu_stream_t stream) {
     if (int rc = check_softmax_args(g, n_segments, n_heads)) return rc;
     if (g->n_rows == 0) return YITU_OK;
     YITU_REQUIRE(query && grad_query, YITU_ERR_INVALID_ARG, "NULL tensor");
@@ -760,21 +832,34 @@ extern "C" int yitu_edge_softmax_bwd_f32(const yitu_csr_t *g, int32_t n_segments
     p.mask = g->index_mask; p.B = n_segments; p.H = static_cast<int>(n_heads); p.HB = head_block(n_heads);
     p.slope = slope; p.q = query; p.k = key; p.attn_in = attn; p.grad_attn = grad_attn;
     p.grad_q = grad_query; p.edge_grad = edge_grad;
-    edge_softmax_bwd_kernel<<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0,
-                              reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    if (int rc = fill_plan(plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    edge_softmax_bwd_kernel<false><<<static_cast<unsigned>((g->n_rows + 7) / 8), 256, 0, st>>>(p);
     YITU_LAUNCH_CHECK();
+    if (p.n_chunks > 0) {
+        edge_softmax_bwd_kernel<true><<<static_cast<unsigned>(p.n_chunks), 256, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
     return YITU_OK;
 }
 
 extern "C" int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indptr_is64,
                                         const int32_t *t_perm, int64_t n_heads, const float *edge_vals, float *out,
-                                        yitu_stream_t stream) {
+                                        const yitu_hub_plan_t *t_plan, yitu_stream_t stream) {
     YITU_REQUIRE(n_cols >= 0 && n_heads >= 1 && t_indptr, YITU_ERR_INVALID_ARG, "bad argument");
     if (n_cols == 0) return YITU_OK;
     YITU_REQUIRE(out, YITU_ERR_INVALID_ARG, "out is NULL");
-    edge_gather_sum_kernel<<<static_cast<unsigned>((n_cols + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        n_cols, t_indptr, indptr_is64, t_perm, static_cast<int>(n_heads), head_block(n_heads), edge_vals, out);
+    GatherSumParams p{};
+    p.n_cols = n_cols; p.t_indptr = t_indptr; p.is64 = indptr_is64; p.perm = t_perm;
+    p.H = static_cast<int>(n_heads); p.HB = head_block(n_heads); p.vals = edge_vals; p.out = out;
+    if (int rc = fill_plan(t_plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    edge_gather_sum_kernel<false><<<static_cast<unsigned>((n_cols + 7) / 8), 256, 0, st>>>(p);
     YITU_LAUNCH_CHECK();
+    if (p.n_chunks > 0) {
+        edge_gather_sum_kernel<true><<<static_cast<unsigned>(p.n_chunks), 256, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
     return YITU_OK;
 }
 
@@ -817,8 +902,14 @@ static int edge_dot_impl(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, 
 }
 
 extern "C" int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out,
-                                 const float *x, float *grad_a, yitu_stream_t stream) {
-    return edge_dot_impl(g, n_heads, n_feats, grad_out, 0, 1.0f, x, grad_a, stream);
+                                 const float *x, float *grad_a, const yitu_hub_plan_t *plan, yitu_stream_t stream) {
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+    if (int rc = fill_plan(plan, &n_chunks, &chunk_edges, &chunk_row, &chunk_begin)) return rc;
+    return edge_dot_impl(g, n_heads, n_feats, grad_out, 0, 1.0f, x, grad_a, stream, n_chunks, chunk_edges, chunk_row,
+                         chunk_begin);
 }
 
 static int check_gat(const yitu_gat_args_t *a, bool backward) {
@@ -836,22 +927,6 @@ static int check_gat(const yitu_gat_args_t *a, bool backward) {
                  "NULL tensor");
     YITU_REQUIRE(a->graph.nnz == 0 || (a->key && a->x), YITU_ERR_INVALID_ARG, "NULL tensor");
     YITU_REQUIRE(aligned16(a->x) && aligned16(a->out), YITU_ERR_INVALID_ARG, "x / out must be 16-byte aligned");
-    return YITU_OK;
-}
-
-static int fill_plan(const yitu_hub_plan_t *plan, int64_t *n_chunks, int *chunk_edges, const int **chunk_row,
-                     const int64_t **chunk_begin) {
-    *n_chunks = 0;
-    *chunk_edges = 0;
-    *chunk_row = nullptr;
-    *chunk_begin = nullptr;
-    if (plan == nullptr || plan->n_chunks == 0) return YITU_OK;
-    YITU_REQUIRE(plan->chunk_edges >= 32 && plan->chunk_row && plan->chunk_begin, YITU_ERR_INVALID_ARG,
-                 "hub plan needs chunk_edges >= 32 and its two tables");
-    *n_chunks = plan->n_chunks;
-    *chunk_edges = plan->chunk_edges;
-    *chunk_row = plan->chunk_row;
-    *chunk_begin = plan->chunk_begin;
     return YITU_OK;
 }
 
@@ -1004,16 +1079,6 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     }
     if (int rc = yitu_spmm_csr_f32(&s, stream)) return rc;
     if (g.n_cols == 0) return YITU_OK;
-    if (t_chunks == 0)
-        return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
-                                        stream);
-    edge_gather_sum_plan_kernel<<<static_cast<unsigned>((g.n_cols + t_chunks + 7) / 8), 256, 0, st>>>(
-        g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, static_cast<int>(H), head_block(H), b->edge_grad, b->grad_key,
-        t_chunks, t_chunk_edges, t_chunk_row, t_chunk_begin, k_partial);
-    YITU_LAUNCH_CHECK();
-    chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(b->t_indptr, g.indptr_is64, t_chunk_edges, t_chunk_row,
-                                                                      t_chunk_begin, static_cast<int>(H), k_partial,
-                                                                      b->grad_key);
-    YITU_LAUNCH_CHECK();
-    return YITU_OK;
+    return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
+                                    t_chunks > 0 ? b->t_plan : nullptr, stream);
 }

@@ -207,40 +207,57 @@ def epilogue_grad(y, grad_y, row_scale=None, activation=None):
     return out
 
 
-def edge_dot(graph, grad_out, x):
+def _hub_plan(graph, chunk_edges):
+    """(pointer to the HubPlan struct or None, number of chunks, objects to keep alive)."""
+    if not chunk_edges:
+        return None, 0, None
+    pl = graph.plan(chunk_edges)
+    if pl is None:
+        return None, 0, None
+    return C.pointer(pl[0]), pl[0].n_chunks, pl
+
+
+def edge_dot(graph, grad_out, x, chunk_edges=DEFAULT_CHUNK_EDGES):
     """grad_a[e,h] = <grad_out[row_e,h,:], x[col_e,h,:]>; grad_out [n_rows,H,F], x [n_cols,H,F]."""
     H, F = x.size(1), x.size(2)
     grad_a = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
+    plan, _, keep = _hub_plan(graph, chunk_edges)
     with torch.cuda.device(x.device):
-        check(lib().yitu_edge_dot_f32(C.byref(graph.csr), H, F, _ptr(grad_out), _ptr(x), _ptr(grad_a),
+        check(lib().yitu_edge_dot_f32(C.byref(graph.csr), H, F, _ptr(grad_out), _ptr(x), _ptr(grad_a), plan,
                                       _stream(x.device)))
+    del keep
     return grad_a
 
 
-def edge_softmax_fwd(graph, query, key, slope=0.2):
+def edge_softmax_fwd(graph, query, key, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDGES):
     """attn [nnz,H]; query [B,n_rows,H], key [n_cols,H]."""
     B, H = query.size(0), key.size(1)
     attn = torch.zeros((graph.nnz, H), dtype=torch.float32, device=key.device)
+    plan, _, keep = _hub_plan(graph, chunk_edges)
     with torch.cuda.device(key.device):
-        check(lib().yitu_edge_softmax_fwd_f32(C.byref(graph.csr), B, H, slope, _ptr(query), _ptr(key), _ptr(attn),
+        check(lib().yitu_edge_softmax_fwd_f32(C.byref(graph.csr), B, H, slope, _ptr(query), _ptr(key), _ptr(attn), plan,
                                               _stream(key.device)))
+    del keep
     return attn
 
 
-def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2):
+def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDGES):
     """(grad_query [B,n_rows,H], grad_key [n_cols,H])."""
     B, H = query.size(0), key.size(1)
     grad_q = torch.empty_like(query)
     edge_grad = torch.zeros_like(attn)
     grad_k = torch.empty_like(key)
     t_indptr, _, t_perm = graph.transpose()
+    plan, _, keep = _hub_plan(graph, chunk_edges)
+    t_plan, _, t_keep = _hub_plan(graph.t_prepared(), chunk_edges)
     L = lib()
     with torch.cuda.device(key.device):
         st = _stream(key.device)
         check(L.yitu_edge_softmax_bwd_f32(C.byref(graph.csr), B, H, slope, _ptr(query), _ptr(key), _ptr(attn),
-                                          _ptr(grad_attn), _ptr(grad_q), _ptr(edge_grad), st))
+                                          _ptr(grad_attn), _ptr(grad_q), _ptr(edge_grad), plan, st))
         check(L.yitu_edge_gather_sum_f32(graph.n_cols, _ptr(t_indptr), int(t_indptr.dtype == torch.int64),
-                                         _ptr(t_perm), H, _ptr(edge_grad), _ptr(grad_k), st))
+                                         _ptr(t_perm), H, _ptr(edge_grad), _ptr(grad_k), t_plan, st))
+    del keep, t_keep
     return grad_q, grad_k
 
 
@@ -253,16 +270,6 @@ def _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean=Fals
     a.out, a.row_max, a.row_sum = _ptr(out), _ptr(row_max), _ptr(row_sum)
     a.out_heads = _ptr(out_heads)
     return a
-
-
-def _hub_plan(graph, chunk_edges):
-    """(pointer to the HubPlan struct or None, number of chunks, objects to keep alive)."""
-    if not chunk_edges:
-        return None, 0, None
-    pl = graph.plan(chunk_edges)
-    if pl is None:
-        return None, 0, None
-    return C.pointer(pl[0]), pl[0].n_chunks, pl
 
 
 def gat_fused_supported(graph, n_heads, n_feats, backward=True):
