@@ -224,7 +224,7 @@ class SpmmWorkload:
 class GatWorkload:
     """configs[2]: fused GAT layer core forward + backward."""
     name = "gat_uniform_n1048576_e33554432_h8_f32_fwd_bwd"
-    dominant_kernel = "gat_fwd_kernel_r64<2,false>"
+    dominant_kernel = "gat_fwd_kernel_r64<2,false,false>"
 
     def __init__(self, device, n=1 << 20, e=1 << 25, H=8, F=32):
         import torch

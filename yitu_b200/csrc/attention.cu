@@ -12,6 +12,8 @@
 // All of them are bound by gather bandwidth (HBM/L2); none uses float atomics.
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace yitu {
@@ -378,23 +380,31 @@ __device__ __forceinline__ int warp_smem_floats_fwd(int H, int stage) { return 3
 // floats of one hub chunk's partial result: H*F sums, then H maxima and H sums (padded so that chunks stay 16-byte aligned)
 __host__ __device__ __forceinline__ int64_t fwd_partial_stride(int64_t H, int64_t F) { return H * F + ((2 * H + 3) & ~3ll); }
 
-template <int NV, bool MEAN>
+template <int NV, bool MEAN, bool PLAN>
 __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t gid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + wib;
     int64_t row, eb, ee;
-    const bool chunk = gid < p.n_chunks;
-    if (chunk) {
-        row = __ldg(p.chunk_row + gid);
-        eb = __ldg(p.chunk_begin + gid);
-        ee = min(eb + static_cast<int64_t>(p.chunk_edges), load_ptr(p.indptr, p.is64, row + 1));
+    bool chunk = false;  // PLAN = false is the kernel for graphs without hub rows: no schedule logic at all
+    if constexpr (PLAN) {
+        chunk = gid < p.n_chunks;
+        if (chunk) {
+            row = __ldg(p.chunk_row + gid);
+            eb = __ldg(p.chunk_begin + gid);
+            ee = min(eb + static_cast<int64_t>(p.chunk_edges), load_ptr(p.indptr, p.is64, row + 1));
+        } else {
+            row = gid - p.n_chunks;
+            if (row >= p.n_rows) return;
+            eb = load_ptr(p.indptr, p.is64, row);
+            ee = load_ptr(p.indptr, p.is64, row + 1);
+            if (ee - eb > p.chunk_edges) return;  // hub row: done by its chunks
+        }
     } else {
-        row = gid - p.n_chunks;
+        row = gid;
         if (row >= p.n_rows) return;
         eb = load_ptr(p.indptr, p.is64, row);
         ee = load_ptr(p.indptr, p.is64, row + 1);
-        if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;  // hub row: done by its chunks
     }
     const int H = p.H;
     float *base = smem + wib * warp_smem_floats_fwd(H, p.stage);
@@ -493,7 +503,7 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
         }
         __syncwarp();
     }
-    if (chunk) {
+    if (PLAN && chunk) {
         float *part = p.partial + gid * fwd_partial_stride(H, p.F);
 #pragma unroll
         for (int i = 0; i < NV; ++i)
@@ -544,16 +554,16 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
     }
 }
 
-template <int NV, bool MEAN>
+template <int NV, bool MEAN, bool PLAN>
 __global__ void __launch_bounds__(256) gat_fwd_kernel(const __grid_constant__ GatParams p) {
-    gat_fwd_body<NV, MEAN>(p);
+    gat_fwd_body<NV, MEAN, PLAN>(p);
 }
 
 // The same body held to 64 registers (four 256-thread CTAs per SM).  Left to itself the compiler settles on 48
 // registers for the two-slice head-mean variant and serialises the gathers: 7.2 ms against 6.5 ms on the 8x32 layer.
-template <int NV, bool MEAN>
+template <int NV, bool MEAN, bool PLAN>
 __global__ void __launch_bounds__(256, 4) gat_fwd_kernel_r64(const __grid_constant__ GatParams p) {
-    gat_fwd_body<NV, MEAN>(p);
+    gat_fwd_body<NV, MEAN, PLAN>(p);
 }
 
 // Finishes the hub rows of the fused forward: combines the chunks' (maximum, sum, unnormalised aggregate) in chunk
@@ -981,16 +991,16 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int sm = 32 + 32 * p.H + 4 * 32 + p.stage;
-    int rc;
-    if (p.head_mean) {
-        if (D <= 128) rc = launch_rows(gat_fwd_kernel<1, true>, p, sm, st);
-        else if (D <= 256) rc = launch_rows(gat_fwd_kernel_r64<2, true>, p, sm, st);
-        else rc = launch_rows(gat_fwd_kernel<4, true>, p, sm, st);
-    } else {
-        if (D <= 128) rc = launch_rows(gat_fwd_kernel<1, false>, p, sm, st);
-        else if (D <= 256) rc = launch_rows(gat_fwd_kernel_r64<2, false>, p, sm, st);
-        else rc = launch_rows(gat_fwd_kernel<4, false>, p, sm, st);
-    }
+    const auto pick = [&](auto mean, auto plan) -> int {
+        constexpr bool M = decltype(mean)::value, P = decltype(plan)::value;
+        if (D <= 128) return launch_rows(gat_fwd_kernel<1, M, P>, p, sm, st);
+        if (D <= 256) return launch_rows(gat_fwd_kernel_r64<2, M, P>, p, sm, st);
+        return launch_rows(gat_fwd_kernel<4, M, P>, p, sm, st);
+    };
+    using T = std::true_type;
+    using Fl = std::false_type;
+    const int rc = p.head_mean ? (p.n_chunks > 0 ? pick(T{}, T{}) : pick(T{}, Fl{}))
+                               : (p.n_chunks > 0 ? pick(Fl{}, T{}) : pick(Fl{}, Fl{}));
     if (rc) return rc;
     if (p.n_chunks > 0) {
         gat_fwd_merge_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
