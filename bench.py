@@ -376,9 +376,34 @@ def cpu_baseline(sample, repeats=5):
         dt = time.perf_counter() - t0
         spent += dt
         best = dt if best is None else min(best, dt)
-    return {"value": sample["nnz"] * sample["d"] / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": sample["sample"] + "; best of %d passes (%.1f s of CPU work)" % (done, spent),
-            "seconds": round(best, 3)}
+    out = {"value": sample["nnz"] * sample["d"] / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+           "sample": sample["sample"] + "; best of %d passes (%.1f s of CPU work)" % (done, spent),
+           "seconds": round(best, 3)}
+    if not sample.get("gat") and not sample.get("mask"):
+        out["scipy_single_thread"] = scipy_sanity(sample)
+    return out
+
+
+def scipy_sanity(sample, max_edges=4_000_000):
+    """Single-thread scipy.sparse CSR x dense on the first rows of the sample holding at most max_edges edges — the
+    library the reference builds its CSR with (YiTu_GNN/data/dataset.py:119-122); a sanity figure beside the port."""
+    import numpy as np
+    try:
+        import scipy.sparse as sp
+    except ImportError:
+        return None
+    ip = np.asarray(sample["indptr"], dtype=np.int64)
+    rows = int(np.searchsorted(ip, max_edges, side="right")) - 1
+    rows = max(1, min(rows, ip.shape[0] - 1))
+    e = int(ip[rows])
+    x = np.asarray(sample["x"], dtype=np.float32)
+    a = sp.csr_matrix((np.asarray(sample["values"][:e], dtype=np.float32), np.asarray(sample["indices"][:e]), ip[:rows + 1]),
+                      shape=(rows, x.shape[0]))
+    t0 = time.perf_counter()
+    a @ x
+    dt = time.perf_counter() - t0
+    return {"value": e * sample["d"] / dt / 1e9, "unit": UNIT, "cores": 1,
+            "sample": "rows [0,%d) (%d edges)" % (rows, e), "seconds": round(dt, 3)}
 
 
 WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload}
