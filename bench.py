@@ -556,6 +556,42 @@ def run_layer_fusion(args):
         row["unfused_%s_ms" % key] = timed(lambda: gat(False, backward))
         row["fused_%s_ms" % key] = timed(lambda: gat(True, backward))
     out["rows"].append(row)
+    del blk, x, q, k, gy, indptr, indices
+    torch.cuda.empty_cache()
+    # hetero RGCN layer for the destination type with the most relations: per-relation linear maps + one stitched pass;
+    # "unfused" concatenates the per-relation GEMM results first, as a list-of-tensors formulation does
+    if not shift:
+        from yitu_b200.nn.layers import StitchedRGCNConv, _AggregateFunction
+        sizes = graphs.HETERO_TYPES
+        rels = graphs.hetero_rgcn(device=dev)
+        by_dst = {}
+        for i, r in enumerate(rels):
+            by_dst.setdefault(r[1], []).append(i)
+        dt, ids = max(by_dst.items(), key=lambda kv: len(kv[1]))
+        relations = [("r%d" % i, Block([sizes[dt], sizes[rels[i][0]]], [rels[i][2], rels[i][3]])) for i in ids]
+        layer = StitchedRGCNConv(relations, 64, 64, reduce="sum").to(dev)
+        xs = {"r%d" % i: graphs.randn_features(20 + i, sizes[rels[i][0]], 64, device=dev).requires_grad_() for i in ids}
+        gy = graphs.randn_features(3, sizes[dt], 64, device=dev)
+
+        def rgcn(fused, backward):
+            if fused:
+                y = layer(xs)
+            else:
+                h = torch.cat([layer.fcs[name](xs[name]) for name in layer.names])
+                y = _AggregateFunction.apply(h, layer._graph(h.device, h.size(0)), layer._weights)
+            if backward:
+                y.backward(gy)
+                for v in xs.values():
+                    v.grad = None
+                layer.zero_grad()
+
+        row = {"layer": "hetero RGCN, %d relations into one destination type (GEMMs + stitched mean aggregation)" % len(ids),
+               "n_dst": sizes[dt], "nnz": sum(int(rels[i][3].numel()) for i in ids), "d": 64}
+        for backward in (False, True):
+            key = "fwd_bwd" if backward else "fwd"
+            row["unfused_%s_ms" % key] = timed(lambda: rgcn(False, backward))
+            row["fused_%s_ms" % key] = timed(lambda: rgcn(True, backward))
+        out["rows"].append(row)
     print(json.dumps(out))
 
 

@@ -135,6 +135,39 @@ class HeteroGraphConv(nn.Module):
         return {dty: res / counts[dty] for dty, res in outputs.items()}
 
 
+class _LinearIntoFunction(autograd.Function):
+    """h = [x_0 W_0^T + b_0 ; x_1 W_1^T + b_1 ; ...]: every relation's GEMM writes its rows of ONE buffer, the source
+    feature matrix of the stitched graph — no concatenation pass over the results."""
+
+    @staticmethod
+    def forward(ctx, n_rel, *tensors):
+        xs, ws, bs = tensors[:n_rel], tensors[n_rel:2 * n_rel], tensors[2 * n_rel:]
+        rows = [x.size(0) for x in xs]
+        h = torch.empty(sum(rows), ws[0].size(0), dtype=xs[0].dtype, device=xs[0].device)
+        off = 0
+        for x, w, b, n in zip(xs, ws, bs, rows):
+            torch.addmm(b, x, w.t(), out=h[off:off + n])
+            off += n
+        ctx.n_rel, ctx.rows = n_rel, rows
+        ctx.save_for_backward(*xs, *ws)
+        return h
+
+    @staticmethod
+    def backward(ctx, grad_h):
+        n_rel = ctx.n_rel
+        saved = ctx.saved_tensors
+        xs, ws = saved[:n_rel], saved[n_rel:]
+        gxs, gws, gbs = [], [], []
+        off = 0
+        for i, (x, w, n) in enumerate(zip(xs, ws, ctx.rows)):
+            g = grad_h[off:off + n]
+            off += n
+            gxs.append(g @ w if ctx.needs_input_grad[1 + i] else None)
+            gws.append(g.t() @ x if ctx.needs_input_grad[1 + n_rel + i] else None)
+            gbs.append(g.sum(0) if ctx.needs_input_grad[1 + 2 * n_rel + i] else None)
+        return (None, *gxs, *gws, *gbs)
+
+
 class StitchedRGCNConv(nn.Module):
     """HeteroGraphConv over GCNLayers (norm = 1/in_degree per relation) for ONE destination type in one kernel pass:
     the relations are stitched into a segmented CSR (stitch_csr), every edge carries 1/(in-degree of its row within
@@ -164,7 +197,9 @@ class StitchedRGCNConv(nn.Module):
 
     def forward(self, xs: dict):
         """xs maps edge type name -> source features [n_src_r, in_features]."""
-        h = torch.cat([self.fcs[name](xs[name]) for name in self.names])
+        fcs = [self.fcs[name] for name in self.names]
+        h = _LinearIntoFunction.apply(len(fcs), *[xs[name] for name in self.names], *[fc.weight for fc in fcs],
+                                      *[fc.bias for fc in fcs])
         g = self._graph(h.device, h.size(0))
         out = _AggregateFunction.apply(h, g, self._weights)
         return out / len(self.names) if self.reduce == "mean" else out
