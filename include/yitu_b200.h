@@ -255,10 +255,11 @@ int yitu_edge_gather_sum_f32(int64_t n_cols, const void *t_indptr, int32_t indpt
  * one pass over each row's edges — the composition sddmm_forward + spmm_forward of the reference
  * (xgnn_h/sparse.py:38-51,84-91; layer YiTu_GNN/YiTu_H/test/common/model.py:75-106) without the [nnz,H]
  * attention tensor.  Plain (unstitched) graphs, H <= 32, F a multiple of 4, H*F <= 512; other shapes return
- * YITU_ERR_UNSUPPORTED and the caller composes the unfused ops.  The backward call is edge-parallel: with the row
- * statistics of the forward pass and D[r,h] = <grad_out[r,h,:], out[r,h,:]> (= sum_e attn_e * d attn_e) every edge's
- * attention, its gradient and the score gradient follow without a second pass over the row; one kernel writes them
- * (edge_attn, edge_grad: [nnz,H] scratch) and grad_query, the transposed SpMM gives grad_x, a per-source sum grad_key. */
+ * YITU_ERR_UNSUPPORTED and the caller composes the unfused ops.  The backward call needs no pass over a row to
+ * normalise: with the row statistics of the forward pass and D[r,h] = <grad_out[r,h,:], out[r,h,:]>
+ * (= sum_e attn_e * d attn_e) every edge's attention and score gradient follow on their own, so ONE pass over the
+ * transposed graph — which gathers the rows of grad_out for grad_x anyway — also yields d attn (against the source's
+ * own features), the score gradients (scattered to edge_grad, then summed per row into grad_query) and grad_key. */
 typedef struct yitu_gat_args_t {
     yitu_csr_t graph;
     int64_t n_heads, n_feats;
@@ -292,13 +293,14 @@ typedef struct yitu_gat_bwd_args_t {
     float *grad_query;         /* [n_rows,H] */
     float *grad_key;           /* [n_cols,H] */
     float *grad_x;             /* [n_cols,H,F] */
-    float *edge_attn;          /* scratch [nnz,H] */
-    float *edge_grad;          /* scratch [nnz,H] */
+    float *edge_attn;          /* scratch [nnz,H]; needed only when F/4 is not a power of two <= 32 (may be NULL otherwise) */
+    float *edge_grad;          /* scratch [nnz,H]: the score gradient per edge, in CSR order */
     const yitu_hub_plan_t *t_plan; /* optional hub-row schedule of the transposed graph (fwd.plan is that of the graph) */
-    float *scratch;            /* a plan is given: yitu_gat_bwd_scratch_bytes(fwd.plan chunks, t_plan chunks, H, F) */
+    float *scratch;            /* yitu_gat_bwd_scratch_bytes(n_rows, fwd.plan chunks or 0, t_plan chunks or 0, H, F) */
     int64_t scratch_bytes;
 } yitu_gat_bwd_args_t;
-int64_t yitu_gat_bwd_scratch_bytes(int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads, int64_t n_feats);
+int64_t yitu_gat_bwd_scratch_bytes(int64_t n_rows, int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads,
+                                   int64_t n_feats);
 int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *args, yitu_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------- multi-GPU */

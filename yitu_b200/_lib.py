@@ -84,7 +84,7 @@ SYMBOLS = {
                                             C.POINTER(HubPlan), c_vp]),
     "yitu_edge_gather_sum_f32": (C.c_int, [c_i64, c_vp, c_i32, c_vp, c_i64, c_vp, c_vp, C.POINTER(HubPlan), c_vp]),
     "yitu_gat_fwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64]),
-    "yitu_gat_bwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64, c_i64]),
+    "yitu_gat_bwd_scratch_bytes": (c_i64, [c_i64, c_i64, c_i64, c_i64, c_i64]),
     "yitu_gat_fwd_f32": (C.c_int, [C.POINTER(GatArgs), c_vp]),
     "yitu_gat_bwd_f32": (C.c_int, [C.POINTER(GatBwdArgs), c_vp]),
     "yitu_shared_alloc": (C.c_int, [c_i64, C.POINTER(c_vp), c_vp]),

@@ -223,14 +223,17 @@ __global__ void __launch_bounds__(256) edge_gather_sum_kernel(const __grid_const
         float a = 0.0f;
         if (h < H) {
             int64_t j = b + slot;
-            for (; j + 3 * ES < e; j += 4 * ES) {  // four permutation loads, then four value loads, in flight together
-                const int p0 = __ldg(perm + j), p1 = __ldg(perm + j + ES), p2 = __ldg(perm + j + 2 * ES),
-                          p3 = __ldg(perm + j + 3 * ES);
-                const float v0 = __ldg(vals + static_cast<int64_t>(p0) * H + h), v1 = __ldg(vals + static_cast<int64_t>(p1) * H + h),
-                            v2 = __ldg(vals + static_cast<int64_t>(p2) * H + h), v3 = __ldg(vals + static_cast<int64_t>(p3) * H + h);
+            // four permutation loads (none when perm is NULL: the identity), then four value loads, in flight together
+            for (; j + 3 * ES < e; j += 4 * ES) {
+                int64_t p0 = j, p1 = j + ES, p2 = j + 2 * ES, p3 = j + 3 * ES;
+                if (perm != nullptr) {
+                    p0 = __ldg(perm + j); p1 = __ldg(perm + j + ES); p2 = __ldg(perm + j + 2 * ES); p3 = __ldg(perm + j + 3 * ES);
+                }
+                const float v0 = __ldg(vals + p0 * H + h), v1 = __ldg(vals + p1 * H + h), v2 = __ldg(vals + p2 * H + h),
+                            v3 = __ldg(vals + p3 * H + h);
                 a += v0; a += v1; a += v2; a += v3;
             }
-            for (; j < e; j += ES) a += __ldg(vals + static_cast<int64_t>(__ldg(perm + j)) * H + h);
+            for (; j < e; j += ES) a += __ldg(vals + (perm ? static_cast<int64_t>(__ldg(perm + j)) : j) * H + h);
         }
         a = slot_sum<CTA>(a, HB, s_red);
         if (slot == 0 && h < H) p.out[c * H + h] = a;
@@ -757,6 +760,199 @@ __global__ void __launch_bounds__(256, 5) gat_bwd_score_kernel(const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Fused GAT backward, source side: the whole backward in ONE pass over the transposed graph.
+// For source c and each of its out-edges e = (c -> r) the row of the upstream gradient g[r] has to be gathered anyway
+// (grad_x[c] = sum_e p_e g[r_e]); with x[c] held in registers the same row gives dp_e = <g[r_e], x[c]>, and with the
+// per-destination constants (query, log-sum statistics, D = <g[r], out[r]>) packed into one 16-byte record per
+// (row, head) the edge's attention p_e and score gradient ds_e follow on the spot:
+//     p = exp(LeakyReLU(q[r] + k[c]) - M[r]) / L[r],   ds = p (dp - D[r]) LeakyReLU'(q[r] + k[c]).
+// grad_key[c] = sum_e ds_e is local to the warp; ds_e is scattered to the edge's CSR position so that grad_query
+// is a plain row sum afterwards.  No pass over the forward graph gathers features, and no [nnz,H] attention array
+// exists.  One warp per source row or hub chunk (chunks leave partial grad_x / grad_key rows); EU edges in flight.
+// ---------------------------------------------------------------------------------------------------------
+struct GatSrcParams {
+    int64_t n_cols;      // rows of the transposed graph
+    const void *t_indptr;
+    int is64;
+    const int *t_rows, *t_perm;
+    int H, F;
+    float slope;
+    int hshift;             // log2(H) if H is a power of two, else -1
+    const float4 *rowpack;  // [n_rows, H]: (query, row max + log row sum, D, unused)
+    const float *k, *x;
+    const float *g;
+    int g_shared;
+    float g_scale;
+    float *grad_x, *grad_k, *edge_grad;
+    int64_t n_chunks;
+    int chunk_edges;
+    const int *chunk_row;
+    const int64_t *chunk_begin;
+    float *x_partial, *k_partial;  // [n_chunks, H*F], [n_chunks, H]
+};
+
+// rowpack[r,h] = (q, M + log L, <g[r,h,:], out[r,h,:]>, 0); warp per row, 128-bit slices, butterfly inside a head
+__global__ void __launch_bounds__(256)
+gat_rowpack_kernel(int64_t n_rows, int H, int F, const float *q, const float *row_max, const float *row_sum,
+                   const float *g, int g_shared, float g_scale, const float *out_heads, float4 *rowpack) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t D = static_cast<int64_t>(H) * F;
+    const int LPH = F >> 2;
+    float d[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t off = static_cast<int64_t>(i * 32 + lane) * 4;
+        d[i] = 0.0f;
+        if (off < D) {
+            const int64_t goff = g_shared ? off % F : off;
+            const float4 gv = __ldg(reinterpret_cast<const float4 *>(g + row * (g_shared ? F : D) + goff));
+            const float4 ov = __ldg(reinterpret_cast<const float4 *>(out_heads + row * D + off));
+            d[i] = gv.x * ov.x + gv.y * ov.y + gv.z * ov.z + gv.w * ov.w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t off = static_cast<int64_t>(i * 32 + lane) * 4;
+        for (int o = LPH >> 1; o > 0; o >>= 1) d[i] += __shfl_xor_sync(0xffffffffu, d[i], o);
+        if (off < D && (lane & (LPH - 1)) == 0) {
+            const int64_t h = off / F;
+            // p = exp(score - M) / L = exp(score - (M + log L)); rows without edges are never looked up
+            const float l = __ldg(row_sum + row * H + h);
+            rowpack[row * H + h] = make_float4(__ldg(q + row * H + h), __ldg(row_max + row * H + h) + logf(fmaxf(l, 1e-38f)),
+                                               d[i] * g_scale, 0.0f);
+        }
+    }
+}
+
+// Shared memory per warp: 32 destination ids, 32 CSR positions, H keys of the source, and per (edge, head) of the tile
+// the attention p, p * LeakyReLU' and the destination's D.
+__host__ __device__ __forceinline__ int src_smem_floats(int H) { return 64 + 32 + 3 * 32 * H; }
+
+template <int NV, int VEC, int EU>
+__global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant__ GatSrcParams p) {
+    extern __shared__ float smem[];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    int64_t c, eb, ee;
+    const bool chunk = gid < p.n_chunks;
+    if (chunk) {
+        c = __ldg(p.chunk_row + gid);
+        eb = __ldg(p.chunk_begin + gid);
+        ee = min(eb + static_cast<int64_t>(p.chunk_edges), load_ptr(p.t_indptr, p.is64, c + 1));
+    } else {
+        c = gid - p.n_chunks;
+        if (c >= p.n_cols) return;
+        eb = load_ptr(p.t_indptr, p.is64, c);
+        ee = load_ptr(p.t_indptr, p.is64, c + 1);
+        if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;
+    }
+    const int H = p.H, F = p.F;
+    const int D = H * F;
+    const int LPH = F / VEC;  // lanes per head: a power of two <= 32
+    const bool leader = (lane & (LPH - 1)) == 0;
+    const int64_t gstride = p.g_shared ? F : D;
+    float *base = smem + wib * src_smem_floats(H);
+    int *s_r = reinterpret_cast<int *>(base), *s_pos = s_r + 32;
+    float *s_k = base + 64, *s_p = s_k + 32, *s_pf = s_p + 32 * H, *s_d = s_pf + 32 * H;
+    if (lane < H) s_k[lane] = __ldg(p.k + c * H + lane);
+    int hd[NV], off[NV], goff[NV];  // offsets inside a row: H*F <= 512
+    bool valid[NV];
+    float xr[NV][VEC], acc[NV][VEC], gk[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        off[i] = (i * 32 + lane) * VEC;
+        valid[i] = off[i] < D;
+        hd[i] = valid[i] ? off[i] / F : 0;
+        goff[i] = p.g_shared ? off[i] - hd[i] * F : off[i];
+        gk[i] = 0.0f;
+        if (valid[i]) {
+            load_vec<VEC>(xr[i], p.x + c * D + off[i]);
+        } else {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) xr[i][v] = 0.0f;
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[i][v] = 0.0f;
+    }
+    for (int64_t e0 = eb; e0 < ee; e0 += 32) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
+        int my_r = 0, my_pos = 0;
+        if (lane < n) {
+            my_r = ld_stream(p.t_rows + e0 + lane);
+            my_pos = ld_stream(p.t_perm + e0 + lane);
+        }
+        const int r_first = __shfl_sync(0xffffffffu, my_r, 0);
+        s_r[lane] = lane < n ? my_r : r_first;  // padding edges repeat the first one with attention 0
+        s_pos[lane] = my_pos;
+        __syncwarp();
+        // attention and its factors for the tile's (edge, head) pairs: one 16-byte record of the destination each
+        const int n_up = (n + EU - 1) & ~(EU - 1);
+        for (int idx = lane; idx < n_up * H; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            float pr = 0.0f, pf = 0.0f, dv = 0.0f;
+            if (e < n) {
+                const float4 rp = __ldg(p.rowpack + static_cast<int64_t>(s_r[e]) * H + h);
+                const float sc = rp.x + s_k[h];
+                pr = expf(leaky_relu(sc, p.slope) - rp.y);
+                pf = sc < 0.0f ? pr * p.slope : pr;
+                dv = rp.z;
+            }
+            s_p[idx] = pr;
+            s_pf[idx] = pf;
+            s_d[idx] = dv;
+        }
+        __syncwarp();
+        for (int j = 0; j < n_up; j += EU) {
+            float gv[EU][NV][VEC];
+#pragma unroll
+            for (int u = 0; u < EU; ++u) {
+                const float *gr = p.g + static_cast<int64_t>(s_r[j + u]) * gstride;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    if (valid[i]) {
+                        load_vec<VEC>(gv[u][i], gr + goff[i]);
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < VEC; ++v) gv[u][i][v] = 0.0f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < EU; ++u) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    float dp = 0.0f;
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) dp = fmaf(gv[u][i][v], xr[i][v], dp);
+                    for (int o = LPH >> 1; o > 0; o >>= 1) dp += __shfl_xor_sync(0xffffffffu, dp, o);
+                    const int slot = (j + u) * H + hd[i];
+                    const float w = valid[i] ? s_p[slot] * p.g_scale : 0.0f;
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[i][v] = fmaf(w, gv[u][i][v], acc[i][v]);
+                    if (leader && valid[i] && j + u < n) {
+                        const float ds = s_pf[slot] * (dp * p.g_scale - s_d[slot]);
+                        p.edge_grad[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = ds;
+                        gk[i] += ds;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    float *xdst = chunk ? p.x_partial + gid * D : p.grad_x + c * D;
+    float *kdst = chunk ? p.k_partial + gid * H : p.grad_k + c * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (!valid[i]) continue;
+        store_vec<VEC>(xdst + off[i], acc[i]);
+        if (leader) kdst[hd[i]] = gk[i];
+    }
+}
+
 // out[row, :W] = sum of the row's chunk partials, in chunk order (one CTA per chunk, the row's first chunk works)
 __global__ void __launch_bounds__(128)
 chunk_sum_kernel(const void *indptr, int is64, int chunk_edges, const int *chunk_row, const int64_t *chunk_begin, int W,
@@ -970,9 +1166,11 @@ extern "C" int64_t yitu_gat_fwd_scratch_bytes(int64_t n_chunks, int64_t n_heads,
 
 static inline int64_t up256f(int64_t floats) { return (floats + 63) / 64 * 64; }  // 256-byte pieces, counted in floats
 
-extern "C" int64_t yitu_gat_bwd_scratch_bytes(int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads, int64_t n_feats) {
-    if (n_chunks < 0 || t_n_chunks < 0 || n_heads < 1 || n_feats < 1) return -1;
-    return (up256f(n_chunks * n_heads) + up256f(t_n_chunks * n_heads) + up256f(t_n_chunks * n_heads * n_feats)) *
+extern "C" int64_t yitu_gat_bwd_scratch_bytes(int64_t n_rows, int64_t n_chunks, int64_t t_n_chunks, int64_t n_heads,
+                                              int64_t n_feats) {
+    if (n_rows < 0 || n_chunks < 0 || t_n_chunks < 0 || n_heads < 1 || n_feats < 1) return -1;
+    return (up256f(n_rows * n_heads * 4) + up256f(n_chunks * n_heads) + up256f(t_n_chunks * n_heads) +
+            up256f(t_n_chunks * n_heads * n_feats)) *
            static_cast<int64_t>(sizeof(float));
 }
 
@@ -1017,7 +1215,7 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     YITU_REQUIRE(g.nnz < (1ll << 31), YITU_ERR_LIMIT, "fused GAT backward needs nnz < 2^31");
     YITU_REQUIRE(b->grad_out && b->grad_query && b->grad_key && b->grad_x && b->t_indptr, YITU_ERR_INVALID_ARG,
                  "NULL tensor");
-    YITU_REQUIRE(g.nnz == 0 || (b->t_rows && b->t_perm && b->edge_attn && b->edge_grad), YITU_ERR_INVALID_ARG,
+    YITU_REQUIRE(g.nnz == 0 || (b->t_rows && b->t_perm && b->edge_grad), YITU_ERR_INVALID_ARG,
                  "NULL transposed graph or scratch");
     YITU_REQUIRE(aligned16(b->grad_out) && aligned16(b->grad_x), YITU_ERR_INVALID_ARG,
                  "grad_out / grad_x must be 16-byte aligned");
@@ -1036,17 +1234,73 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     const int64_t *t_chunk_begin = nullptr;
     if (int rc = fill_plan(a->plan, &p.n_chunks, &p.chunk_edges, &p.chunk_row, &p.chunk_begin)) return rc;
     if (int rc = fill_plan(b->t_plan, &t_chunks, &t_chunk_edges, &t_chunk_row, &t_chunk_begin)) return rc;
-    float *q_partial = nullptr, *k_partial = nullptr, *spmm_scratch = nullptr;
-    if (p.n_chunks > 0 || t_chunks > 0) {
-        const int64_t need = yitu_gat_bwd_scratch_bytes(p.n_chunks, t_chunks, H, F);
-        YITU_REQUIRE(b->scratch && b->scratch_bytes >= need && aligned16(b->scratch), YITU_ERR_WORKSPACE,
-                     "fused GAT backward with hub plans needs %lld bytes of scratch", (long long)need);
-        q_partial = b->scratch;
-        k_partial = q_partial + up256f(p.n_chunks * H);
-        spmm_scratch = k_partial + up256f(t_chunks * H);
+    const int64_t need = yitu_gat_bwd_scratch_bytes(g.n_rows, p.n_chunks, t_chunks, H, F);
+    YITU_REQUIRE(b->scratch && b->scratch_bytes >= need && aligned16(b->scratch), YITU_ERR_WORKSPACE,
+                 "fused GAT backward needs %lld bytes of 16-byte aligned scratch", (long long)need);
+    float *rowpack = b->scratch;
+    float *q_partial = rowpack + up256f(g.n_rows * H * 4);
+    float *k_partial = q_partial + up256f(p.n_chunks * H);
+    float *x_partial = k_partial + up256f(t_chunks * H);
+    const int64_t lph = F / 4;
+    const bool one_pass = lph <= 32 && (lph & (lph - 1)) == 0 && aligned16(a->x) && aligned16(out_heads);
+
+    if (one_pass) {
+        // (1) per-destination constants, (2) everything else in one pass over the transposed graph, (3) grad_query as
+        // the row sum of the scattered score gradients
+        if (g.n_rows > 0) {
+            gat_rowpack_kernel<<<static_cast<unsigned>((g.n_rows + 7) / 8), 256, 0, st>>>(
+                g.n_rows, static_cast<int>(H), static_cast<int>(F), a->query, a->row_max, a->row_sum, b->grad_out, shared,
+                gscale, out_heads, reinterpret_cast<float4 *>(rowpack));
+            YITU_LAUNCH_CHECK();
+        }
+        if (g.n_cols > 0) {
+            GatSrcParams sp{};
+            sp.n_cols = g.n_cols; sp.t_indptr = b->t_indptr; sp.is64 = g.indptr_is64;
+            sp.t_rows = b->t_rows; sp.t_perm = b->t_perm; sp.H = static_cast<int>(H); sp.F = static_cast<int>(F);
+            sp.slope = a->slope; sp.rowpack = reinterpret_cast<const float4 *>(rowpack); sp.k = a->key; sp.x = a->x;
+            sp.g = b->grad_out; sp.g_shared = shared; sp.g_scale = gscale;
+            sp.grad_x = b->grad_x; sp.grad_k = b->grad_key; sp.edge_grad = b->edge_grad;
+            sp.n_chunks = t_chunks; sp.chunk_edges = t_chunk_edges; sp.chunk_row = t_chunk_row;
+            sp.chunk_begin = t_chunk_begin; sp.x_partial = x_partial; sp.k_partial = k_partial;
+            sp.hshift = (sp.H & (sp.H - 1)) == 0 ? 31 - __builtin_clz(sp.H) : -1;
+            const unsigned blocks = static_cast<unsigned>((g.n_cols + t_chunks + 7) / 8);
+            const size_t smem = 8 * static_cast<size_t>(src_smem_floats(sp.H)) * sizeof(float);
+            auto run = [&](auto kernel) -> int {
+                if (smem > 48 * 1024)
+                    YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                kernel<<<blocks, 256, smem, st>>>(sp);
+                YITU_LAUNCH_CHECK();
+                return YITU_OK;
+            };
+            // 256-bit gathers when a head spans whole 32-byte slices and every row starts on a 32-byte boundary
+            const auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+            const bool wide = F % 8 == 0 && a32(a->x) && a32(b->grad_out) && a32(b->grad_x) && a32(x_partial);
+            int rc;
+            if (wide && D > 128) rc = D <= 256 ? run(gat_bwd_src_kernel<1, 8, 4>) : run(gat_bwd_src_kernel<2, 8, 2>);
+            else if (D <= 128) rc = run(gat_bwd_src_kernel<1, 4, 4>);
+            else if (D <= 256) rc = run(gat_bwd_src_kernel<2, 4, 4>);
+            else rc = run(gat_bwd_src_kernel<4, 4, 2>);
+            if (rc) return rc;
+            if (t_chunks > 0) {
+                chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(
+                    b->t_indptr, g.indptr_is64, t_chunk_edges, t_chunk_row, t_chunk_begin, static_cast<int>(D), x_partial,
+                    b->grad_x);
+                YITU_LAUNCH_CHECK();
+                chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(
+                    b->t_indptr, g.indptr_is64, t_chunk_edges, t_chunk_row, t_chunk_begin, static_cast<int>(H), k_partial,
+                    b->grad_key);
+                YITU_LAUNCH_CHECK();
+            }
+        }
+        return yitu_edge_gather_sum_f32(g.n_rows, g.indptr, g.indptr_is64, nullptr, H, b->edge_grad, b->grad_query,
+                                        p.n_chunks > 0 ? a->plan : nullptr, stream);
     }
 
-    // destination side: dp into edge_grad, then attention, score gradient (in place) and grad_query
+    // Head widths whose lanes-per-head count is not a power of two (or exceeds a warp): destination side as a gather
+    // pass (dp) and a score pass over the forward graph, source side as a per-head SpMM and a per-source sum.
+    YITU_REQUIRE(g.nnz == 0 || b->edge_attn, YITU_ERR_INVALID_ARG,
+                 "this head width takes the two-sided backward, which needs the edge_attn scratch");
+    float *spmm_scratch = x_partial;
     if (g.n_rows > 0) {
         if (int rc = edge_dot_impl(&g, H, F, b->grad_out, shared, gscale, a->x, b->edge_grad, stream, p.n_chunks,
                                    p.chunk_edges, p.chunk_row, p.chunk_begin))
@@ -1072,7 +1326,6 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
             YITU_LAUNCH_CHECK();
         }
     }
-    // source side: grad_x = A^T-weighted gather of grad_out rows, grad_key = per-source sum of the score gradients
     yitu_hub_plan_t tp{};
     yitu_spmm_args_t s{};
     s.graph.n_rows = g.n_cols; s.graph.n_cols = g.n_rows; s.graph.nnz = g.nnz;

@@ -71,6 +71,35 @@ __device__ __forceinline__ float ld_stream(const float *p) {
     return v;
 }
 
+// Row slices of VEC floats: 128-bit or (new with sm_100) 256-bit global loads; streaming stores for outputs.
+template <int VEC>
+__device__ __forceinline__ void load_vec(float (&r)[VEC], const float *p) {
+    if constexpr (VEC == 8) {
+        // 256-bit global load (new with sm_100): one request moves 32 bytes per lane, 1 KiB per warp
+        asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7])
+                     : "l"(p));
+    } else if constexpr (VEC == 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    } else {
+        r[0] = __ldg(p);
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec(float *p, const float (&r)[VEC]) {
+    // output rows are written once and not read again by this kernel: streaming stores (evict-first)
+    if constexpr (VEC == 8) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(r[0], r[1], r[2], r[3]));
+        __stcs(reinterpret_cast<float4 *>(p) + 1, make_float4(r[4], r[5], r[6], r[7]));
+    } else if constexpr (VEC == 4) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(r[0], r[1], r[2], r[3]));
+    } else {
+        __stcs(p, r[0]);
+    }
+}
+
 inline int validate_csr(const yitu_csr_t *g) {
     YITU_REQUIRE(g != nullptr, YITU_ERR_INVALID_ARG, "graph is NULL");
     YITU_REQUIRE(g->n_rows >= 0 && g->n_cols >= 0 && g->nnz >= 0, YITU_ERR_INVALID_ARG,

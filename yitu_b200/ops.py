@@ -319,7 +319,9 @@ def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, he
     grad_q = torch.empty_like(query)
     grad_k = torch.empty_like(key)
     grad_x = torch.empty_like(x)
-    edge_attn = torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
+    lph = F // 4
+    one_pass = lph <= 32 and (lph & (lph - 1)) == 0
+    edge_attn = None if one_pass else torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
     edge_grad = torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
     b.grad_out = _ptr(grad_out)
     b.t_indptr, b.t_rows, b.t_perm = _ptr(t_indptr), _ptr(t_rows), _ptr(t_perm)
@@ -328,11 +330,10 @@ def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, he
     plan, n_chunks, keep = _hub_plan(graph, chunk_edges)
     t_plan, t_chunks, t_keep = _hub_plan(graph.t_prepared(), chunk_edges)
     L = lib()
-    if plan is not None or t_plan is not None:
-        nbytes = L.yitu_gat_bwd_scratch_bytes(n_chunks, t_chunks, H, F)
-        scratch = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=dev)
-        b.fwd.plan, b.t_plan = plan, t_plan
-        b.scratch, b.scratch_bytes = _ptr(scratch), nbytes
+    nbytes = L.yitu_gat_bwd_scratch_bytes(graph.n_rows, n_chunks, t_chunks, H, F)
+    scratch = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=dev)
+    b.fwd.plan, b.t_plan = plan, t_plan
+    b.scratch, b.scratch_bytes = _ptr(scratch), nbytes
     with torch.cuda.device(dev):
         check(L.yitu_gat_bwd_f32(C.byref(b), _stream(dev)))
     del keep, t_keep
