@@ -827,12 +827,15 @@ gat_rowpack_kernel(int64_t n_rows, int H, int F, const float *q, const float *ro
     }
 }
 
-// Shared memory per warp: 32 destination ids, 32 CSR positions, H keys of the source, and per (edge, head) of the tile
-// the attention p, p * LeakyReLU' and the destination's D.
-__host__ __device__ __forceinline__ int src_smem_floats(int H) { return 64 + 32 + 3 * 32 * H; }
+// Edges are taken in tiles of SRC_TILE.  Shared memory per warp: SRC_TILE destination ids and CSR positions, H keys of
+// the source, and per (edge, head) of the tile the attention p, p * LeakyReLU' and the destination's D.  (Tiles of 64,
+// which spare rows of 33..64 edges a second chain of dependent loads, were measured slower on the 8x32 layer, 10.5 ms
+// against 8.95 ms: the doubled shared memory costs more than the shorter chain gains.)
+constexpr int SRC_TILE = 32;
+__host__ __device__ __forceinline__ int src_smem_floats(int H) { return 2 * SRC_TILE + 32 + 3 * SRC_TILE * H; }
 
 template <int NV, int VEC, int EU>
-__global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant__ GatSrcParams p) {
+__device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -855,8 +858,8 @@ __global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant_
     const bool leader = (lane & (LPH - 1)) == 0;
     const int64_t gstride = p.g_shared ? F : D;
     float *base = smem + wib * src_smem_floats(H);
-    int *s_r = reinterpret_cast<int *>(base), *s_pos = s_r + 32;
-    float *s_k = base + 64, *s_p = s_k + 32, *s_pf = s_p + 32 * H, *s_d = s_pf + 32 * H;
+    int *s_r = reinterpret_cast<int *>(base), *s_pos = s_r + SRC_TILE;
+    float *s_k = base + 2 * SRC_TILE, *s_p = s_k + 32, *s_pf = s_p + SRC_TILE * H, *s_d = s_pf + SRC_TILE * H;
     if (lane < H) s_k[lane] = __ldg(p.k + c * H + lane);
     int hd[NV], off[NV], goff[NV];  // offsets inside a row: H*F <= 512
     bool valid[NV];
@@ -877,16 +880,23 @@ __global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant_
 #pragma unroll
         for (int v = 0; v < VEC; ++v) acc[i][v] = 0.0f;
     }
-    for (int64_t e0 = eb; e0 < ee; e0 += 32) {
-        const int n = static_cast<int>(min(static_cast<int64_t>(32), ee - e0));
-        int my_r = 0, my_pos = 0;
-        if (lane < n) {
-            my_r = ld_stream(p.t_rows + e0 + lane);
-            my_pos = ld_stream(p.t_perm + e0 + lane);
+    for (int64_t e0 = eb; e0 < ee; e0 += SRC_TILE) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(SRC_TILE), ee - e0));
+        int my_r[SRC_TILE / 32], my_pos[SRC_TILE / 32];
+#pragma unroll
+        for (int t = 0; t < SRC_TILE / 32; ++t) {
+            my_r[t] = my_pos[t] = 0;
+            if (t * 32 + lane < n) {
+                my_r[t] = ld_stream(p.t_rows + e0 + t * 32 + lane);
+                my_pos[t] = ld_stream(p.t_perm + e0 + t * 32 + lane);
+            }
         }
-        const int r_first = __shfl_sync(0xffffffffu, my_r, 0);
-        s_r[lane] = lane < n ? my_r : r_first;  // padding edges repeat the first one with attention 0
-        s_pos[lane] = my_pos;
+        const int r_first = __shfl_sync(0xffffffffu, my_r[0], 0);
+#pragma unroll
+        for (int t = 0; t < SRC_TILE / 32; ++t) {
+            s_r[t * 32 + lane] = t * 32 + lane < n ? my_r[t] : r_first;  // padding edges repeat the first one, attention 0
+            s_pos[t * 32 + lane] = my_pos[t];
+        }
         __syncwarp();
         // attention and its factors for the tile's (edge, head) pairs: one 16-byte record of the destination each
         const int n_up = (n + EU - 1) & ~(EU - 1);
@@ -951,6 +961,18 @@ __global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant_
         store_vec<VEC>(xdst + off[i], acc[i]);
         if (leader) kdst[hd[i]] = gk[i];
     }
+}
+
+template <int NV, int VEC, int EU>
+__global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant__ GatSrcParams p) {
+    gat_bwd_src_body<NV, VEC, EU>(p);
+}
+
+// the same body held to 64 registers, four CTAs per SM: 8.95 ms against 9.58 ms at 80 registers for the backward of the
+// 8x32 layer (the few spilled values cost less than the lost warps)
+template <int NV, int VEC, int EU>
+__global__ void __launch_bounds__(256, 4) gat_bwd_src_kernel_r64(const __grid_constant__ GatSrcParams p) {
+    gat_bwd_src_body<NV, VEC, EU>(p);
 }
 
 // out[row, :W] = sum of the row's chunk partials, in chunk order (one CTA per chunk, the row's first chunk works)
@@ -1276,7 +1298,7 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
             const auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
             const bool wide = F % 8 == 0 && a32(a->x) && a32(b->grad_out) && a32(b->grad_x) && a32(x_partial);
             int rc;
-            if (wide && D > 128) rc = D <= 256 ? run(gat_bwd_src_kernel<1, 8, 4>) : run(gat_bwd_src_kernel<2, 8, 2>);
+            if (wide && D > 128) rc = D <= 256 ? run(gat_bwd_src_kernel_r64<1, 8, 4>) : run(gat_bwd_src_kernel<2, 8, 2>);
             else if (D <= 128) rc = run(gat_bwd_src_kernel<1, 4, 4>);
             else if (D <= 256) rc = run(gat_bwd_src_kernel<2, 4, 4>);
             else rc = run(gat_bwd_src_kernel<4, 4, 2>);
