@@ -6,8 +6,11 @@
 //   edge_gather_sum         per-source sum of per-edge gradients over the transposed graph (replaces the
 //                           reference's atomicAdd scatter);
 //   gat_fwd / gat_bwd       the fused layer core: one pass over a row's edges computes scores, an online
-//                           max/sum softmax and the weighted aggregation; the backward recomputes the
-//                           attention and chains edge_softmax / edge_dot / transposed SpMM / edge_gather_sum.
+//                           max/sum softmax and the weighted aggregation; the backward is one pass over the
+//                           transposed graph that reuses every gathered gradient row for grad_x and for d attn
+//                           (attention rebuilt per edge from the forward's row statistics);
+//   hub rows                every kernel takes the optional hub schedule: long rows are cut into chunks with an ordered
+//                           merge, or handed to a whole CTA.
 //
 // All of them are bound by gather bandwidth (HBM/L2); none uses float atomics.
 #include <math_constants.h>
