@@ -228,6 +228,29 @@ int yitu_segment_mean_weights_f32(const yitu_csr_t *g, float *values, yitu_strea
 int yitu_edge_dot_f32(const yitu_csr_t *g, int64_t n_heads, int64_t n_feats, const float *grad_out, const float *x,
                       float *grad_a, const yitu_hub_plan_t *plan, yitu_stream_t stream);
 
+/* Both gradients of out[r,h,:] = sum_e values[e,h] * x[col_e,h,:] in ONE pass over the transposed graph
+ * (YiTu_GNN/YiTu_H/src/spmm_cuda.cu:24-42, two atomicAdds per edge, head and feature there): the rows of grad_out
+ * gathered for grad_x[c] = sum_e values_e * grad_out[row_e] also give grad_values[e] = <grad_out[row_e], x[c]> against
+ * the source's own features.  H <= 32, H*F <= 512, F/4 a power of two <= 32; other shapes return YITU_ERR_UNSUPPORTED
+ * (use yitu_edge_dot_f32 + yitu_spmm_csr_f32 over the transposed graph).  graph: sizes and index width of the forward
+ * graph; edge_values / grad_values are in its edge order. */
+typedef struct yitu_spmm_bwd_args_t {
+    yitu_csr_t graph;
+    int64_t n_heads, n_feats;
+    const float *edge_values;  /* [nnz,H] */
+    const float *x;            /* [n_cols,H,F] */
+    const float *grad_out;     /* [n_rows,H,F] */
+    const void *t_indptr;      /* transposed graph from yitu_csr_transpose */
+    const int32_t *t_rows;
+    const int32_t *t_perm;
+    float *grad_values;        /* [nnz,H] */
+    float *grad_x;             /* [n_cols,H,F] */
+    const yitu_hub_plan_t *t_plan; /* optional hub schedule of the transposed graph */
+    float *scratch;            /* t_plan: >= t_plan->n_chunks * H*F floats */
+    int64_t scratch_bytes;
+} yitu_spmm_bwd_args_t;
+int yitu_spmm_bwd_f32(const yitu_spmm_bwd_args_t *args, yitu_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------- GAT */
 /* The `plan` argument of the functions below is the optional hub-row schedule of the graph they walk (the transposed
  * graph's for yitu_edge_gather_sum_f32): with it, rows longer than plan->chunk_edges are processed by a whole CTA, or

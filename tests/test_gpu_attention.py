@@ -461,6 +461,11 @@ def test_standalone_attention_ops_on_hub_rows(oracle, H, B, chunk):
         gout = rng.standard_normal((n, H, F)).astype(np.float32)
         ga = ops.edge_dot(graph, _dev(gout), _dev(x), chunk_edges=chunk)
         plain = ops.edge_dot(graph, _dev(gout), _dev(x), chunk_edges=0)
-        rga, _ = oracle.spmm_backward(ref, indptr, indices, x, gout)
+        rga, rgx = oracle.spmm_backward(ref, indptr, indices, x, gout)
         assert_close(ga.cpu().numpy(), rga, rtol=2e-5, what="edge dot on hub rows")
         assert torch.equal(ga, plain)
+        # both gradients of the multi-head SpMM from one pass over the transposed graph, hub sources in chunks
+        assert ops.spmm_bwd_supported(H, F)
+        ga1, gx1 = ops.spmm_bwd(graph, _dev(ref), _dev(x), _dev(gout), chunk_edges=chunk)
+        assert_close(ga1.cpu().numpy(), rga, rtol=2e-5, what="one-pass grad_values on hub rows")
+        assert_close(gx1.cpu().numpy(), rgx, rtol=2e-5, what="one-pass grad_x on hub rows")

@@ -34,6 +34,12 @@ class SpmmArgs(C.Structure):
                 ("scratch_bytes", c_i64), ("bias", c_vp), ("x_shared_heads", c_i32), ("reserved", c_i32)]
 
 
+class SpmmBwdArgs(C.Structure):
+    _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("edge_values", c_vp), ("x", c_vp),
+                ("grad_out", c_vp), ("t_indptr", c_vp), ("t_rows", c_vp), ("t_perm", c_vp), ("grad_values", c_vp),
+                ("grad_x", c_vp), ("t_plan", C.POINTER(HubPlan)), ("scratch", c_vp), ("scratch_bytes", c_i64)]
+
+
 class GatArgs(C.Structure):
     _fields_ = [("graph", Csr), ("n_heads", c_i64), ("n_feats", c_i64), ("slope", c_f32), ("head_mean", c_i32),
                 ("query", c_vp), ("key", c_vp), ("x", c_vp), ("out", c_vp), ("row_max", c_vp), ("row_sum", c_vp),
@@ -73,6 +79,7 @@ SYMBOLS = {
     "yitu_relabel_edges": (C.c_int, [c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "yitu_edge_span_sum": (C.c_int, [c_i64, c_vp, c_vp, c_vp, c_vp]),
     "yitu_spmm_csr_f32": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
+    "yitu_spmm_bwd_f32": (C.c_int, [C.POINTER(SpmmBwdArgs), c_vp]),
     "yitu_static_scratch_bytes": (c_i64, []),
     "yitu_spmm_csr_f32_static": (C.c_int, [C.POINTER(SpmmArgs), c_vp]),
     "yitu_epilogue_grad_f32": (C.c_int, [c_i64, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp]),

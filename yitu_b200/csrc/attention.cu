@@ -793,6 +793,8 @@ struct GatSrcParams {
     const int *chunk_row;
     const int64_t *chunk_begin;
     float *x_partial, *k_partial;  // [n_chunks, H*F], [n_chunks, H]
+    const float *values;           // GIVEN: per-edge weights [nnz, H] in CSR order instead of attention
+    float *grad_values;            // GIVEN: d weight [nnz, H] in CSR order
 };
 
 // rowpack[r,h] = (q, M + log L, <g[r,h,:], out[r,h,:]>, 0); warp per row, 128-bit slices, butterfly inside a head
@@ -837,7 +839,9 @@ gat_rowpack_kernel(int64_t n_rows, int H, int F, const float *q, const float *ro
 constexpr int SRC_TILE = 32;
 __host__ __device__ __forceinline__ int src_smem_floats(int H) { return 2 * SRC_TILE + 32 + 3 * SRC_TILE * H; }
 
-template <int NV, int VEC, int EU>
+// GIVEN = true is the backward of a multi-head SpMM with stored edge values (graph_ext.spmm_backward): the weights are
+// read instead of rebuilt, and the by-product is d value = <g[r], x[c]> per edge and head.
+template <int NV, int VEC, int EU, bool GIVEN>
 __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     extern __shared__ float smem[];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -863,7 +867,7 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     float *base = smem + wib * src_smem_floats(H);
     int *s_r = reinterpret_cast<int *>(base), *s_pos = s_r + SRC_TILE;
     float *s_k = base + 2 * SRC_TILE, *s_p = s_k + 32, *s_pf = s_p + SRC_TILE * H, *s_d = s_pf + SRC_TILE * H;
-    if (lane < H) s_k[lane] = __ldg(p.k + c * H + lane);
+    if (!GIVEN && lane < H) s_k[lane] = __ldg(p.k + c * H + lane);
     int hd[NV], off[NV], goff[NV];  // offsets inside a row: H*F <= 512
     bool valid[NV];
     float xr[NV][VEC], acc[NV][VEC], gk[NV];
@@ -907,7 +911,9 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
             const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
             const int h = idx - e * H;
             float pr = 0.0f, pf = 0.0f, dv = 0.0f;
-            if (e < n) {
+            if constexpr (GIVEN) {
+                if (e < n) pr = __ldg(p.values + static_cast<int64_t>(s_pos[e]) * H + h);
+            } else if (e < n) {
                 const float4 rp = __ldg(p.rowpack + static_cast<int64_t>(s_r[e]) * H + h);
                 const float sc = rp.x + s_k[h];
                 pr = expf(leaky_relu(sc, p.slope) - rp.y);
@@ -915,8 +921,10 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
                 dv = rp.z;
             }
             s_p[idx] = pr;
-            s_pf[idx] = pf;
-            s_d[idx] = dv;
+            if constexpr (!GIVEN) {
+                s_pf[idx] = pf;
+                s_d[idx] = dv;
+            }
         }
         __syncwarp();
         for (int j = 0; j < n_up; j += EU) {
@@ -947,9 +955,13 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
 #pragma unroll
                     for (int v = 0; v < VEC; ++v) acc[i][v] = fmaf(w, gv[u][i][v], acc[i][v]);
                     if (leader && valid[i] && j + u < n) {
-                        const float ds = s_pf[slot] * (dp * p.g_scale - s_d[slot]);
-                        p.edge_grad[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = ds;
-                        gk[i] += ds;
+                        if constexpr (GIVEN) {
+                            p.grad_values[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = dp * p.g_scale;
+                        } else {
+                            const float ds = s_pf[slot] * (dp * p.g_scale - s_d[slot]);
+                            p.edge_grad[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = ds;
+                            gk[i] += ds;
+                        }
                     }
                 }
             }
@@ -962,20 +974,20 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     for (int i = 0; i < NV; ++i) {
         if (!valid[i]) continue;
         store_vec<VEC>(xdst + off[i], acc[i]);
-        if (leader) kdst[hd[i]] = gk[i];
+        if (!GIVEN && leader) kdst[hd[i]] = gk[i];
     }
 }
 
-template <int NV, int VEC, int EU>
+template <int NV, int VEC, int EU, bool GIVEN>
 __global__ void __launch_bounds__(256) gat_bwd_src_kernel(const __grid_constant__ GatSrcParams p) {
-    gat_bwd_src_body<NV, VEC, EU>(p);
+    gat_bwd_src_body<NV, VEC, EU, GIVEN>(p);
 }
 
 // the same body held to 64 registers, four CTAs per SM: 8.95 ms against 9.58 ms at 80 registers for the backward of the
 // 8x32 layer (the few spilled values cost less than the lost warps)
-template <int NV, int VEC, int EU>
+template <int NV, int VEC, int EU, bool GIVEN>
 __global__ void __launch_bounds__(256, 4) gat_bwd_src_kernel_r64(const __grid_constant__ GatSrcParams p) {
-    gat_bwd_src_body<NV, VEC, EU>(p);
+    gat_bwd_src_body<NV, VEC, EU, GIVEN>(p);
 }
 
 // out[row, :W] = sum of the row's chunk partials, in chunk order (one CTA per chunk, the row's first chunk works)
@@ -1232,6 +1244,32 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     return YITU_OK;
 }
 
+// Launches the source-side pass (attention rebuilt, or GIVEN edge values) and, with hub chunks, the ordered merge of
+// the chunks' grad_x rows.
+template <bool GIVEN>
+static int launch_src(GatSrcParams &sp, int64_t t_chunks, const float *x, const float *grad_out, float *grad_x,
+                      float *x_partial, cudaStream_t st) {
+    const int D = sp.H * sp.F;
+    sp.hshift = (sp.H & (sp.H - 1)) == 0 ? 31 - __builtin_clz(sp.H) : -1;
+    const unsigned blocks = static_cast<unsigned>((sp.n_cols + t_chunks + 7) / 8);
+    const size_t smem = 8 * static_cast<size_t>(src_smem_floats(sp.H)) * sizeof(float);
+    auto run = [&](auto kernel) -> int {
+        if (smem > 48 * 1024)
+            YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        kernel<<<blocks, 256, smem, st>>>(sp);
+        YITU_LAUNCH_CHECK();
+        return YITU_OK;
+    };
+    // 256-bit gathers when a head spans whole 32-byte slices and every row starts on a 32-byte boundary
+    const auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+    const bool wide = sp.F % 8 == 0 && a32(x) && a32(grad_out) && a32(grad_x) && a32(x_partial);
+    if (wide && D > 128)
+        return D <= 256 ? run(gat_bwd_src_kernel_r64<1, 8, 4, GIVEN>) : run(gat_bwd_src_kernel<2, 8, 2, GIVEN>);
+    if (D <= 128) return run(gat_bwd_src_kernel<1, 4, 4, GIVEN>);
+    if (D <= 256) return run(gat_bwd_src_kernel<2, 4, 4, GIVEN>);
+    return run(gat_bwd_src_kernel<4, 4, 2, GIVEN>);
+}
+
 extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stream) {
     YITU_REQUIRE(b != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
     const yitu_gat_args_t *a = &b->fwd;
@@ -1287,24 +1325,7 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
             sp.grad_x = b->grad_x; sp.grad_k = b->grad_key; sp.edge_grad = b->edge_grad;
             sp.n_chunks = t_chunks; sp.chunk_edges = t_chunk_edges; sp.chunk_row = t_chunk_row;
             sp.chunk_begin = t_chunk_begin; sp.x_partial = x_partial; sp.k_partial = k_partial;
-            sp.hshift = (sp.H & (sp.H - 1)) == 0 ? 31 - __builtin_clz(sp.H) : -1;
-            const unsigned blocks = static_cast<unsigned>((g.n_cols + t_chunks + 7) / 8);
-            const size_t smem = 8 * static_cast<size_t>(src_smem_floats(sp.H)) * sizeof(float);
-            auto run = [&](auto kernel) -> int {
-                if (smem > 48 * 1024)
-                    YITU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-                kernel<<<blocks, 256, smem, st>>>(sp);
-                YITU_LAUNCH_CHECK();
-                return YITU_OK;
-            };
-            // 256-bit gathers when a head spans whole 32-byte slices and every row starts on a 32-byte boundary
-            const auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
-            const bool wide = F % 8 == 0 && a32(a->x) && a32(b->grad_out) && a32(b->grad_x) && a32(x_partial);
-            int rc;
-            if (wide && D > 128) rc = D <= 256 ? run(gat_bwd_src_kernel_r64<1, 8, 4>) : run(gat_bwd_src_kernel<2, 8, 2>);
-            else if (D <= 128) rc = run(gat_bwd_src_kernel<1, 4, 4>);
-            else if (D <= 256) rc = run(gat_bwd_src_kernel<2, 4, 4>);
-            else rc = run(gat_bwd_src_kernel<4, 4, 2>);
+            int rc = launch_src<false>(sp, t_chunks, a->x, b->grad_out, b->grad_x, x_partial, st);
             if (rc) return rc;
             if (t_chunks > 0) {
                 chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(
@@ -1369,4 +1390,41 @@ extern "C" int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *b, yitu_stream_t stre
     if (g.n_cols == 0) return YITU_OK;
     return yitu_edge_gather_sum_f32(g.n_cols, b->t_indptr, g.indptr_is64, b->t_perm, H, b->edge_grad, b->grad_key,
                                     t_chunks > 0 ? b->t_plan : nullptr, stream);
+}
+
+extern "C" int yitu_spmm_bwd_f32(const yitu_spmm_bwd_args_t *a, yitu_stream_t stream) {
+    YITU_REQUIRE(a != nullptr, YITU_ERR_INVALID_ARG, "args is NULL");
+    if (int rc = validate_csr(&a->graph)) return rc;
+    const yitu_csr_t &g = a->graph;
+    const int64_t H = a->n_heads, F = a->n_feats, D = H * F, lph = F / 4;
+    YITU_REQUIRE(H >= 1 && F >= 1, YITU_ERR_INVALID_ARG, "bad shape");
+    YITU_REQUIRE(H <= 32 && F % 4 == 0 && D <= 512 && lph <= 32 && (lph & (lph - 1)) == 0, YITU_ERR_UNSUPPORTED,
+                 "one-pass SpMM backward needs H <= 32, H*F <= 512 and F/4 a power of two <= 32 (H=%lld F=%lld)",
+                 (long long)H, (long long)F);
+    YITU_REQUIRE(g.nnz < (1ll << 31), YITU_ERR_LIMIT, "one-pass SpMM backward needs nnz < 2^31");
+    YITU_REQUIRE(a->t_indptr && (g.n_cols == 0 || a->grad_x), YITU_ERR_INVALID_ARG, "NULL tensor");
+    YITU_REQUIRE(g.nnz == 0 || (a->edge_values && a->x && a->grad_out && a->t_rows && a->t_perm && a->grad_values),
+                 YITU_ERR_INVALID_ARG, "NULL tensor");
+    YITU_REQUIRE(aligned16(a->x) && aligned16(a->grad_out) && aligned16(a->grad_x), YITU_ERR_INVALID_ARG,
+                 "x / grad_out / grad_x must be 16-byte aligned");
+    if (g.n_cols == 0) return YITU_OK;
+    GatSrcParams sp{};
+    int64_t t_chunks = 0;
+    if (int rc = fill_plan(a->t_plan, &t_chunks, &sp.chunk_edges, &sp.chunk_row, &sp.chunk_begin)) return rc;
+    if (t_chunks > 0)
+        YITU_REQUIRE(a->scratch && aligned16(a->scratch) && a->scratch_bytes >= t_chunks * D * 4, YITU_ERR_WORKSPACE,
+                     "one-pass SpMM backward with a hub plan needs %lld bytes of scratch", (long long)(t_chunks * D * 4));
+    sp.n_cols = g.n_cols; sp.t_indptr = a->t_indptr; sp.is64 = g.indptr_is64; sp.t_rows = a->t_rows; sp.t_perm = a->t_perm;
+    sp.H = static_cast<int>(H); sp.F = static_cast<int>(F); sp.x = a->x; sp.g = a->grad_out; sp.g_shared = 0;
+    sp.g_scale = 1.0f; sp.grad_x = a->grad_x; sp.n_chunks = t_chunks; sp.x_partial = a->scratch;
+    sp.values = a->edge_values; sp.grad_values = a->grad_values;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (int rc = launch_src<true>(sp, t_chunks, a->x, a->grad_out, a->grad_x, a->scratch, st)) return rc;
+    if (t_chunks > 0) {
+        chunk_sum_kernel<<<static_cast<unsigned>(t_chunks), 128, 0, st>>>(a->t_indptr, g.indptr_is64, sp.chunk_edges,
+                                                                          sp.chunk_row, sp.chunk_begin,
+                                                                          static_cast<int>(D), a->scratch, a->grad_x);
+        YITU_LAUNCH_CHECK();
+    }
+    return YITU_OK;
 }

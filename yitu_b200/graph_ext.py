@@ -63,6 +63,8 @@ def spmm_backward(values, indptr, indices, features, grad_out):
     _need(values.dim() == 2 and indptr.dim() == 1 and indices.dim() == 1 and features.dim() == 3 and
           grad_out.dim() == 3, "spmm_backward: bad ranks")
     g = _graph(indptr, indices, features.size(0))
+    if ops.spmm_bwd_supported(features.size(1), features.size(2)):
+        return list(ops.spmm_bwd(g, values, features, grad_out))  # both gradients from one pass over the transposed graph
     grad_a = ops.edge_dot(g, grad_out, features)
     _, _, t_perm = g.transpose()
     grad_x = ops.spmm(g.t_prepared(), grad_out, n_heads=grad_out.size(1), mode=W_EDGE_HEAD, edge_values=values,

@@ -8,8 +8,8 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import (ACT_ELU, ACT_NONE, ACT_RELU, Csr, GatArgs, GatBwdArgs, HubPlan, SpmmArgs, W_EDGE, W_EDGE_HEAD,
-                   W_NODE, W_NONE, check, lib)
+from ._lib import (ACT_ELU, ACT_NONE, ACT_RELU, Csr, GatArgs, GatBwdArgs, HubPlan, SpmmArgs, SpmmBwdArgs, W_EDGE,
+                   W_EDGE_HEAD, W_NODE, W_NONE, check, lib)
 
 DEFAULT_CHUNK_EDGES = 512
 STITCH_MASK = 0xFFFFFF
@@ -227,6 +227,35 @@ def edge_dot(graph, grad_out, x, chunk_edges=DEFAULT_CHUNK_EDGES):
                                       _stream(x.device)))
     del keep
     return grad_a
+
+
+def spmm_bwd_supported(n_heads, n_feats):
+    lph = n_feats // 4
+    return n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512 and lph <= 32 and (lph & (lph - 1)) == 0
+
+
+def spmm_bwd(graph, values, x, grad_out, chunk_edges=DEFAULT_CHUNK_EDGES):
+    """(grad_values [nnz,H], grad_x [n_cols,H,F]) of the multi-head SpMM with per-edge values, in one pass over the
+    transposed graph (yitu_spmm_bwd_f32); shapes outside spmm_bwd_supported take edge_dot + the transposed spmm."""
+    H, F = x.size(1), x.size(2)
+    dev = x.device
+    t_indptr, t_rows, t_perm = graph.transpose()
+    a = SpmmBwdArgs()
+    a.graph = graph.csr
+    a.n_heads, a.n_feats = H, F
+    grad_values = torch.empty((graph.nnz, H), dtype=torch.float32, device=dev)
+    grad_x = torch.empty((graph.n_cols, H, F), dtype=torch.float32, device=dev)
+    a.edge_values, a.x, a.grad_out = _ptr(values), _ptr(x), _ptr(grad_out)
+    a.t_indptr, a.t_rows, a.t_perm = _ptr(t_indptr), _ptr(t_rows), _ptr(t_perm)
+    a.grad_values, a.grad_x = _ptr(grad_values), _ptr(grad_x)
+    t_plan, t_chunks, keep = _hub_plan(graph.t_prepared(), chunk_edges)
+    if t_plan is not None:
+        scratch = torch.empty(t_chunks * H * F, dtype=torch.float32, device=dev)
+        a.t_plan, a.scratch, a.scratch_bytes = t_plan, _ptr(scratch), scratch.numel() * 4
+    with torch.cuda.device(dev):
+        check(lib().yitu_spmm_bwd_f32(C.byref(a), _stream(dev)))
+    del keep
+    return grad_values, grad_x
 
 
 def edge_softmax_fwd(graph, query, key, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDGES):
