@@ -1244,8 +1244,7 @@ extern "C" int yitu_gat_fwd_f32(const yitu_gat_args_t *a, yitu_stream_t stream) 
     return YITU_OK;
 }
 
-// Launches the source-side pass (attention rebuilt, or GIVEN edge values) and, with hub chunks, the ordered merge of
-// the chunks' grad_x rows.
+// Launches the source-side pass (attention rebuilt, or GIVEN edge values); the caller merges hub chunks afterwards.
 template <bool GIVEN>
 static int launch_src(GatSrcParams &sp, int64_t t_chunks, const float *x, const float *grad_out, float *grad_x,
                       float *x_partial, cudaStream_t st) {
