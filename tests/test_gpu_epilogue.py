@@ -263,3 +263,19 @@ def test_gat_layer_head_mean_matches_unfused_composition(act):
     assert _close(y, y2)
     for a, b in zip(got, ref):
         assert _close(a, b, 5e-5)
+
+
+def test_head_mean_inference_skips_the_per_head_write():
+    from yitu_b200 import ops
+    from yitu_b200.xgnn_h import sparse
+    rng = np.random.default_rng(23)
+    n, H, F = 300, 4, 16
+    indptr, indices = random_csr(rng, n, n, density=0.05)
+    blk = _block(indptr, indices, n)
+    q, k, x = torch.randn(n, H, device="cuda"), torch.randn(n, H, device="cuda"), torch.randn(n, H, F, device="cuda")
+    y_train = sparse.fused_gat(blk, q.clone().requires_grad_(), k, x, head_mean=True, activation="elu")
+    with torch.no_grad():
+        y_eval = sparse.fused_gat(blk, q, k, x, head_mean=True, activation="elu")
+    assert torch.equal(y_train.detach(), y_eval)
+    g = ops.prepared(blk.adj_sparse[0], blk.adj_sparse[1], n, 0)
+    assert ops.gat_fwd(g, q, k, x, head_mean=True, keep_heads=False)[3] is None

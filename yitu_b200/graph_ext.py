@@ -130,7 +130,7 @@ def gat_supported(indptr, indices, n_heads, n_feats):
     return n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
-def gat_forward(indptr, indices, query, key, features, head_mean=False, activation=None):
+def gat_forward(indptr, indices, query, key, features, head_mean=False, activation=None, keep_heads=True):
     """[out [n_dst,H,F], row_max [n_dst,H], row_sum [n_dst,H]]: sddmm_forward + spmm_forward in one pass, for an
     unstitched graph (every segment id 0).  query [n_dst,H], key [n_src,H], features [n_src,H,F].
     head_mean / activation fuse the layer's mean over heads (out [n_dst,F]) and the model's ReLU / ELU; with
@@ -141,7 +141,7 @@ def gat_forward(indptr, indices, query, key, features, head_mean=False, activati
         ops.require_cuda(t, n, _F32)
     _need(query.dim() == 2 and key.dim() == 2 and features.dim() == 3, "gat_forward: bad ranks")
     g = ops.prepared(indptr, indices, features.size(0), 0)
-    return list(ops.gat_fwd(g, query, key, features, SLOPE, head_mean, activation))
+    return list(ops.gat_fwd(g, query, key, features, SLOPE, head_mean, activation, keep_heads=keep_heads))
 
 
 def gat_backward(indptr, indices, query, key, features, out, row_max, row_sum, grad_out, head_mean=False,

@@ -305,15 +305,17 @@ def gat_fused_supported(graph, n_heads, n_feats, backward=True):
     return graph.index_mask == 0 and n_heads <= 32 and n_feats % 4 == 0 and n_heads * n_feats <= 512
 
 
-def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None, chunk_edges=DEFAULT_CHUNK_EDGES):
+def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None, chunk_edges=DEFAULT_CHUNK_EDGES,
+            keep_heads=True):
     """Fused scores + edge softmax + aggregation: (out [n_rows,H,F], row_max [n_rows,H], row_sum [n_rows,H]).
     head_mean: out is act(mean over heads), [n_rows,F], and a fourth tensor comes back: the per-head result
-    [n_rows,H,F] that gat_bwd needs.  Rows longer than chunk_edges are split over several warps (0: never)."""
+    [n_rows,H,F] that gat_bwd needs (None with keep_heads=False: inference, nothing is written but the mean).
+    Rows longer than chunk_edges are split over several warps (0: never)."""
     H, F = x.size(1), x.size(2)
     dev = x.device
     shape = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
     out = torch.empty(shape, dtype=torch.float32, device=dev)
-    out_heads = torch.empty((graph.n_rows, H, F), dtype=torch.float32, device=dev) if head_mean else None
+    out_heads = torch.empty((graph.n_rows, H, F), dtype=torch.float32, device=dev) if head_mean and keep_heads else None
     row_max = torch.empty((graph.n_rows, H), dtype=torch.float32, device=dev)
     row_sum = torch.empty((graph.n_rows, H), dtype=torch.float32, device=dev)
     a = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, activation, out_heads)

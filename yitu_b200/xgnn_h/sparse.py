@@ -100,7 +100,9 @@ class FusedGATFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, adj_sparse, query, key, x, head_mean=False, activation=None):
-        res = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x, head_mean, activation)
+        # the per-head result of a head-mean forward is only written when a backward pass may follow
+        keep = any(ctx.needs_input_grad[1:4])
+        res = graph_ext.gat_forward(adj_sparse[0], adj_sparse[1], query, key, x, head_mean, activation, keep_heads=keep)
         out, row_max, row_sum = res[:3]
         ctx.adj_sparse, ctx.head_mean, ctx.activation = adj_sparse, head_mean, activation
         ctx.out_heads = res[3] if head_mean else None
