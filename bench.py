@@ -654,6 +654,28 @@ def run_reorder(args):
     print(json.dumps(out))
 
 
+def gat_layer_ms(dev, steps=5):
+    """The other half of the headline metric, "GAT layer ms": fused GAT layer core on the uniform 8x32 graph
+    (configs[2]), forward and forward+backward, CUDA events after 3 warm-up steps."""
+    import torch
+    wl = GatWorkload(dev)
+    wl.verify()
+    for _ in range(3):
+        wl.step()
+    torch.cuda.synchronize()
+    events = []
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        wl.step(events)
+    b.record()
+    torch.cuda.synchronize()
+    fwd = sum(x.elapsed_time(y) for x, y in events) / len(events)
+    total = a.elapsed_time(b) / steps
+    return {"workload": wl.name, "nnz": wl.nnz, "fwd_ms": fwd, "bwd_ms": total - fwd, "fwd_bwd_ms": total,
+            "value": wl.units_per_step / (total * 1e-3) / 1e9, "unit": UNIT}
+
+
 def partitioned_single_gpu_base(dev, steps=5):
     """The N>1 workload (row-partitioned SpMM graph) on this one GPU, so that a scaling series that starts from the
     default N=1 line has its like-for-like base: returns Gedge*feat/s and ms per step."""
@@ -766,6 +788,7 @@ def run_single(args):
                          "avg_launch_ms": k_avg_ms, "traffic": load_traffic(wl.traffic_key)},
             "cpu_baseline": base,
             "scaling_base_1gpu": None,
+            "gat_layer": None,
             "e2e": e2e,
             "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
     if args.workload == "spmm" and not args.scale and not args.no_scaling_base:
@@ -775,6 +798,11 @@ def run_single(args):
             line["scaling_base_1gpu"] = partitioned_single_gpu_base(dev)
         except Exception as exc:  # never lose the headline line to the extra measurement
             line["scaling_base_1gpu"] = {"error": str(exc)[:200]}
+        torch.cuda.empty_cache()
+        try:
+            line["gat_layer"] = gat_layer_ms(dev)
+        except Exception as exc:
+            line["gat_layer"] = {"error": str(exc)[:200]}
     print(json.dumps(line))
 
 
