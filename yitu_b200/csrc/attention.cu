@@ -878,14 +878,14 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     if (!GIVEN && lane < H) s_k[lane] = __ldg(p.k + c * H + lane);
     int hd[NV], off[NV], goff[NV];  // offsets inside a row: H*F <= 512
     bool valid[NV];
-    float xr[NV][VEC], acc[NV][VEC], gk[NV];
+    float xr[NV][VEC], acc[NV][VEC];
+    float gk_lane = 0.0f;  // partial sum of the score gradients of head lane % H (lane h of head h when H is not 2^k)
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         off[i] = (i * 32 + lane) * VEC;
         valid[i] = off[i] < D;
         hd[i] = valid[i] ? off[i] / F : 0;
         goff[i] = p.g_shared ? off[i] - hd[i] * F : off[i];
-        gk[i] = 0.0f;
         if (valid[i]) {
             load_vec<VEC>(xr[i], p.x + c * D + off[i]);
         } else {
@@ -962,17 +962,29 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
                     const float w = valid[i] ? s_p[slot] * p.g_scale : 0.0f;
 #pragma unroll
                     for (int v = 0; v < VEC; ++v) acc[i][v] = fmaf(w, gv[u][i][v], acc[i][v]);
-                    if (leader && valid[i] && j + u < n) {
-                        if constexpr (GIVEN) {
-                            p.grad_values[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = dp * p.g_scale;
-                        } else {
-                            const float ds = s_pf[slot] * (dp * p.g_scale - s_d[slot]);
-                            p.edge_grad[static_cast<int64_t>(s_pos[j + u]) * H + hd[i]] = ds;
-                            gk[i] += ds;
-                        }
-                    }
+                    // the head's leader lane leaves dp (minus the destination's D) for the pass over the pairs below
+                    if (leader && valid[i]) s_d[slot] = dp * p.g_scale - (GIVEN ? 0.0f : s_d[slot]);
                 }
             }
+        }
+        __syncwarp();
+        // score gradients (or d value) of the tile, spread over (edge, head) pairs: scattered to the edges' CSR positions
+        for (int idx = lane; idx < n * H; idx += 32) {
+            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
+            const int h = idx - e * H;
+            if constexpr (GIVEN) {
+                p.grad_values[static_cast<int64_t>(s_pos[e]) * H + h] = s_d[idx];
+            } else {
+                const float ds = s_pf[idx] * s_d[idx];
+                p.edge_grad[static_cast<int64_t>(s_pos[e]) * H + h] = ds;
+                if (p.hshift >= 0) gk_lane += ds;  // H a power of two: this lane always meets head lane % H
+                else s_pf[idx] = ds;
+            }
+        }
+        if (!GIVEN && p.hshift < 0) {
+            __syncwarp();
+            if (lane < H)
+                for (int e = 0; e < n; ++e) gk_lane += s_pf[e * H + lane];
         }
         __syncwarp();
     }
@@ -982,7 +994,11 @@ __device__ __forceinline__ void gat_bwd_src_body(const GatSrcParams &p) {
     for (int i = 0; i < NV; ++i) {
         if (!valid[i]) continue;
         store_vec<VEC>(xdst + off[i], acc[i]);
-        if (!GIVEN && leader) kdst[hd[i]] = gk[i];
+    }
+    if constexpr (!GIVEN) {
+        if (p.hshift >= 0)
+            for (int o = H; o < 32; o <<= 1) gk_lane += __shfl_xor_sync(0xffffffffu, gk_lane, o);
+        if (lane < H) kdst[lane] = gk_lane;
     }
 }
 
