@@ -460,28 +460,49 @@ __device__ __forceinline__ void gat_fwd_body(const GatParams &p) {
             s_p[idx] = leaky_relu(s_q[h] + __ldg(p.k + static_cast<int64_t>(s_col[e]) * H + h), p.slope);
         }
         __syncwarp();
-        if (lane < H) {
+        const int n4 = (n + 3) & ~3;
+        if (p.hshift >= 0) {
+            // H a power of two: a lane's pairs idx = lane + 32t all belong to head lane % H, so the tile's maximum and
+            // sum are butterflies over the lanes of equal lane % H; every lane keeps the running statistics of that head
             float tm = -CUDART_INF_F;
-            for (int e = 0; e < n; ++e) tm = fmaxf(tm, s_p[e * H + lane]);
+            for (int idx = lane; idx < npairs; idx += 32) tm = fmaxf(tm, s_p[idx]);
+            for (int o = H; o < 32; o <<= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
             const float m_new = fmaxf(m_run, tm);
             const float sc = expf(m_run - m_new);  // 0 on the first tile (m_run = -inf)
-            s_scale[lane] = sc;
-            s_m[lane] = m_new;
-            l_run *= sc;
-            m_run = m_new;
-        }
-        __syncwarp();
-        const int n4 = (n + 3) & ~3;
-        for (int idx = lane; idx < n4 * H; idx += 32) {
-            const int e = p.hshift >= 0 ? (idx >> p.hshift) : (idx / H);
-            const int h = idx - e * H;
-            s_p[idx] = idx < npairs ? expf(s_p[idx] - s_m[h]) : 0.0f;
-        }
-        __syncwarp();
-        if (lane < H) {
+            if (lane < H) s_scale[lane] = sc;
             float ls = 0.0f;
-            for (int e = 0; e < n; ++e) ls += s_p[e * H + lane];
-            l_run += ls;
+            for (int idx = lane; idx < n4 * H; idx += 32) {
+                const float v = idx < npairs ? expf(s_p[idx] - m_new) : 0.0f;
+                s_p[idx] = v;
+                ls += v;
+            }
+            for (int o = H; o < 32; o <<= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+            l_run = l_run * sc + ls;
+            m_run = m_new;
+            __syncwarp();
+        } else {
+            if (lane < H) {
+                float tm = -CUDART_INF_F;
+                for (int e = 0; e < n; ++e) tm = fmaxf(tm, s_p[e * H + lane]);
+                const float m_new = fmaxf(m_run, tm);
+                const float sc = expf(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+                s_scale[lane] = sc;
+                s_m[lane] = m_new;
+                l_run *= sc;
+                m_run = m_new;
+            }
+            __syncwarp();
+            for (int idx = lane; idx < n4 * H; idx += 32) {
+                const int e = idx / H;
+                const int h = idx - e * H;
+                s_p[idx] = idx < npairs ? expf(s_p[idx] - s_m[h]) : 0.0f;
+            }
+            __syncwarp();
+            if (lane < H) {
+                float ls = 0.0f;
+                for (int e = 0; e < n; ++e) ls += s_p[e * H + lane];
+                l_run += ls;
+            }
         }
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
