@@ -140,6 +140,38 @@ def test_hetero_conv_and_stitched_form_agree():
     assert _close(summed({"rel_" + n: xs[n] for n in sizes}), ref, 3e-5)
 
 
+def test_hetero_gat_and_stitched_form_agree():
+    """HeteroGraphConv over one GATLayer per relation against the stitched form (segmented softmax + one SpMM)."""
+    from yitu_b200.nn import GATLayer, HeteroGraphConv, StitchedRGATConv
+    rng = np.random.default_rng(5)
+    n_dst, d_in, H, F = 180, 10, 4, 8
+    sizes = {"a": 70, "b": 120, "c": 50}
+    hgraph, xs = {}, {}
+    for name, n_src in sizes.items():
+        indptr, indices = random_csr(rng, n_dst, n_src, density=0.1, empty_rows=False)
+        hgraph[(name, "rel_" + name, "dst")] = _block(indptr, indices, n_src)
+        xs[name] = torch.randn(n_src, d_in, device="cuda", requires_grad=True)
+    xs["dst"] = torch.randn(n_dst, d_in, device="cuda", requires_grad=True)
+    conv = HeteroGraphConv({"rel_" + n: GATLayer(d_in, F, H) for n in sizes}).cuda()
+    y = conv(hgraph, xs)["dst"]
+    w_out = torch.randn(n_dst, F, device="cuda")
+    (y * w_out).sum().backward()
+    g1 = {n: xs[n].grad.clone() for n in xs}
+    gw1 = {n: conv.convs["rel_" + n].linear_q.weight.grad.clone() for n in sizes}
+    for n in xs:
+        xs[n].grad = None
+    stitched = StitchedRGATConv([("rel_" + n, hgraph[(n, "rel_" + n, "dst")]) for n in sizes], d_in, F, H).cuda()
+    for n in sizes:
+        stitched.layers["rel_" + n].load_state_dict(conv.convs["rel_" + n].state_dict())
+    y2 = stitched({"rel_" + n: xs[n] for n in sizes}, xs["dst"])
+    (y2 * w_out).sum().backward()
+    assert y2.shape == (n_dst, F) and _close(y2, y, 3e-5)
+    for n in xs:
+        assert _close(xs[n].grad, g1[n], 1e-4)
+    for n in sizes:
+        assert _close(stitched.layers["rel_" + n].linear_q.weight.grad, gw1[n], 2e-4)
+
+
 def test_two_layer_gcn_replays_from_a_cuda_graph():
     """The operators take the current stream and allocate only through torch, so a whole forward pass can be captured
     once and replayed (the small 2-layer GCN configuration is launch-bound when run eagerly)."""

@@ -2,7 +2,7 @@
 YiTu_H layers GCNLayer / GATLayer / HeteroGraphConv (YiTu_GNN/YiTu_H/test/common/model.py)."""
 from .GCNConv import GCNConv, GNNAFunction
 from .GINConv import GINConv, GNNAFunction_GIN
-from .layers import GATLayer, GCNLayer, HeteroGraphConv, StitchedRGCNConv, aggregate
+from .layers import GATLayer, GCNLayer, HeteroGraphConv, StitchedRGATConv, StitchedRGCNConv, aggregate
 
 __all__ = ["GCNConv", "GNNAFunction", "GINConv", "GNNAFunction_GIN", "GATLayer", "GCNLayer", "HeteroGraphConv",
-           "StitchedRGCNConv", "aggregate"]
+           "StitchedRGCNConv", "StitchedRGATConv", "aggregate"]

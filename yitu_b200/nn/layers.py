@@ -203,3 +203,36 @@ class StitchedRGCNConv(nn.Module):
         g = self._graph(h.device, h.size(0))
         out = _AggregateFunction.apply(h, g, self._weights)
         return out / len(self.names) if self.reduce == "mean" else out
+
+
+class StitchedRGATConv(nn.Module):
+    """HeteroGraphConv over GATLayers (model.py:61-106,137-171) for ONE destination type over the stitched relations:
+    the attention of every relation is normalised inside its own segment of the row (the segmented edge softmax of
+    graph_ext.sddmm_forward, queries [n_relations, n_dst, H]) and one multi-head SpMM over the stitched graph adds the
+    relations up; then the mean over heads and, with reduce="mean", the division by the number of relations.
+    Each relation has its own linear_v / linear_q / linear_k, as one GATLayer per edge type has in the reference."""
+
+    def __init__(self, relations, in_features: int, out_features: int, n_heads: int, reduce: str = "mean"):
+        """relations: list of (edge type name, Block) that share the destination type."""
+        nn.Module.__init__(self)
+        assert reduce in ("mean", "sum")
+        self.names = [name for name, _ in relations]
+        self.n_heads, self.n_features, self.reduce = n_heads, out_features, reduce
+        self.layers = nn.ModuleDict({name: GATLayer(in_features, out_features, n_heads) for name in self.names})
+        self.block = stitch_csr([blk for _, blk in relations])
+
+    def forward(self, xs: dict, x_dst):
+        """xs maps edge type name -> source features [n_src_r, in_features]; x_dst [n_dst, in_features]."""
+        if self.block.adj_sparse[0].device != x_dst.device:
+            self.block.to(x_dst.device)
+        hs, ks, qs = [], [], []
+        for name in self.names:
+            layer = self.layers[name]
+            h_src = layer.linear_v(xs[name])
+            hs.append(h_src)
+            ks.append(layer.linear_k(h_src))
+            qs.append(layer.linear_q(layer.linear_v(x_dst)))
+        h = torch.cat(hs).view(-1, self.n_heads, self.n_features)
+        attn = sparse.fused_gsddmm(self.block, torch.stack(qs).contiguous(), torch.cat(ks).contiguous())
+        out = torch.mean(sparse.gspmm(self.block, attn, h.contiguous()), dim=1)
+        return out / len(self.names) if self.reduce == "mean" else out
