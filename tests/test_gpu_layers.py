@@ -206,3 +206,41 @@ def test_two_layer_gcn_replays_from_a_cuda_graph():
     torch.cuda.synchronize()
     assert torch.equal(captured, forward()), "replay must reproduce the eager result for the new input"
     assert not torch.equal(captured, eager)
+
+
+def test_fused_gat_forward_and_backward_replay_from_a_cuda_graph():
+    """The fused GAT forward and its one-pass backward (hub schedules included) are plain stream work once the cached
+    graph structures exist: capture both, replay on new inputs, compare with eager execution."""
+    from yitu_b200 import ops
+    rng = np.random.default_rng(9)
+    n, H, F = 3000, 8, 32
+    a = rng.random((n, n)) < 0.004
+    a[5, rng.choice(n, size=1500, replace=False)] = True     # a hub row and a hub column: both schedules non-empty
+    a[rng.choice(n, size=1500, replace=False), 7] = True
+    indptr = np.concatenate([[0], np.cumsum(a.sum(1))]).astype(np.int32)
+    indices = np.nonzero(a)[1].astype(np.int32)
+    g = ops.PreparedGraph(torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda(), n)
+    q, k = torch.randn(n, H, device="cuda"), torch.randn(n, H, device="cuda")
+    x, grad = torch.randn(n, H, F, device="cuda"), torch.randn(n, H, F, device="cuda")
+
+    def step():
+        out, rmax, rsum = ops.gat_fwd(g, q, k, x)
+        return (out,) + tuple(ops.gat_bwd(g, q, k, x, out, rmax, rsum, grad))
+
+    step()  # builds the transposed graph and both hub schedules (synchronises): before the capture
+    assert g.plan() is not None and g.t_prepared().plan() is not None
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    x.copy_(torch.randn(n, H, F, device="cuda"))
+    q.copy_(torch.randn(n, H, device="cuda"))
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, ref in zip(captured, step()):
+        assert torch.equal(got, ref)
