@@ -472,6 +472,27 @@ def run_reference_gpu_comparison(args):
     out["rows"].append({"op": "graph_ext.sddmm_forward+spmm_forward", "n": n, "nnz": indices.numel(), "d": H * F,
                         "reference_ms": t_ref, "this_ms_two_operators": t_two, "this_ms_fused": t_fused,
                         "speedup": t_ref / t_fused, "max_abs_diff": err})
+    # the backward of the same pair: the reference scatters with atomicAdd (spmm_cuda.cu:24-42, sddmm_cuda.cu:36-67)
+    attn = graph_ext.sddmm_forward(indptr, indices, q, k)
+    gout = graphs.randn_features(6, n, H * F, device=dev).view(n, H, F)
+
+    def ref_bwd():
+        ga, gx = ref_h.spmm_backward(attn, indptr, indices, xh, gout)
+        return ref_h.sddmm_backward(indptr, indices, q, k, attn, ga) + [gx]
+
+    def two_bwd():
+        ga, gx = graph_ext.spmm_backward(attn, indptr, indices, xh, gout)
+        return graph_ext.sddmm_backward(indptr, indices, q, k, attn, ga) + [gx]
+
+    fo, fmax, fsum = graph_ext.gat_forward(indptr, indices, q[0], k, xh)
+    t_ref = timed(ref_bwd, 5)
+    t_two = timed(two_bwd, 20)
+    t_fused = timed(lambda: graph_ext.gat_backward(indptr, indices, q[0], k, xh, fo, fmax, fsum, gout), 20)
+    r, o = ref_bwd(), graph_ext.gat_backward(indptr, indices, q[0], k, xh, fo, fmax, fsum, gout)
+    err = max(float((r[0][0] - o[0]).abs().max()), float((r[1] - o[1]).abs().max()), float((r[2] - o[2]).abs().max()))
+    out["rows"].append({"op": "graph_ext.spmm_backward+sddmm_backward", "n": n, "nnz": indices.numel(), "d": H * F,
+                        "reference_ms": t_ref, "this_ms_two_operators": t_two, "this_ms_fused": t_fused,
+                        "speedup": t_ref / t_fused, "max_abs_diff": err})
     print(json.dumps(out))
 
 
