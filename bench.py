@@ -6,16 +6,25 @@
 Prints ONE JSON line.  metric = aggregation throughput in Gedge*feat/s (stored edges x feature width per
 second, whole job).  A step is one pass of the workload's hot path over the resident synthetic graph:
 
+  partitioned  N GPUs R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, D=128, rows split into N
+                      edge-balanced ranges, halo source rows pushed over NVLink by their owners (strong scaling);
+                      with N=1 the whole graph on one GPU
   spmm         1 GPU  R-MAT N=2^21, 2^26 sampled edges (deduplicated), fp32 per-edge symmetric-normalised
                       weights, D=256: forward A*X and the transposed product A^T*G (2 * nnz * D edge-feats)
   gat          1 GPU  uniform random N=2^20, 2^25 edges + self loops, 8 heads x 32: fused GAT forward+backward
   rgcn         1 GPU  4 node types, 8 bipartite R-MAT relations x 4M edges, D=64: mean per relation, sum per type
-  partitioned  N GPUs R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, D=128, rows split into N
-                      edge-balanced ranges, halo source rows fetched over NVLink (strong scaling)
 
-Default: N=1 -> spmm; N>1 -> partitioned.  Inputs are far larger than L2 (126 MB), so no flush is needed
-between timed iterations.  `--impl reference` times the CPU restatement of the reference kernels (the
-reference has no CPU implementation of this path) on all host cores, on a bounded row slice.
+Default at every N: partitioned - ONE series at 1/2/4/8 GPUs, the same graph throughout.  The N=1 line also
+carries the other three configurations as sub-records (spmm_c2, gat_layer, rgcn_layer), each with its own time and
+roofline.  Inputs are far larger than L2 (126 MB), so no flush is needed between timed iterations.
+`--impl reference` times the CPU restatement of the reference kernels (the reference has no CPU implementation of
+this path) on all host cores, on a bounded row slice.
+
+roofline keys: `frac` = algorithmic bytes (every edge counts its whole source row, no cache credit) / kernel time /
+measured HBM copy bandwidth - it exceeds 1 where the L2 serves the hot rows of a power-law graph; `dram_frac` =
+DRAM bytes per launch as counted by ncu (`traffic`, from the committed capture named in `traffic_source`) / kernel
+time / the same peak - the physical share of HBM bandwidth; `compulsory_frac` = bytes that must move at least once
+(each source row, index, weight and output row once) / kernel time / peak.
 """
 import argparse
 import json
@@ -42,13 +51,36 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
-def load_traffic(key):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary (None until profiled)."""
+def load_traffic(key, kernel):
+    """DRAM bytes per launch of a workload's dominant kernel from the committed ncu captures
+    (profiles/dram_traffic.json): (bytes, provenance), or (None, why) when there is no capture of THIS kernel on
+    this workload - a figure taken with another kernel is not reported."""
     path = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return json.load(f).get(key)
-    return None
+    if key is None or not os.path.exists(path):
+        return None, "no capture"
+    with open(path) as f:
+        rec = json.load(f).get(key)
+    if not isinstance(rec, dict):
+        return None, "no capture"
+    if rec.get("kernel", "").split("<")[0] != kernel.split("<")[0].split(" ")[0]:
+        return None, "the capture on file is of %s" % rec.get("kernel")
+    return rec["bytes"], rec.get("source")
+
+
+def roofline(kernel, algorithmic_bytes, avg_launch_ms, traffic_key, compulsory_bytes=None):
+    peak, peak_kind = load_peaks()
+    achieved = algorithmic_bytes / (avg_launch_ms * 1e-3) / 1e9
+    traffic, source = load_traffic(traffic_key, kernel)
+    out = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "peak_kind": "of " + peak_kind,
+           "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
+           "algorithmic_bytes_per_launch": algorithmic_bytes, "avg_launch_ms": avg_launch_ms,
+           "traffic": traffic, "traffic_source": source,
+           "dram_frac": None if traffic is None else traffic / (avg_launch_ms * 1e-3) / 1e9 / peak,
+           "note": "frac counts algorithmic bytes (L2 hits included, can exceed 1); dram_frac counts DRAM bytes"}
+    if compulsory_bytes is not None:
+        out["compulsory_bytes_per_launch"] = compulsory_bytes
+        out["compulsory_frac"] = compulsory_bytes / (avg_launch_ms * 1e-3) / 1e9 / peak
+    return out
 
 
 class ClockSampler:
@@ -104,7 +136,7 @@ class ClockSampler:
 class SpmmWorkload:
     """configs[1]: forward and transposed sum-aggregation SpMM."""
     name = "spmm_rmat_n2097152_e67108864_d256_fwd_bwd"
-    dominant_kernel = "spmm_kernel<32,1,8,4,false,true>"
+    dominant_kernel = "spmm_stream_kernel<8,4,16,true,true>"
 
     def __init__(self, device, n=1 << 21, e=1 << 26, d=256):
         import torch
@@ -127,6 +159,7 @@ class SpmmWorkload:
         # algorithmic bytes of ONE SpMM launch: per edge a feature row, a column id and a weight; per row a
         # pointer and the written output row
         self.kernel_bytes = self.nnz * (4 * d + 8) + (n + 1) * 4 + 4 * n * d
+        self.compulsory_bytes = self.nnz * 8 + (n + 1) * 4 + 2 * 4 * n * d  # every source row and output row once
         self.traffic_key = "spmm_rmat_d256"
 
     def step(self, kernel_events=None):
@@ -246,6 +279,7 @@ class GatWorkload:
         self.launches_per_step = 1 + 3  # fused forward; backward = edge kernel, transposed SpMM, per-source sum
         self.kernel_launches_per_step = 1
         self.kernel_bytes = self.nnz * (4 + 4 * H + 4 * H * F) + n * (4 + 4 * H + 4 * H * F + 8 * H)
+        self.compulsory_bytes = self.nnz * 4 + n * (4 + 8 * H + 2 * 4 * H * F + 8 * H)
         self.traffic_key = "gat_fwd_h8_f32"
 
     def step(self, kernel_events=None):
@@ -316,6 +350,7 @@ class RgcnWorkload:
             self.nnz += g.nnz
             self.kernel_bytes += g.nnz * (4 * d + 8) + (sizes[dt] + 1) * 4 + 4 * sizes[dt] * d
         self.kernel_bytes //= len(self.groups)
+        self.compulsory_bytes = None
         self.units_per_step = self.nnz * d
         self.launches_per_step = sum(1 + (1 if g.plan() else 0) for g, *_ in self.groups)
         self.kernel_launches_per_step = len(self.groups)
@@ -358,14 +393,14 @@ class RgcnWorkload:
                         g.n_rows, g.nnz, self.nnz))
 
 
-def cpu_baseline(sample, repeats=5):
+def cpu_baseline(sample, repeats=5, min_seconds=10.0):
     """Times the CPU restatement (oracle/yitu_oracle.c, OpenMP over destination rows) on the sample."""
     from oracle import oracle as O
     cores = len(os.sched_getaffinity(0))
     O.build()
     cores = O.set_threads(cores)  # torchrun exports OMP_NUM_THREADS=1: ask for every core explicitly
     best, spent, done = None, 0.0, 0
-    while done < repeats or (spent < 10.0 and done < 40):  # at least `repeats` passes and about 10 s of CPU work
+    while done < repeats or (spent < min_seconds and done < 40):  # at least `repeats` passes and about 10 s of CPU work
         done += 1
         t0 = time.perf_counter()
         if sample.get("gat"):
@@ -407,6 +442,73 @@ def scipy_sanity(sample, max_edges=4_000_000):
 
 
 WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload}
+
+
+def cpu_baseline_partitioned(dev, n, e, d, repeats=5, min_seconds=10.0):
+    """CPU baseline of the partitioned workload: the rows of partition 8 of 16 (1/16 of the edges) of the same graph,
+    whole feature matrix, OpenMP restatement on all host cores."""
+    import torch
+    from yitu_b200 import graphs
+    indptr, indices, values = graphs.spmm_partitioned(device=dev, n=n, e=e)
+    nnz = indices.numel()
+    lo, hi = torch.searchsorted(indptr, torch.tensor([(8 * nnz + 15) // 16, (9 * nnz + 15) // 16], device=dev)).tolist()
+    e0, e1 = int(indptr[lo]), int(indptr[hi])
+    sample = dict(indptr=(indptr[lo:hi + 1] - e0).cpu().numpy(), indices=indices[e0:e1].cpu().numpy(),
+                  values=values[e0:e1].cpu().numpy(), nnz=e1 - e0, d=d,
+                  sample="partition 8 of 16 (%d rows, %d of %d edges), forward SpMM, full feature matrix" % (
+                      hi - lo, e1 - e0, nnz))
+    del indptr, indices, values
+    sample["x"] = graphs.randn_features(1, n, d, device=dev).cpu().numpy()
+    torch.cuda.empty_cache()
+    out = cpu_baseline(sample, repeats=repeats, min_seconds=min_seconds)
+    out.pop("scipy_single_thread", None)
+    return out
+
+
+def _measure(wl, steps=5, warmup=3):
+    """(ms per step, mean ms of the dominant kernel's launches) by CUDA events, after `warmup` untimed steps."""
+    import torch
+    wl.verify()
+    for _ in range(warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    events = []
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        wl.step(events)
+    b.record()
+    torch.cuda.synchronize()
+    kms = [x.elapsed_time(y) for x, y in events]
+    return a.elapsed_time(b) / steps, sum(kms) / len(kms), kms
+
+
+def sub_record_spmm(dev, steps=5):
+    """configs[1] beside the headline: forward + transposed SpMM, D=256, with the roofline of its kernel."""
+    wl = SpmmWorkload(dev)
+    ms, k_ms, _ = _measure(wl, steps)
+    return {"workload": wl.name, "nnz": wl.nnz, "ms_per_step": ms, "value": wl.units_per_step / (ms * 1e-3) / 1e9,
+            "unit": UNIT, "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, k_ms, wl.traffic_key, wl.compulsory_bytes)}
+
+
+def sub_record_gat(dev, steps=5):
+    """The other half of the headline metric, "GAT layer ms": fused GAT layer core on the uniform 8x32 graph
+    (configs[2]), forward, backward and both, with the roofline of the forward kernel."""
+    wl = GatWorkload(dev)
+    total, fwd, _ = _measure(wl, steps)
+    return {"workload": wl.name, "nnz": wl.nnz, "fwd_ms": fwd, "bwd_ms": total - fwd, "fwd_bwd_ms": total,
+            "value": wl.units_per_step / (total * 1e-3) / 1e9, "unit": UNIT,
+            "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, fwd, wl.traffic_key, wl.compulsory_bytes)}
+
+
+def sub_record_rgcn(dev, steps=5):
+    """configs[3]: hetero RGCN aggregation, one stitched pass per destination type (4 launches per step)."""
+    wl = RgcnWorkload(dev)
+    ms, k_ms, kms = _measure(wl, steps)
+    per_type = [sum(kms[i::len(wl.groups)]) / steps for i in range(len(wl.groups))]
+    return {"workload": wl.name, "nnz": wl.nnz, "ms_per_step": ms, "ms_per_destination_type": per_type,
+            "value": wl.units_per_step / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, k_ms, wl.traffic_key)}
 
 
 def run_reference_gpu_comparison(args):
@@ -675,55 +777,6 @@ def run_reorder(args):
     print(json.dumps(out))
 
 
-def gat_layer_ms(dev, steps=5):
-    """The other half of the headline metric, "GAT layer ms": fused GAT layer core on the uniform 8x32 graph
-    (configs[2]), forward and forward+backward, CUDA events after 3 warm-up steps."""
-    import torch
-    wl = GatWorkload(dev)
-    wl.verify()
-    for _ in range(3):
-        wl.step()
-    torch.cuda.synchronize()
-    events = []
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        wl.step(events)
-    b.record()
-    torch.cuda.synchronize()
-    fwd = sum(x.elapsed_time(y) for x, y in events) / len(events)
-    total = a.elapsed_time(b) / steps
-    return {"workload": wl.name, "nnz": wl.nnz, "fwd_ms": fwd, "bwd_ms": total - fwd, "fwd_bwd_ms": total,
-            "value": wl.units_per_step / (total * 1e-3) / 1e9, "unit": UNIT}
-
-
-def partitioned_single_gpu_base(dev, steps=5):
-    """The N>1 workload (row-partitioned SpMM graph) on this one GPU, so that a scaling series that starts from the
-    default N=1 line has its like-for-like base: returns Gedge*feat/s and ms per step."""
-    import torch
-    from yitu_b200 import graphs
-    from yitu_b200.distributed import PartitionedSpmm, RowShard
-    n, e, d = 1 << 24, 1 << 29, 128
-    indptr, indices, values = graphs.spmm_partitioned(device=dev, n=n, e=e)
-    shard = RowShard(indptr, indices, values, [0, n], 0)
-    runner = PartitionedSpmm(shard, d, dev, mode="local")
-    runner.x_local.copy_(graphs.randn_features(1, n, d, device=dev))
-    for _ in range(3):
-        runner.step()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        runner.step()
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / steps
-    nnz = indices.numel()
-    runner.close()
-    return {"workload": "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d), "nnz": nnz, "ms_per_step": ms,
-            "value": nnz * d / (ms * 1e-3) / 1e9, "unit": UNIT}
-
-
 def run_single(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -769,8 +822,6 @@ def run_single(args):
     value = wl.units_per_step / (ms_step * 1e-3) / 1e9
     kms = [a.elapsed_time(b) for a, b in kernel_events]
     k_avg_ms = sum(kms) / len(kms)
-    peak, peak_kind = load_peaks()
-    achieved = wl.kernel_bytes / (k_avg_ms * 1e-3) / 1e9
 
     # end to end: pinned host features in, results back to pinned host memory, every step
     e2e = None
@@ -803,27 +854,11 @@ def run_single(args):
             "data": "synthetic",
             "config": {"workload": wl.name, "nnz": wl.nnz, "l2": "inputs_larger_than_l2",
                        "edge_feats_per_step": wl.units_per_step},
-            "roofline": {"bound": "hbm", "kernel": wl.dominant_kernel, "achieved": achieved, "peak": peak,
-                         "peak_kind": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "frac_of_nominal_8000": achieved / 8000.0, "algorithmic_bytes_per_launch": wl.kernel_bytes,
-                         "avg_launch_ms": k_avg_ms, "traffic": load_traffic(wl.traffic_key)},
+            "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, k_avg_ms, None if args.scale else wl.traffic_key,
+                                 getattr(wl, "compulsory_bytes", None)),
             "cpu_baseline": base,
-            "scaling_base_1gpu": None,
-            "gat_layer": None,
             "e2e": e2e,
             "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
-    if args.workload == "spmm" and not args.scale and not args.no_scaling_base:
-        del wl, kernel_events
-        torch.cuda.empty_cache()
-        try:
-            line["scaling_base_1gpu"] = partitioned_single_gpu_base(dev)
-        except Exception as exc:  # never lose the headline line to the extra measurement
-            line["scaling_base_1gpu"] = {"error": str(exc)[:200]}
-        torch.cuda.empty_cache()
-        try:
-            line["gat_layer"] = gat_layer_ms(dev)
-        except Exception as exc:
-            line["gat_layer"] = {"error": str(exc)[:200]}
     print(json.dumps(line))
 
 
@@ -837,15 +872,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
-    ap.add_argument("--no-scaling-base", action="store_true",
-                    help="default workload: skip timing the N>1 workload on this one GPU")
+    ap.add_argument("--no-sub-records", action="store_true",
+                    help="default workload at N=1: skip the spmm_c2 / gat_layer / rgcn_layer sub-records")
+    ap.add_argument("--halo", default="push,peer",
+                    help="partitioned, N>1: exchange modes to try for 3 steps each, the fastest is timed "
+                         "(push | push1..push4 | pushnp | peer | allgather)")
     ap.add_argument("--row-cost", type=int, default=0,
                     help="partitioned: balance edges + ROW_COST * rows instead of edges alone (not the prescribed split)")
-    ap.add_argument("--no-single", action="store_true", help="partitioned: skip the 1-GPU comparison run on rank 0")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload is None:
-        args.workload = "spmm" if max(args.gpus, world) == 1 else "partitioned"
+        args.workload = "partitioned"  # one series at every N: the same graph on 1, 2, 4 and 8 GPUs
     if args.workload == "partitioned":
         import bench_partitioned
         bench_partitioned.run(args)

@@ -1,9 +1,14 @@
 """bench.py's leg for the row-partitioned SpMM (R-MAT N=2^24, 2^29 sampled edges, int64 row pointers, fp32
-weights 1/in-degree, 128 features), one process per GPU.  Strong scaling: the graph is fixed, each rank
-aggregates its edge-balanced row range.  Every rank builds the same graph from the same seed on its own GPU
-(integer generator, bit-identical everywhere) and keeps its shard."""
+weights 1/in-degree, 128 features), one process per GPU; with one GPU the shard is the whole graph.  Strong
+scaling: the graph is fixed, each rank aggregates its edge-balanced row range.  Every rank builds the same graph
+from the same seed on its own GPU (integer generator, bit-identical everywhere) and keeps its shard.
+
+Before anything is timed every rank checks rows of its own output against float64 sums formed from the definition
+(features are a function of the global row id, so any rank can produce any source row); the line carries the
+outcome as "verify" and the process exits non-zero when the check fails."""
 import json
 import os
+import sys
 import time
 
 import torch
@@ -11,40 +16,51 @@ import torch.distributed as dist
 
 METRIC = "aggregation_gedge_feat_per_s"
 UNIT = "Gedge*feat/s"
-NVLINK_PEER_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+NVLINK_PEER_GBS = 770.0  # peer-copy bandwidth per direction measured between two B200s through NVSwitch (nominal 900)
+FEATURE_SEED = 1
+
+
+def workload_name(n, e, d):
+    return "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d)
 
 
 def _reference_leg(args, device, n, e, d):
-    """CPU restatement on all host cores, on the rows of partition 0 of 16 (bounded sample)."""
+    """CPU restatement on all host cores, on the rows of partition 8 of 16 (bounded sample).  The graph is made with
+    torch on the GPU (the generator is plain tensor arithmetic); nothing of the CUDA library is loaded or called."""
     from oracle import oracle as O
     from yitu_b200 import graphs
-    from yitu_b200.distributed.partition import RowShard, partition_bounds
     indptr, indices, values = graphs.spmm_partitioned(device=device, n=n, e=e)
-    bounds = partition_bounds(indptr, 16)
-    sh = RowShard(indptr, indices, values, bounds, 8)
-    x = graphs.randn_features(1, n, d, device=device).cpu().numpy()
-    ip, ix, vals = sh.indptr.cpu().numpy(), sh.indices.cpu().numpy(), sh.values.cpu().numpy()
+    nnz = indices.numel()
+    targets = torch.tensor([(8 * nnz + 15) // 16, (9 * nnz + 15) // 16], device=device)
+    lo, hi = torch.searchsorted(indptr, targets).tolist()  # the edge-balanced bounds of partition 8 of 16
+    e0, e1 = int(indptr[lo]), int(indptr[hi])
+    x = graphs.randn_features(FEATURE_SEED, n, d, device=device).cpu().numpy()
+    ip = (indptr[lo:hi + 1] - e0).cpu().numpy()
+    ix, vals = indices[e0:e1].cpu().numpy(), values[e0:e1].cpu().numpy()
+    del indptr, indices, values
     O.build()
     cores = O.set_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1
     best = None
-    for _ in range(max(1, args.steps + args.warmup)):
+    reps = max(1, args.steps + args.warmup)
+    for _ in range(reps):
         t0 = time.perf_counter()
         O.spmm(ip, ix, x, wmode=O.W_EDGE, values=vals)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    value = sh.nnz * d / best / 1e9
+    value = (e1 - e0) * d / best / 1e9
     base = {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "seconds": round(best, 3),
             "sample": "partition 8 of 16 (%d rows, %d of %d edges), forward SpMM, full feature matrix; best of %d" % (
-                sh.n_local, sh.nnz, indices.numel(), max(1, args.steps + args.warmup))}
+                hi - lo, e1 - e0, nnz, reps)}
     print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": best * 1e3, "higher_is_better": True,
                       "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d),
+                      "config": {"workload": workload_name(n, e, d),
                                  "note": "CPU restatement of the reference kernels; the reference has no CPU "
                                          "implementation of this path"},
                       "cpu_baseline": base,
                       "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                       "gpu_launches": 0}))
+    return base
 
 
 def _time_steps(runner, steps, world, events=None):
@@ -66,9 +82,43 @@ def _time_steps(runner, steps, world, events=None):
     return float(ms)
 
 
+def verify_rows(shard, out, d, n_random=96, chunk=1 << 16):
+    """Sampled rows of this rank's output against float64 sums taken from the definition, out[r] = sum_e w_e * x[col_e]
+    with x regenerated from the global column ids: the longest row, the last row, the row that holds the largest
+    source id, and seeded random ones.  Returns (rows checked, worst |err| / max|truth|, ok) at the parity bar of the
+    test suite, |err| <= 1e-5 * (|truth| + max|truth|)."""
+    from yitu_b200 import graphs
+    dev = out.device
+    n_local = shard.n_local
+    if n_local == 0:
+        return 0, 0.0, True
+    deg = shard.indptr[1:] - shard.indptr[:-1]
+    gen = torch.Generator(device="cpu").manual_seed(1000 + shard.rank)
+    picks = [int(deg.argmax()), n_local - 1, 0]
+    if shard.nnz:
+        far = int(shard.indices.argmax())
+        picks.append(int(torch.searchsorted(shard.indptr, torch.tensor([far], device=dev), right=True)[0]) - 1)
+    picks += torch.randint(0, n_local, (n_random,), generator=gen).tolist()
+    rows = sorted(set(picks))
+    truth = torch.zeros(len(rows), d, dtype=torch.float64, device=dev)
+    for i, r in enumerate(rows):
+        b, e = int(shard.indptr[r]), int(shard.indptr[r + 1])
+        for s in range(b, e, chunk):
+            t = min(s + chunk, e)
+            cols = shard.indices[s:t].long()
+            xs = graphs.randn_rows(FEATURE_SEED, cols, d).double()
+            w = shard.values[s:t].double() if shard.values is not None else torch.ones(t - s, dtype=torch.float64, device=dev)
+            truth[i] += (w[:, None] * xs).sum(0)
+    got = out[torch.tensor(rows, device=dev)].double()
+    scale = float(truth.abs().max())
+    err = (got - truth).abs()
+    ok = bool(torch.isfinite(got).all()) and float((err - 1e-5 * (truth.abs() + scale)).max()) <= 0.0
+    return len(rows), float(err.max()) / max(scale, 1e-30), ok
+
+
 def run(args):
-    import bench  # the repo-root script: clock sampler and peak numbers
-    from yitu_b200 import graphs, ops
+    import bench  # the repo-root script: clock sampler, peak numbers, the secondary workloads
+    from yitu_b200 import graphs
     from yitu_b200.distributed.partition import RowShard, partition_bounds
     from yitu_b200.distributed.runtime import PartitionedSpmm
 
@@ -82,8 +132,7 @@ def run(args):
     dev = torch.device("cuda", local_rank)
 
     if args.impl == "reference":
-        if rank == 0:
-            _reference_leg(args, dev, n, e, d)
+        _reference_leg(args, dev, n, e, d)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -93,21 +142,41 @@ def run(args):
     nnz = indices.numel()
     bounds = partition_bounds(indptr, world, row_cost=args.row_cost)
     shard = RowShard(indptr, indices, values, bounds, rank)
-    if rank != 0:
-        del indptr, indices, values
+    del indptr, indices, values
     torch.cuda.empty_cache()
-    x_shard = graphs.randn_features(1, shard.n_local, d, device=dev, row_begin=shard.row_begin)
+    x_shard = graphs.randn_features(FEATURE_SEED, shard.n_local, d, device=dev, row_begin=shard.row_begin)
 
-    candidates = [("local", False, 1)] if world == 1 else [("peer", False, 1), ("peer", True, 1), ("allgather", False, 1)]
-    runners, trial = {}, {}
-    for mode, overlap, blocks in candidates:
-        r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap, row_blocks=blocks)
+    modes = ["local"] if world == 1 else [m for m in args.halo.split(",") if m]
+    runners, trial, verify = {}, {}, {}
+    for mode in modes:
+        kw = {}
+        name = mode
+        if mode.startswith("push"):  # "push", "push1".."push4": at most that many phases; "pushnp": no priority rank
+            kw = dict(max_phases=int(mode[4:]) if mode[4:].isdigit() else 3,
+                      priority=None if mode.endswith("np") else "auto")
+            mode = "push"
+        r = PartitionedSpmm(shard, d, dev, mode=mode, **kw)
         r.x_local.copy_(x_shard)
-        key = mode + ("+overlap" if overlap else "") + ("+rowblocks%d" % blocks if blocks > 1 else "")
-        runners[key] = r
+        runners[name] = r
+        out = None
         for _ in range(3):
-            r.step()
-        trial[key] = _time_steps(r, 3, world)
+            out = r.step()
+        # correctness first: sampled rows of this rank's result against float64, before anything is timed
+        k, err, ok = verify_rows(shard, out, d)
+        stat = torch.tensor([float(k), err, 0.0 if ok else 1.0], device=dev, dtype=torch.float64)
+        if world > 1:
+            both = [torch.zeros_like(stat) for _ in range(world)]
+            dist.all_gather(both, stat)
+            stat = torch.stack(both)
+            stat = torch.stack([stat[:, 0].sum(), stat[:, 1].max(), stat[:, 2].sum()])
+        verify[name] = {"rows": int(stat[0]), "max_rel_err": float(stat[1]), "ok": float(stat[2]) == 0.0,
+                        "bar": "|err| <= 1e-5*(|truth| + max|truth|), float64 truth, every rank checks its own rows"}
+        trial[name] = _time_steps(r, 3, world)
+    bad = [k for k, v in verify.items() if not v["ok"]]
+    if bad:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "error": "result check failed", "verify": verify}))
+        sys.exit(1)
     best = min(trial, key=trial.get)
     runner = runners[best]
     for k, r in runners.items():
@@ -126,107 +195,159 @@ def run(args):
     value = nnz * d / (ms_step * 1e-3) / 1e9
 
     spmm_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "spmm"]
-    fetch_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "fetch"]
-    # this library's kernels per step on this rank: one gather per fetch, one SpMM (+ one hub reduction when the
-    # graph it ran on has split rows) per aggregation
-    n_fetch = len(fetch_ms) / args.steps
+    move_ms = [a.elapsed_time(b) for tag, a, b in events if tag in ("fetch", "push")]
     n_spmm = len(spmm_ms) / args.steps
-    has_hub = 1 if runner.graph.plan() is not None else 0  # (row-block runs: counted from the whole-shard graph)
-    launches_per_step = n_fetch + n_spmm * (1 + has_hub)
-    k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (one or two launches)
+    n_move = sum(1 for tag, _, _ in events if tag == "fetch") / args.steps
+    if runner.mode == "push":
+        n_move = (runner._push_first is not None) + (runner._push_rest is not None)
+        graphs_used = [g for g, _, _ in runner._passes]
+    else:
+        graphs_used = [runner.graph]
+    # this library's kernels per step on this rank: the gather / push kernels, one SpMM per pass and one hub
+    # reduction for every pass whose graph has split rows
+    launches = n_move + sum(1 + (1 if g.plan() is not None else 0) for g in graphs_used)
+    k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (all passes)
     k_bytes = shard.nnz * (4 * d + 8) + (shard.n_local + 1) * 8 + 4 * shard.n_local * d
-    by_owner = [0.0] * world  # bytes this rank pulls from each owner per step
+    by_owner = [0.0] * world  # bytes this rank receives from each owner per step
     if getattr(runner, "plan", None) is not None and world > 1:
         off = runner.plan.owner_offsets
         by_owner = [float((off[p + 1] - off[p]) * d * 4) for p in range(world)]
-    stats = torch.tensor([k_ms, sum(fetch_ms) / args.steps if fetch_ms else 0.0, float(runner.halo_bytes),
-                          float(shard.nnz), float(shard.n_local)] + by_owner, device=dev, dtype=torch.float64)
+    stats = torch.tensor([k_ms, sum(move_ms) / args.steps if move_ms else 0.0, float(runner.halo_bytes),
+                          float(shard.nnz), float(shard.n_local), float(launches), n_spmm] + by_owner,
+                         device=dev, dtype=torch.float64)
     all_stats = [torch.zeros_like(stats) for _ in range(world)]
     if world > 1:
         dist.all_gather(all_stats, stats)
     else:
         all_stats = [stats]
 
-    # end to end: pinned host shard in, result shard back to pinned host memory, every step
+    # end to end: pinned host shard in, result shard back to pinned host memory, every step.  The copies of
+    # neighbouring steps overlap the aggregation: step k+1's features arrive in a staging buffer on a copy-in stream
+    # while step k aggregates and step k-1's result leaves from a second staging buffer on a copy-out stream (PCIe is
+    # full duplex); every step's H2D and D2H lie inside the timed region.
     h_x = x_shard.cpu().pin_memory()
     h_out = torch.empty(shard.n_local, d).pin_memory()
+    stage_in, stage_out = torch.empty_like(x_shard), torch.empty_like(x_shard)
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
     class E2E:
         device = dev
 
+        def __init__(self):
+            self.in_done = self.consumed = self.out_ready = self.out_free = None
+
+        def prefetch(self):
+            with torch.cuda.stream(s_in):
+                if self.consumed is not None:
+                    s_in.wait_event(self.consumed)
+                stage_in.copy_(h_x, non_blocking=True)
+                self.in_done = s_in.record_event()
+
         def step(self, events=None):
-            runner.x_local.copy_(h_x, non_blocking=True)
-            h_out.copy_(runner.step(), non_blocking=True)
+            main = torch.cuda.current_stream(dev)
+            if self.in_done is None:
+                s_in.wait_stream(main)
+                self.prefetch()
+            main.wait_event(self.in_done)
+            runner.x_local.copy_(stage_in, non_blocking=True)
+            self.consumed = main.record_event()
+            self.prefetch()  # the next step's input, while this one aggregates
+            out = runner.step()
+            if self.out_free is not None:
+                main.wait_event(self.out_free)
+            stage_out.copy_(out, non_blocking=True)
+            self.out_ready = main.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(self.out_ready)
+                h_out.copy_(stage_out, non_blocking=True)
+                self.out_free = s_out.record_event()
+
+        def drain(self):
+            main = torch.cuda.current_stream(dev)
+            main.wait_stream(s_out)
+            main.wait_stream(s_in)
 
     e2e_runner = E2E()
     for _ in range(2):
         e2e_runner.step()
-    e2e_ms = _time_steps(e2e_runner, max(2, min(args.steps, 5)), world)
+    e2e_runner.drain()
+    e2e_steps = max(3, min(args.steps, 6))
+
+    class Timed:
+        device = dev
+
+        def step(self, events=None):
+            e2e_runner.step()
+            if self.left == 1:
+                e2e_runner.drain()  # the last result has to be on the host before the clock stops
+            self.left -= 1
+
+    timed = Timed()
+    timed.left = e2e_steps
+    e2e_ms = _time_steps(timed, e2e_steps, world)
     bytes_io = torch.tensor([h_x.numel() * 4.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(bytes_io)
-
-    # the same aggregation on one GPU, for the speed-up (rank 0 only, outside the timed region)
-    single = None
-    if world > 1 and rank == 0 and not args.no_single:
-        sh1 = RowShard(indptr, indices, values, [0, n], 0)
-        r1 = PartitionedSpmm(sh1, d, dev, mode="local")
-        r1.x_local.copy_(graphs.randn_features(1, n, d, device=dev))
-        for _ in range(3):
-            r1.step()
-        single = nnz * d / (_time_steps(r1, max(3, args.steps // 2), 1) * 1e-3) / 1e9
-    if world > 1:
         dist.barrier()
+    torch.cuda.synchronize(dev)
+    del stage_in, stage_out, timed
+    schedule = runner.schedule.describe() if runner.schedule is not None else None
+    runner.close()
+    del runner, runners, h_x, h_out, x_shard, shard, e2e_runner
+    torch.cuda.empty_cache()
 
     if rank == 0:
         peak, peak_kind = bench.load_peaks()
         per_rank = [[float(v) for v in s.tolist()] for s in all_stats]
-        achieved = k_bytes / (k_ms * 1e-3) / 1e9
-        max_halo = max(s[2] for s in per_rank)
-        max_fetch = max(s[1] for s in per_rank)
+        egress = [sum(s[7 + o] for s in per_rank) for o in range(world)]
+        move_max = max(s[1] for s in per_rank)
+        roof = bench.roofline("spmm_stream_kernel<4,8,16,true,true>" + (" (rank 0 shard, all passes)" if world > 1 else ""),
+                              k_bytes, k_ms, "spmm_partitioned_d128" if world == 1 and not args.scale else None)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "partitioned_spmm_rmat_n%d_e%d_d%d" % (n, e, d), "nnz": nnz,
+                "config": {"workload": workload_name(n, e, d), "nnz": nnz,
                            "parallelism": "row_partition_%d" % world,
                            "balance": "edges" if not args.row_cost else "edges + %d * rows" % args.row_cost,
-                           "halo": best, "trial_ms": trial,
+                           "halo": best, "trial_ms": trial, "schedule": schedule,
                            "l2": "inputs_larger_than_l2", "rows_per_rank": [int(s[4]) for s in per_rank],
                            "edges_per_rank": [int(s[3]) for s in per_rank],
                            "halo_bytes_per_rank": [int(s[2]) for s in per_rank],
-                           "egress_bytes_per_rank": [int(sum(s[5 + o] for s in per_rank)) for o in range(world)],
+                           "egress_bytes_per_rank": [int(v) for v in egress],
                            "spmm_ms_per_rank": [round(s[0], 3) for s in per_rank],
-                           "fetch_ms_per_rank": [round(s[1], 3) for s in per_rank]},
-                "roofline": {"bound": "hbm", "kernel": "spmm_kernel<32,1,4,false> (rank 0 shard)",
-                             "achieved": achieved, "peak": peak, "peak_kind": "of " + peak_kind, "unit": "GB/s",
-                             "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
-                             "algorithmic_bytes_per_launch": k_bytes, "avg_launch_ms": k_ms,
-                             "traffic": bench.load_traffic("spmm_partitioned_d128")},
-                "nvlink": None if max_fetch == 0 else {
-                    "halo_fetch_ms_max": max_fetch, "halo_bytes_max": max_halo,
-                    "achieved_gbs": max(s[2] / (s[1] * 1e-3) / 1e9 for s in per_rank if s[1] > 0),
-                    "peak_gbs": NVLINK_PEER_GBS, "note": "plain peer loads, each needed source row crosses once"},
-                "single_gpu_value": single, "speedup_vs_single_gpu": None if single is None else value / single,
+                           "spmm_passes_per_rank": [int(round(s[6])) for s in per_rank],
+                           "exchange_ms_per_rank": [round(s[1], 3) for s in per_rank]},
+                "verify": verify[best],
+                "roofline": roof,
+                "nvlink": None if move_max == 0 else {
+                    "largest_egress_bytes": max(egress), "its_exchange_ms": per_rank[egress.index(max(egress))][1]
+                    if best.startswith("push") else move_max,
+                    "achieved_gbs": (max(egress) / (per_rank[egress.index(max(egress))][1] * 1e-3) / 1e9)
+                    if best.startswith("push") else max(s[2] / (s[1] * 1e-3) / 1e9 for s in per_rank if s[1] > 0),
+                    "peak_gbs": NVLINK_PEER_GBS,
+                    "note": ("owner-side push: bytes leaving the busiest owner / duration of its push kernels"
+                             if best.startswith("push") else
+                             "reader-side peer loads: halo bytes of a rank / duration of its gather kernel (best rank)")},
                 "cpu_baseline": None,
-                "e2e": {"value": nnz * d / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
-                        "h2d_bytes_per_step": int(bytes_io), "d2h_bytes_per_step": int(bytes_io)},
-                "gpu_launches": int(round(launches_per_step)) * args.steps * world, "clocks": clocks}
-        if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle as O
-            sh = RowShard(indptr, indices, values, partition_bounds(indptr, 16), 8)
-            xs = graphs.randn_features(1, n, d, device=dev).cpu().numpy()
-            ip, ix, vals = sh.indptr.cpu().numpy(), sh.indices.cpu().numpy(), sh.values.cpu().numpy()
-            O.build()
-            O.set_threads(len(os.sched_getaffinity(0)))
-            t_best = None
-            for _ in range(5):
-                t0 = time.perf_counter()
-                O.spmm(ip, ix, xs, wmode=O.W_EDGE, values=vals)
-                t_best = min(t_best or 1e9, time.perf_counter() - t0)
-            line["cpu_baseline"] = {"value": sh.nnz * d / t_best / 1e9, "unit": UNIT,
-                                    "cores": len(os.sched_getaffinity(0)), "kind": "port", "seconds": round(t_best, 3),
-                                    "sample": "partition 8 of 16 (%d of %d edges), best of 5" % (sh.nnz, nnz)}
+                "e2e": {"value": nnz * d / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": int(bytes_io), "d2h_bytes_per_step": int(bytes_io),
+                        "mode": "pipelined: copy-in / aggregation / copy-out of neighbouring steps overlap"},
+                "gpu_launches": int(round(sum(s[5] for s in per_rank))) * args.steps, "clocks": clocks}
+        if not args.no_cpu_baseline:
+            try:
+                line["cpu_baseline"] = bench.cpu_baseline_partitioned(dev, n, e, d, repeats=5 if world == 1 else 2,
+                                                                          min_seconds=10.0 if world == 1 else 0.0)
+            except Exception as exc:  # never lose the line to the extra measurement
+                line["cpu_baseline"] = {"error": str(exc)[:200]}
+        if world == 1 and not args.scale and not args.no_sub_records:
+            for key, fn in (("spmm_c2", bench.sub_record_spmm), ("gat_layer", bench.sub_record_gat),
+                            ("rgcn_layer", bench.sub_record_rgcn)):
+                try:
+                    line[key] = fn(dev)
+                except Exception as exc:
+                    line[key] = {"error": str(exc)[:200]}
+                torch.cuda.empty_cache()
         print(json.dumps(line))
-    runner.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()

@@ -337,6 +337,17 @@ int yitu_gat_bwd_f32(const yitu_gat_bwd_args_t *args, yitu_stream_t stream);
 int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host, const int64_t *shard_bounds_host,
                          const int32_t *ids, int64_t n_ids, int64_t row_floats, float *dst, yitu_stream_t stream);
 
+/* The same exchange driven by the OWNER of the rows: row ids[i] of this GPU's shard `x` (local row numbers) is
+ * written to row (i - list_begin_host[d]) of destination d's buffer dst_ptrs_host[d], for the destination d with
+ * list_begin_host[d] <= i < list_begin_host[d+1].  Destination pointers are peer mappings (yitu_shared_open) that
+ * already point at the first row reserved for this owner.  Plain 128-bit stores over NVLink: posted writes, no
+ * collective, no multicast.  Completion of the kernel on `stream` means the rows have left; the destinations must
+ * still learn of it (a stream-ordered collective or event chain that follows this call).  Both `_host` arrays are
+ * HOST memory (n_dests <= 16, n_dests+1 offsets).  Takes the role of the per-destination sends of
+ * YiTu_GNN/distributed/communication.py:230-264. */
+int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, const int64_t *list_begin_host,
+                       const int32_t *ids, const float *x, int64_t row_floats, yitu_stream_t stream);
+
 /* Feature shards that peers can read.  yitu_shared_alloc allocates `bytes` of device memory on the current
  * device (one cudaMalloc, so the pointer is an allocation base) and fills `handle_out` with its 64-byte CUDA IPC
  * handle; another PROCESS passes those bytes to yitu_shared_open, with its own GPU current, and receives a pointer

@@ -10,14 +10,36 @@ if ROOT not in sys.path:
 
 
 def pytest_configure(config):
-    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+    config.addinivalue_line("markers", "gpu: needs a CUDA device")
+
+
+ACHIEVED = {}  # test family -> [worst max-norm relative error, worst element-wise relative error, comparisons]
+
+
+def record_error(family, max_norm_rel, elem_rel):
+    """Keeps the worst achieved errors per test family; written to gpurun_out/parity_errors.json (when that
+    folder exists) at the end of the session, so the tolerance that the tests state can be read beside the error
+    that the kernels actually reach."""
+    cur = ACHIEVED.setdefault(family, [0.0, 0.0, 0])
+    cur[0], cur[1], cur[2] = max(cur[0], float(max_norm_rel)), max(cur[1], float(elem_rel)), cur[2] + 1
+
+
+def pytest_sessionfinish(session, exitstatus):
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if ACHIEVED and os.path.isdir(out_dir):
+        import json
+        with open(os.path.join(out_dir, "parity_errors.json"), "w") as f:
+            json.dump({k: {"max_norm_rel": v[0], "elementwise_rel_where_ref_ge_1pct_of_max": v[1], "comparisons": v[2]}
+                       for k, v in sorted(ACHIEVED.items())}, f, indent=1)
 
 
 def assert_close(got, ref, rtol=1e-5, what=""):
     """fp32 parity bar of the aggregation kernels: |got - ref| <= rtol * (|ref| + max|ref|).
 
     The max|ref| term covers entries that are small through cancellation: a sum of n terms of size s carries
-    a reduction-order error ~ eps*sqrt(n)*s whatever the sum's own size."""
+    a reduction-order error ~ eps*sqrt(n)*s whatever the sum's own size.  The achieved errors are recorded per
+    test family (first word of `what`): max|got-ref| / max|ref|, and the worst element-wise relative error over
+    the entries with |ref| >= 1 % of max|ref| (below that, cancellation makes a relative figure meaningless)."""
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, "%s shape %s vs %s" % (what, got.shape, ref.shape)
@@ -25,6 +47,10 @@ def assert_close(got, ref, rtol=1e-5, what=""):
         return
     assert np.isfinite(got).all(), "%s: non-finite values" % what
     scale = np.abs(ref).max()
+    if scale > 0:
+        big = np.abs(ref) >= 0.01 * scale
+        record_error((what.split() or ["?"])[0], np.abs(got - ref).max() / scale,
+                     (np.abs(got - ref)[big] / np.abs(ref)[big]).max())
     err = np.abs(got - ref) - rtol * (np.abs(ref) + scale)
     worst = err.max()
     assert worst <= 0, "%s: max excess %.3e (max|ref|=%.3e, max abs err %.3e)" % (

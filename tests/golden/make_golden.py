@@ -24,7 +24,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REFERENCE = os.environ.get("YITU_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("YITU_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")  # beside the repository
 
 
 def _load(path, name):

@@ -1,6 +1,7 @@
-"""Row partition and halo bookkeeping on CPU ranks over gloo (world_size 2 and 3): bounds, shards, halo lists and
-renumbered columns are bit-exact against the CPU checker, and the partitioned aggregation assembled from
-[own rows | halo rows] (and from the all-gather layout) equals the single-graph result."""
+"""Row partition and halo bookkeeping on CPU ranks over gloo (world_size 2, 3 and 4): bounds, shards, halo lists and
+renumbered columns are bit-exact against the CPU checker, the partitioned aggregation assembled from
+[own rows | halo rows] (and from the all-gather layout) equals the single-graph result, and the owner-side push
+(request lists, slot layout, schedule, aggregation passes) is consistent across ranks."""
 import os
 import socket
 import sys
@@ -31,7 +32,8 @@ def _worker(rank, world, port, errors):
         dist.init_process_group("gloo", rank=rank, world_size=world)
         from oracle import oracle as O
         from yitu_b200 import graphs
-        from yitu_b200.distributed import HaloPlan, RowShard, allgather_columns, partition_bounds, split_local_halo
+        from yitu_b200.distributed import (HaloPlan, PushSchedule, RowShard, allgather_columns, exchange_need_lists,
+                                           owner_edge_counts, partition_bounds, source_passes)
 
         n, d = 3000, 12
         src, dst = graphs.rmat_edges(4, n, n, 40000)
@@ -84,31 +86,48 @@ def _worker(rank, world, port, errors):
         got = O.spmm(shard.indptr.numpy(), li, xbuf, wmode=O.W_EDGE, values=shard.values.numpy())
         assert np.array_equal(got, ref), "partitioned aggregation must equal the single-graph rows"
 
-        # halo list ordered by the first row block that needs a row
-        rb = [0, shard.n_local // 3, (2 * shard.n_local) // 3, shard.n_local]
-        plan_b = HaloPlan(shard, rb)
-        assert sorted(plan_b.halo_ids.tolist()) == halo.tolist() and plan_b.chunk_offsets[-1] == plan_b.n_halo
-        lib_ = plan_b.local_indices.numpy()
-        hb = plan_b.halo_ids.numpy()
-        assert np.array_equal(np.where(lib_ < shard.n_local, lib_ + lo, hb[np.maximum(lib_ - shard.n_local, 0)]), cols)
-        ipn = shard.indptr.numpy()
-        for b in range(3):
-            used = lib_[ipn[rb[b]]:ipn[rb[b + 1]]]
-            used = used[used >= shard.n_local] - shard.n_local
-            assert used.size == 0 or used.max() < plan_b.chunk_offsets[b + 1], "block b may only use chunks 0..b"
-            seg = hb[plan_b.chunk_offsets[b]:plan_b.chunk_offsets[b + 1]]
-            assert np.all(np.diff(seg) > 0), "ascending ids inside a chunk"
-        xbuf_b = torch.cat([x[lo:hi], x[torch.from_numpy(hb).long()]]).numpy()
-        got_b = O.spmm(shard.indptr.numpy(), lib_, xbuf_b, wmode=O.W_EDGE, values=shard.values.numpy())
-        assert np.array_equal(got_b, ref)
-
-        (ipo, ixo, vo), (iph, ixh, vh) = split_local_halo(shard, plan)
-        assert int(ipo[-1]) + int(iph[-1]) == shard.nnz
-        assert ixo.numel() == 0 or int(ixo.max()) < shard.n_local
-        assert ixh.numel() == 0 or int(ixh.max()) < plan.n_halo
-        part = O.spmm(ipo.numpy(), ixo.numpy(), xbuf[:shard.n_local], wmode=O.W_EDGE, values=vo.numpy()).astype(np.float64)
-        part += O.spmm(iph.numpy(), ixh.numpy(), xbuf[shard.n_local:], wmode=O.W_EDGE, values=vh.numpy())
-        assert np.abs(part - ref).max() <= 1e-5 * np.abs(ref).max()
+        # owner-side push: the request lists that reach every owner, the slot layout, the schedule and the passes
+        need_rows, recv_ids, recv_counts = exchange_need_lists(plan, rank, world)
+        assert need_rows[rank] == [plan.owner_offsets[p + 1] - plan.owner_offsets[p] for p in range(world)]
+        assert all(need_rows[q][q] == 0 for q in range(world))
+        assert recv_ids.numel() == sum(recv_counts) and recv_counts[rank] == 0
+        assert recv_ids.numel() == 0 or (int(recv_ids.min()) >= lo and int(recv_ids.max()) < hi), "only rows this rank owns"
+        # the push itself, emulated by an all-to-all of the requested rows: what arrives, in arrival order
+        # (by owner, ascending ids within an owner), must be exactly the halo part of the reader's buffer
+        sent = x[recv_ids.long()].contiguous()
+        got_rows = torch.empty(plan.n_halo, d)
+        dist.all_to_all_single(got_rows, sent, output_split_sizes=need_rows[rank], input_split_sizes=recv_counts)
+        assert torch.equal(got_rows, x[plan.halo_ids.long()]), "pushed rows must land in the slots the columns point to"
+        mine = torch.tensor(owner_edge_counts(shard, world), dtype=torch.int64)
+        assert int(mine.sum()) == shard.nnz
+        blocks = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(blocks, mine)
+        rows_per_rank = [bounds[p + 1] - bounds[p] for p in range(world)]
+        for max_phases, prio in ((3, "auto"), (1, None), (2, world - 1)):
+            sched = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_phases=max_phases,
+                                 priority=prio)
+            seen = [None] * world
+            dist.all_gather_object(seen, sched.describe())
+            assert all(s_ == seen[0] for s_ in seen), "every rank must derive the same schedule"
+            assert sched.n_phases <= max_phases and sorted(sched.phase_of_owner)[0] == 0
+            my = sched.passes[rank]
+            assert sorted(p for owners, _ in my for p in owners) == list(range(world)), "each owner in exactly one pass"
+            assert rank in my[0][0], "own sources belong to the first pass"
+            if prio == world - 1 and rank == prio:
+                assert my == [(list(range(world)), PushSchedule.PRIORITY)]
+            waits = [w_ for _, w_ in my]
+            assert waits == sorted(waits) or waits[0] == PushSchedule.PRIORITY
+            for owners, wait in my:  # a pass may only use shards whose phase has ended by the time it starts
+                for p in owners:
+                    assert p == rank or wait == PushSchedule.PRIORITY or sched.phase_of_owner[p] <= wait
+            total = np.zeros_like(ref, dtype=np.float64)
+            nnz_sum = 0
+            for ip_j, li_j, v_j, _ in source_passes(shard, plan, my):
+                assert ip_j.numel() == shard.n_local + 1 and int(ip_j[-1]) == li_j.numel() == v_j.numel()
+                nnz_sum += li_j.numel()
+                total += O.spmm(ip_j.numpy(), li_j.numpy(), xbuf, wmode=O.W_EDGE, values=v_j.numpy())
+            assert nnz_sum == shard.nnz
+            assert np.abs(total - ref).max() <= 1e-5 * np.abs(ref).max(), "the passes together give the whole aggregation"
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
@@ -116,7 +135,7 @@ def _worker(rank, world, port, errors):
         raise
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 4])
 def test_partition_and_halo_plan_over_gloo(world):
     ctx = mp.get_context("spawn")
     errors = ctx.SimpleQueue()

@@ -1,5 +1,7 @@
-"""Row-partitioned SpMM on 2 GPUs (one process per GPU, NCCL + CUDA-IPC peer loads): every halo mode must give
-the rows the single-GPU SpMM gives.  Skipped on a single-GPU box."""
+"""Row-partitioned SpMM.  On 2 GPUs (one process per GPU, NCCL + CUDA-IPC peer mappings; skipped on a single-GPU
+box): every exchange mode must give the rows the single-GPU SpMM gives.  On one GPU: the owner-side push and the
+aggregation passes of its schedule with four ranks emulated in one process (every "peer" buffer lives on the same
+GPU and the kernels run one after another on one stream - nothing waits on anything)."""
 import os
 import socket
 import sys
@@ -41,18 +43,21 @@ def _worker(rank, world, port, errors):
         bounds = partition_bounds(indptr, world)
         shard = RowShard(indptr, indices, values, bounds, rank)
         lo, hi = shard.row_begin, shard.row_end
-        for mode, overlap, blocks in (("peer", False, 1), ("peer", True, 1), ("peer", False, 4), ("allgather", False, 1)):
-            r = PartitionedSpmm(shard, d, dev, mode=mode, overlap=overlap, row_blocks=blocks)
-            r.x_local.copy_(x[lo:hi])
-            for _ in range(2):
-                out = r.step()
-            torch.cuda.synchronize(dev)
-            err = float((out - ref[lo:hi]).abs().max())
-            assert err <= 1e-5 * float(ref.abs().max()), "%s overlap=%s blocks=%d: max err %g" % (mode, overlap, blocks, err)
-            if mode == "peer":
-                assert r.plan.n_halo > 0
-                assert torch.equal(r.x_halo, x[r.plan.halo_ids.long()]), "halo rows must be the owners' rows"
-            dist.barrier()
+        for mode, kw in (("push", {}), ("push", dict(max_phases=1, priority=None)), ("push", dict(priority=1)),
+                         ("peer", {}), ("allgather", {})):
+            r = PartitionedSpmm(shard, d, dev, mode=mode, **kw)
+            for step in range(3):  # new features every step: a stale halo row would show
+                xs = x * float(step + 1)
+                r.x_local.copy_(xs[lo:hi])
+                out = r.step(fence=True)
+                torch.cuda.synchronize(dev)
+                err = float((out - ref[lo:hi] * float(step + 1)).abs().max())
+                assert err <= 1e-5 * float(ref.abs().max()) * (step + 1), "%s %s step %d: max err %g" % (mode, kw, step, err)
+                if mode in ("peer", "push"):
+                    assert r.plan.n_halo > 0
+                    assert torch.equal(r.x_halo, xs[r.plan.halo_ids.long()]), "halo rows must be the owners' rows"
+            if mode == "push":
+                assert sum(g.nnz for g, _, _ in r._passes) == shard.nnz
             r.close()
         # differentiable form: forward over this rank's rows of A, backward over the same rows of A^T
         from yitu_b200.distributed import PartitionedAggregate
@@ -97,6 +102,61 @@ def test_partitioned_spmm_two_gpus():
             p.terminate()
             msgs.append("a rank did not finish")
     assert not msgs and all(p.exitcode == 0 for p in procs), "\n".join(msgs)
+
+
+def test_push_exchange_and_passes_with_four_ranks_emulated_on_one_gpu():
+    """yitu_halo_push_f32 and the aggregation passes of a PushSchedule without a second GPU: four ranks' buffers live
+    on this GPU, every owner's push runs as an ordinary kernel on the current stream (its "peer" pointers are local),
+    then every rank aggregates pass by pass.  Checks the slot layout bit for bit and the result against the
+    whole-graph SpMM."""
+    import ctypes as C
+    sys.path.insert(0, ROOT)
+    from yitu_b200 import graphs, ops
+    from yitu_b200._lib import check, lib
+    from yitu_b200.distributed import HaloPlan, PushSchedule, RowShard, owner_edge_counts, partition_bounds, source_passes
+    dev = torch.device("cuda", 0)
+    world, n, d = 4, 1 << 15, 128
+    src, dst = graphs.rmat_edges(4, n, n, 1 << 19, device=dev)
+    indptr, indices = graphs.csr_by_destination(src, dst, n, n, ptr_dtype=torch.int64)
+    deg = (indptr[1:] - indptr[:-1]).clamp(min=1)
+    values = torch.repeat_interleave(1.0 / deg.float(), indptr[1:] - indptr[:-1])
+    x = graphs.randn_features(7, n, d, device=dev)
+    ref = ops.spmm(ops.PreparedGraph(indptr, indices, n), x, mode=ops.W_EDGE, edge_values=values)
+    bounds = partition_bounds(indptr, world)
+    shards = [RowShard(indptr, indices, values, bounds, r) for r in range(world)]
+    plans = [HaloPlan(s) for s in shards]
+    bufs = [torch.full((s.n_local + p.n_halo, d), float("nan"), device=dev) for s, p in zip(shards, plans)]
+    for r, s in enumerate(shards):
+        bufs[r][:s.n_local] = x[s.row_begin:s.row_end]
+    need = [[plans[q].owner_offsets[p + 1] - plans[q].owner_offsets[p] for p in range(world)] for q in range(world)]
+    st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    for p in range(world):  # owner p pushes to every reader q
+        dests = [q for q in range(world) if q != p and need[q][p] > 0]
+        ids = torch.cat([plans[q].halo_ids[plans[q].owner_offsets[p]:plans[q].owner_offsets[p + 1]] for q in dests])
+        ids = (ids - shards[p].row_begin).to(torch.int32).contiguous()
+        begin = [0]
+        for q in dests:
+            begin.append(begin[-1] + need[q][p])
+        dst_ptrs = [bufs[q].data_ptr() + 4 * d * (shards[q].n_local + plans[q].owner_offsets[p]) for q in dests]
+        check(lib().yitu_halo_push_f32(len(dests), (C.c_void_p * len(dests))(*dst_ptrs),
+                                       (C.c_int64 * (len(dests) + 1))(*begin), C.c_void_p(ids.data_ptr()),
+                                       C.c_void_p(bufs[p].data_ptr()), d, st))
+    torch.cuda.synchronize(dev)
+    for q in range(world):
+        assert torch.equal(bufs[q][shards[q].n_local:], x[plans[q].halo_ids.long()]), "rank %d: halo slots" % q
+    blocks = [owner_edge_counts(s, world) for s in shards]
+    rows = [s.n_local for s in shards]
+    for kw in (dict(), dict(max_phases=1, priority=None), dict(max_phases=4, priority=world - 1)):
+        sched = PushSchedule(need, blocks, rows, d, **kw)
+        for q, s in enumerate(shards):
+            out = torch.full((s.n_local, d), float("nan"), device=dev)
+            passes = source_passes(s, plans[q], sched.passes[q])
+            assert sum(li.numel() for _, li, _, _ in passes) == s.nnz
+            for j, (ip, li, vals, _) in enumerate(passes):
+                g = ops.PreparedGraph(ip, li, s.n_local + plans[q].n_halo)
+                ops.spmm(g, bufs[q], mode=ops.W_EDGE, edge_values=vals, out=out, accumulate=j > 0)
+            err = float((out - ref[s.row_begin:s.row_end]).abs().max())
+            assert err <= 1e-5 * float(ref.abs().max()), "rank %d %s: max err %g" % (q, kw, err)
 
 
 def test_partitioned_aggregate_single_gpu_autograd():

@@ -70,6 +70,76 @@ def test_empty_graph_and_empty_rows(oracle):
     assert ops.spmm(g0, torch.randn(4, 8, device="cuda")).shape == (0, 8)
 
 
+def _csr_from_degrees(rng, degs, n_cols):
+    rows = [np.sort(rng.choice(n_cols, size=int(k), replace=False)).astype(np.int32) for k in degs]
+    indptr = np.zeros(len(degs) + 1, dtype=np.int64)
+    indptr[1:] = np.cumsum([len(r) for r in rows])
+    indices = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int32)
+    return indptr, indices.astype(np.int32)
+
+
+STREAM_PATTERNS = {
+    # runs of empty rows at the start, in the middle and at the end of 16-row batches
+    "empty_runs": [0] * 5 + [3, 0, 0, 7, 1] + [0] * 20 + [40, 0, 33, 0, 0, 0] + [2] * 9 + [0] * 18,
+    # rows that end exactly on 32-edge tile borders and on borders of the 4/8/16-edge gather groups
+    "tile_borders": [32, 32, 64, 16, 16, 8, 8, 8, 8, 4, 4, 96, 1, 31, 33, 63, 65],
+    # hub rows (above the 64-edge chunk limit used below) inside batches, adjacent to each other and at the ends
+    "hubs_inside": [70, 3, 0, 200, 130, 5, 1] + [2] * 12 + [300] + [1] * 30 + [65, 64, 66],
+    "single_row": [5],
+    "only_empty": [0] * 37,
+    "one_long_row_no_plan": [1000],
+}
+
+
+@pytest.mark.parametrize("pattern", sorted(STREAM_PATTERNS))
+@pytest.mark.parametrize("D", [96, 128, 136, 256])
+def test_stream_kernel_row_patterns(oracle, monkeypatch, pattern, D):
+    """The edge-stream SpMM (warp = batch of consecutive rows walked as one edge stream) on row patterns that put
+    every bookkeeping branch to work: empty rows anywhere in a batch, rows ending on tile / group borders, hub rows
+    stepped over inside a batch, accumulate mode with and without an epilogue, every batch size and unroll."""
+    from yitu_b200 import ops
+    rng = np.random.default_rng(len(pattern) * 131 + D)
+    n_cols = 1100
+    degs = STREAM_PATTERNS[pattern]
+    indptr, indices = _csr_from_degrees(rng, degs, n_cols)
+    n_rows = len(degs)
+    x = rng.standard_normal((n_cols, D)).astype(np.float32)
+    vals = rng.standard_normal(indices.shape[0]).astype(np.float32)
+    nd = rng.uniform(0.1, 1.0, n_rows).astype(np.float32)
+    ns = rng.uniform(0.1, 1.0, n_cols).astype(np.float32)
+    base = rng.standard_normal((n_rows, D)).astype(np.float32)
+    bias = rng.standard_normal(D).astype(np.float32)
+    chunk = 0 if pattern == "one_long_row_no_plan" else 64
+    ref_edge = oracle.spmm(indptr, indices, x, wmode=oracle.W_EDGE, values=vals)
+    ref_node = oracle.spmm(indptr, indices, x, wmode=oracle.W_NODE, norm_dst=nd, norm_src=ns)
+    ref_acc = oracle.spmm(indptr, indices, x, alpha=0.5, out=base)
+    ref_acc_epi = np.maximum(oracle.spmm(indptr, indices, x, out=base) + bias, 0)
+    for rows, eu in ((16, None), (8, None), (31, None), (16, 16 if D <= 128 else 8)):
+        monkeypatch.setenv("YITU_SPMM_STREAM_ROWS", str(rows))
+        if eu is None:
+            monkeypatch.delenv("YITU_SPMM_STREAM_EU", raising=False)
+        else:
+            monkeypatch.setenv("YITU_SPMM_STREAM_EU", str(eu))
+        for ptr_dtype in (torch.int32, torch.int64):
+            g = ops.PreparedGraph(_dev(indptr, ptr_dtype), _dev(indices), n_cols)
+            tag = "stream %s D=%d rows=%d eu=%s" % (pattern, D, rows, eu)
+            got = ops.spmm(g, _dev(x), mode=ops.W_EDGE, edge_values=_dev(vals), chunk_edges=chunk)
+            assert_close(got.cpu().numpy(), ref_edge, what=tag + " edge")
+            got = ops.spmm(g, _dev(x), mode=ops.W_NODE, norm_dst=_dev(nd), norm_src=_dev(ns), chunk_edges=chunk)
+            assert_close(got.cpu().numpy(), ref_node, what=tag + " node")
+            out = _dev(base).clone()
+            ops.spmm(g, _dev(x), out=out, accumulate=True, alpha=0.5, chunk_edges=chunk)
+            assert_close(out.cpu().numpy(), ref_acc, what=tag + " accumulate")
+            out = _dev(base).clone()
+            ops.spmm(g, _dev(x), out=out, accumulate=True, bias=_dev(bias), activation="relu", chunk_edges=chunk)
+            assert_close(out.cpu().numpy(), ref_acc_epi, what=tag + " accumulate+epilogue")
+    # the warp-per-row kernel on the same inputs gives the same sums up to the order of the additions
+    monkeypatch.setenv("YITU_SPMM_STREAM", "0")
+    g = ops.PreparedGraph(_dev(indptr, torch.int32), _dev(indices), n_cols)
+    got = ops.spmm(g, _dev(x), mode=ops.W_EDGE, edge_values=_dev(vals), chunk_edges=chunk)
+    assert_close(got.cpu().numpy(), ref_edge, what="rows-kernel %s D=%d" % (pattern, D))
+
+
 def test_kernel_module_matches_oracle_on_gcn_graph(oracle):
     """2-layer GCN forward of the small benchmark configuration, plus the other YiTu_GNN_kernel entry points."""
     from yitu_b200 import YiTu_GNN_kernel as K, graphs
@@ -225,3 +295,34 @@ def test_full_size_sampled_rows_against_float64():
     scale_t = float(truth_t.abs().max())
     err_t = (yt[cols.cuda()].double() - truth_t).abs()
     assert float((err_t - 1e-5 * (truth_t.abs() + scale_t)).max()) <= 0, "transposed rows off by %g" % float(err_t.max())
+
+
+def test_partitioned_config_on_one_gpu_sampled_rows_against_float64():
+    """The 8-GPU configuration's graph on one GPU: R-MAT 2^24 nodes, 2^29 sampled edges, int64 row pointers,
+    weights 1/in-degree, 128 features (2^31 feature elements: element offsets use all 32 bits).  Sampled destination
+    rows in float64 - the longest rows, rows whose sources lie at the very end of the feature matrix, and random
+    ones - plus the exact identities A*1 = in-degree and (A/deg)*1 = 1."""
+    from yitu_b200 import graphs, ops
+    n, d = 1 << 24, 128
+    indptr, indices, values = graphs.spmm_partitioned(device="cuda", n=n, e=1 << 29)
+    assert indptr.dtype == torch.int64
+    g = ops.PreparedGraph(indptr, indices, n)
+    deg = indptr[1:] - indptr[:-1]
+    ones = torch.ones(n, 4, device="cuda")
+    assert torch.equal(ops.spmm(g, ones)[:, 0], deg.float()), "A*1 must equal the in-degree exactly"
+    del ones
+    x = graphs.randn_features(1, n, d, device="cuda")
+    y = ops.spmm(g, x, mode=ops.W_EDGE, edge_values=values)
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    # destination rows of the edges whose source id is largest (the last rows of x, offsets just below 2^31)
+    far = torch.topk(indices.long(), 64).indices
+    far_rows = (torch.searchsorted(indptr, far, right=True) - 1).cpu()
+    assert int(indices.max()) * d + d > (1 << 30), "the sample must reach the upper half of the offset range"
+    rows = torch.cat([torch.topk(deg, 16).indices.cpu(), far_rows, torch.randint(0, n, (240,), generator=gen)]).unique()
+    truth = _rows_truth_f64(indptr, indices, values, x, rows)
+    scale = float(truth.abs().max())
+    err = (y[rows.cuda()].double() - truth).abs()
+    assert float((err - 1e-5 * (truth.abs() + scale)).max()) <= 0, "rows off by %g" % float(err.max())
+    from conftest import record_error
+    big = truth.abs() >= 0.01 * scale
+    record_error("partitioned-config-1gpu", float(err.max()) / scale, float((err[big] / truth.abs()[big]).max()))

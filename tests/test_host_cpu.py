@@ -90,6 +90,12 @@ def test_stitch_csr_limits():
     big = Block([1, (1 << 24) + 5], [torch.IntTensor([0, 1]), torch.IntTensor([(1 << 24) + 3])])
     with pytest.raises(AssertionError):  # column beyond 2^24, as the reference asserts
         stitch_csr([big])
+    # the boundary: column 2^24 - 1 is the largest that leaves the segment tag intact.  The reference's
+    # `assert col <= 2**24` lets 2^24 itself through, where it turns into column 0 of the next relation; rejected here.
+    edge = Block([1, 1 << 24], [torch.IntTensor([0, 1]), torch.IntTensor([(1 << 24) - 1])])
+    assert stitch_csr([edge]).adj_sparse[1].tolist() == [(1 << 24) - 1]
+    with pytest.raises(AssertionError):  # shifted by the one column of the block before it: exactly 2^24
+        stitch_csr([one, edge])
 
 
 def test_partition_rows_host(oracle):
@@ -264,3 +270,76 @@ def test_cost_aware_partition_balances_edges_plus_rows():
     rows_plain = np.diff(plain)
     rows_aware = np.diff(aware)
     assert rows_aware.max() < rows_plain.max(), "weighing rows must shrink the largest shard of a skewed graph"
+
+
+def test_operator_wrappers_reject_bad_tensors_before_any_launch():
+    """The tensor-level wrappers hand raw pointers to the kernels; sizes, dtypes, layout and device are checked on
+    the host first.  One rejection per operator, on CPU tensors: the check fires before anything is launched."""
+    from yitu_b200 import ops
+    ip = torch.tensor([0, 2, 3, 3, 5], dtype=torch.int32)
+    ix = torch.tensor([0, 1, 2, 0, 2], dtype=torch.int32)
+    g = ops.PreparedGraph(ip, ix, 3)
+    x = torch.zeros(3, 8)
+    xh = torch.zeros(3, 2, 4)
+    with pytest.raises(RuntimeError, match="edge_values must hold 5"):
+        ops.spmm(g, x, mode=ops.W_EDGE, edge_values=torch.zeros(4))
+    with pytest.raises(RuntimeError, match="edge_values must hold 10"):
+        ops.spmm(g, xh, n_heads=2, mode=ops.W_EDGE_HEAD, edge_values=torch.zeros(5, 1))
+    with pytest.raises(RuntimeError, match="needs edge_values"):
+        ops.spmm(g, x, mode=ops.W_EDGE)
+    with pytest.raises(RuntimeError, match="norm_src must hold 3"):
+        ops.spmm(g, x, mode=ops.W_NODE, norm_dst=torch.zeros(4), norm_src=torch.zeros(4))
+    with pytest.raises(RuntimeError, match="row_scale must hold 4"):
+        ops.spmm(g, x, row_scale=torch.zeros(3))
+    with pytest.raises(RuntimeError, match="edge_perm must have dtype"):
+        ops.spmm(g, x, mode=ops.W_EDGE, edge_values=torch.zeros(5), edge_perm=torch.zeros(5, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="source nodes"):
+        ops.spmm(g, torch.zeros(4, 8))
+    with pytest.raises(RuntimeError, match="out must hold"):
+        ops.spmm(g, x, out=torch.zeros(3, 8))
+    with pytest.raises(RuntimeError, match="grad_out must have shape"):
+        ops.edge_dot(g, torch.zeros(3, 2, 4), xh)
+    with pytest.raises(RuntimeError, match="values must have shape"):
+        ops.spmm_bwd(g, torch.zeros(5, 1), xh, torch.zeros(4, 2, 4))
+    with pytest.raises(RuntimeError, match="query must have shape"):
+        ops.edge_softmax_fwd(g, torch.zeros(1, 3, 2), torch.zeros(3, 2))
+    with pytest.raises(RuntimeError, match="grad_attn must have shape"):
+        ops.edge_softmax_bwd(g, torch.zeros(1, 4, 2), torch.zeros(3, 2), torch.zeros(5, 2), torch.zeros(4, 2))
+    with pytest.raises(RuntimeError, match="key must have shape"):
+        ops.gat_fwd(g, torch.zeros(4, 2), torch.zeros(4, 2), xh)
+    with pytest.raises(RuntimeError, match="row_max must have shape"):
+        ops.gat_bwd(g, torch.zeros(4, 2), torch.zeros(3, 2), xh, torch.zeros(4, 2, 4), torch.zeros(3, 2),
+                    torch.zeros(4, 2), torch.zeros(4, 2, 4))
+    if torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="the graph is on"):
+            ops.spmm(g, x.cuda())
+
+
+def test_prepared_graph_is_found_by_memory_not_by_tensor_object():
+    """Reference-style callers pass a fresh tensor object per call (a view of the same storage): the derived
+    structures must be built once.  An in-place edit of the tables leads to a new build."""
+    from yitu_b200 import ops
+    ip = torch.tensor([0, 2, 3, 3, 5], dtype=torch.int32)
+    ix = torch.tensor([0, 1, 2, 0, 2], dtype=torch.int32)
+    g1 = ops.prepared(ip, ix, 3)
+    g2 = ops.prepared(ip.view(-1), ix[:], 3)          # distinct tensor objects, same memory
+    g3 = ops.prepared(ip.detach(), ix.detach(), 3, 0)
+    assert g1 is g2 and g1 is g3
+    assert ops.prepared(ip, ix, 3, ops.STITCH_MASK) is not g1   # another mask: another entry
+    assert ops.prepared(ip.clone(), ix, 3) is not g1            # other memory
+    ix[0] = 1                                                    # in-place edit bumps the version counter
+    assert ops.prepared(ip, ix, 3) is not g1
+
+
+def test_fused_gat_route_is_closed_for_stitched_blocks():
+    """A stitched block carries relation ids in the top index bits; the fused GAT kernels would read them as column
+    ids.  stitch_csr marks its result, a Block built from raw packed tensors is inspected once."""
+    from yitu_b200.xgnn_h import Block, stitch_csr
+    a = Block([2, 3], [torch.IntTensor([0, 1, 2]), torch.IntTensor([0, 2])])
+    b = Block([2, 2], [torch.IntTensor([0, 1, 1]), torch.IntTensor([1])])
+    assert a.is_stitched() is False
+    st = stitch_csr([a, b])
+    assert st.stitched is True and st.is_stitched() is True
+    assert stitch_csr([a]).is_stitched() is False
+    raw = Block(st.size, [st.adj_sparse[0].clone(), st.adj_sparse[1].clone()])
+    assert raw.stitched is None and raw.is_stitched() is True

@@ -215,7 +215,7 @@ __global__ void stitch_fill_kernel(const __grid_constant__ StitchParams p, const
         const int beg = p.indptr[b][row], end = p.indptr[b][row + 1];
         for (int i = beg + lane; i < end; i += 32) {
             const int col = p.shift[b] + p.indices[b][i];
-            if (col > (1 << 24)) *overflow = 1;
+            if (col >= (1 << 24)) *overflow = 1;  // would carry into the segment tag
             out_indices[w + (i - beg)] = (b << 24) + col;
         }
         w += end - beg;
@@ -463,9 +463,11 @@ extern "C" int yitu_stitch_csr(int32_t n_blocks, int64_t n_rows, const int32_t *
         YITU_REQUIRE(indptrs_host[b] != nullptr, YITU_ERR_INVALID_ARG, "block %d has no row pointers", b);
         p.indptr[b] = indptrs_host[b];
         p.indices[b] = indices_host[b];
-        YITU_REQUIRE(shift <= (1 << 24), YITU_ERR_LIMIT, "stitched column offset %lld exceeds 2^24", (long long)shift);
         p.shift[b] = static_cast<int>(shift);
         shift += n_cols_host[b];
+        // The reference asserts col <= 2**24 (xgnn_h/block.py:52), which lets column 2^24 through: added to the tag it
+        // becomes column 0 of the next relation.  Deliberately stricter here: a stitched column must be below 2^24.
+        YITU_REQUIRE(shift <= (1 << 24), YITU_ERR_LIMIT, "stitched blocks have %lld columns, more than 2^24", (long long)shift);
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     YITU_CUDA(cudaMemsetAsync(overflow_flag, 0, 4, st));
@@ -532,7 +534,8 @@ extern "C" int yitu_stitch_csr_host(int32_t n_blocks, int64_t n_rows, const int3
             const int32_t tag = b << 24;
             for (int32_t i = ip[r]; i < ip[r + 1]; ++i) {
                 const int64_t col = shift[b] + id[i];
-                YITU_REQUIRE(col <= (1 << 24), YITU_ERR_LIMIT, "stitched column %lld exceeds 2^24", (long long)col);
+                // stricter than the reference's `col <= 2**24` (xgnn_h/block.py:52): column 2^24 would carry into the tag
+                YITU_REQUIRE(col < (1 << 24), YITU_ERR_LIMIT, "stitched column %lld exceeds 2^24 - 1", (long long)col);
                 out_indices_host[w++] = tag + static_cast<int32_t>(col);
             }
         }

@@ -93,6 +93,97 @@ extern "C" int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Owner-side push: the mirror image of the gather above.  The owner of a feature shard copies the rows that each
+// peer needs straight into that peer's halo buffer with ordinary stores through the NVLink peer mapping.  Stores
+// are posted (nothing waits for a round trip), the reads are local, and the owner paces its own egress - which
+// is what bounds the exchange when one shard holds far more rows than the others.
+// ---------------------------------------------------------------------------------------------------------
+namespace yitu {
+
+struct PushParams {
+    float *dst[16];        // halo buffer of destination d (peer mapping), first row of this owner's slot range
+    int64_t begin[17];     // items [begin[d], begin[d+1]) of the id list go to destination d
+    int n_dests;
+    const int *ids;        // local row ids, concatenated by destination, ascending within a destination
+    const float *x;        // this rank's feature shard
+    int64_t row_floats;
+    int64_t stripes, per_stripe;
+};
+
+template <int ROWS>
+__global__ void __launch_bounds__(256) halo_push_kernel(const __grid_constant__ PushParams p) {
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int64_t nvec = p.row_floats >> 2;
+    const int64_t n_items = p.begin[p.n_dests];
+    const int64_t total = p.stripes * p.per_stripe;
+    for (int64_t j0 = warp * ROWS; j0 < total; j0 += n_warps * ROWS) {
+        const float4 *src[ROWS];
+        float4 *dst[ROWS];
+        bool ok[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const int64_t j = j0 + r;
+            // striped visiting order: consecutive items of the grid come from all over the list, hence from every
+            // destination, so every link out of this GPU is busy from the first moment to the last
+            const int64_t i = (j % p.stripes) * p.per_stripe + j / p.stripes;
+            ok[r] = j < total && i < n_items;
+            src[r] = nullptr;
+            dst[r] = nullptr;
+            if (ok[r]) {
+                int d = 0;
+                while (d + 1 < p.n_dests && i >= p.begin[d + 1]) ++d;
+                src[r] = reinterpret_cast<const float4 *>(p.x + static_cast<int64_t>(__ldg(p.ids + i)) * p.row_floats);
+                dst[r] = reinterpret_cast<float4 *>(p.dst[d] + (i - p.begin[d]) * p.row_floats);
+            }
+        }
+        for (int64_t v = lane; v < nvec; v += 32) {
+            float4 val[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (ok[r]) val[r] = __ldg(src[r] + v);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (ok[r]) dst[r][v] = val[r];
+        }
+    }
+}
+
+}  // namespace yitu
+
+extern "C" int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, const int64_t *list_begin_host,
+                                  const int32_t *ids, const float *x, int64_t row_floats, yitu_stream_t stream) {
+    YITU_REQUIRE(n_dests >= 0 && n_dests <= 16, YITU_ERR_LIMIT, "n_dests=%d (0..16)", n_dests);
+    YITU_REQUIRE(row_floats > 0 && row_floats % 4 == 0, YITU_ERR_INVALID_ARG, "row_floats must be a multiple of 4");
+    if (n_dests == 0) return YITU_OK;
+    YITU_REQUIRE(dst_ptrs_host && list_begin_host, YITU_ERR_INVALID_ARG, "NULL destination table");
+    PushParams p{};
+    p.n_dests = n_dests;
+    YITU_REQUIRE(list_begin_host[0] == 0, YITU_ERR_INVALID_ARG, "list_begin[0] must be 0");
+    for (int d = 0; d < n_dests; ++d) {
+        YITU_REQUIRE(list_begin_host[d + 1] >= list_begin_host[d], YITU_ERR_INVALID_ARG, "list_begin must not decrease");
+        YITU_REQUIRE(list_begin_host[d + 1] == list_begin_host[d] || (dst_ptrs_host[d] && aligned16(dst_ptrs_host[d])),
+                     YITU_ERR_INVALID_ARG, "destination %d pointer NULL or misaligned", d);
+        p.dst[d] = dst_ptrs_host[d];
+        p.begin[d] = list_begin_host[d];
+    }
+    p.begin[n_dests] = list_begin_host[n_dests];
+    const int64_t n_items = p.begin[n_dests];
+    if (n_items == 0) return YITU_OK;
+    YITU_REQUIRE(ids && x && aligned16(x), YITU_ERR_INVALID_ARG, "NULL or misaligned ids/x");
+    p.ids = ids; p.x = x; p.row_floats = row_floats;
+    p.stripes = n_items >= (1 << 16) ? 1024 : 1;
+    p.per_stripe = (n_items + p.stripes - 1) / p.stripes;
+    constexpr int kRows = 4;
+    const int64_t blocks = (n_items + 8 * kRows - 1) / (8 * kRows);
+    const unsigned grid = static_cast<unsigned>(blocks < 148 * 2 ? blocks : 148 * 2);
+    halo_push_kernel<kRows><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Peer-readable feature shards (CUDA IPC).  Allocation happens once per shard at set-up, never per step.
 // ---------------------------------------------------------------------------------------------------------
 static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");

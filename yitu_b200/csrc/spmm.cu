@@ -22,6 +22,8 @@
 // The kernel is bound by HBM/L2 gather bandwidth; algorithmic bytes per edge = 4*D + 4 (+4 with edge
 // values), per row = 4*D written + one row pointer.
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace yitu {
@@ -317,6 +319,200 @@ __global__ void __launch_bounds__(256) spmm_wide_kernel(const __grid_constant__ 
     }
 }
 
+// Edge-stream variant for rows of 16*VEC < D <= 32*VEC floats with scalar weights: a warp owns R consecutive
+// destination rows (or one hub chunk) and walks their edges - which are contiguous in the CSR - as ONE stream.
+// Row pointers of the batch come from one coalesced load, column ids / weights from one coalesced load per 32
+// edges (the next tile is requested before the current one is consumed), and the feature gathers are issued EU
+// edges at a time without regard to row boundaries: when the stream crosses into the next row the accumulator is
+// written out (a store, nothing waits for it) and cleared.  A short row therefore costs one store and a
+// warp-uniform branch instead of its own chain of three dependent memory latencies (row pointer -> ids ->
+// features) and its own warp, and no gather slot is spent on padding a row up to EU edges.  Rows that the hub
+// schedule cuts into chunks are stepped over (their edges are neither loaded nor gathered).  Sums are formed in
+// edge order, so results are run-to-run identical.
+template <int VEC, int EU, int R, bool HUB, bool IDX32>
+__global__ void __launch_bounds__(128, (VEC * EU <= 32) ? 6 : 4) spmm_stream_kernel(const __grid_constant__ SpmmParams p) {
+    static_assert(R >= 1 && R <= 31 && EU >= 1 && EU <= 16 && 32 % EU == 0, "batch / unroll out of range");
+    constexpr unsigned FULL = 0xffffffffu;
+    constexpr unsigned GM = (1u << EU) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+
+    // rp: first edge of row `lane` of the batch, relative to the batch's first edge (positions inside a batch fit 32
+    // bits: the launcher sends graphs of 2^31 or more edges to the warp-per-row kernel)
+    int64_t r0, E0;
+    int nr, rp;
+    bool raw;
+    if (gid < p.n_chunks) {  // one chunk of a hub row: a one-row batch whose sum goes to scratch
+        raw = true;
+        nr = 1;
+        r0 = __ldg(p.chunk_row + gid);
+        E0 = __ldg(p.chunk_begin + gid);
+        const int64_t rend = load_ptr(p.indptr, p.is64, r0 + 1);
+        rp = lane == 0 ? 0 : static_cast<int>(min(static_cast<int64_t>(p.chunk_edges), rend - E0));
+    } else {
+        raw = false;
+        r0 = (gid - p.n_chunks) * R;
+        if (r0 >= p.n_rows) return;
+        nr = static_cast<int>(min(static_cast<int64_t>(R), p.n_rows - r0));
+        const int64_t myptr = load_ptr(p.indptr, p.is64, r0 + min(lane, nr));
+        E0 = __shfl_sync(FULL, myptr, 0);
+        rp = static_cast<int>(myptr - E0);
+    }
+    const int len = __shfl_sync(FULL, rp, nr);  // edges of the batch
+    const int rp_next = __shfl_down_sync(FULL, rp, 1);  // end of row `lane` (lanes < nr)
+    const bool myhub = HUB && !raw && lane < nr && (rp_next - rp) > p.chunk_edges;
+    const unsigned hub_rows = HUB ? __ballot_sync(FULL, myhub) : 0u;
+    const int *idx = p.indices + E0;
+
+    const int off = lane * VEC;
+    const bool valid = off < p.D;
+    float acc[VEC];
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
+
+    auto load_tile = [&](int t, int &col, float &w) {
+        col = 0;
+        w = 0.0f;
+        const int te = t + lane;
+        if (te < len) {
+            const int rawidx = ld_stream(idx + te);
+            col = p.mask ? (rawidx & p.mask) : rawidx;
+            if (p.wmode == YITU_W_NONE) {
+                w = 1.0f;
+            } else if (p.wmode == YITU_W_NODE) {
+                w = __ldg(p.norm_src + col);  // the destination's factor is applied once per row, at the end
+            } else {
+                const int64_t ee = E0 + te;
+                const int64_t vi = p.perm ? static_cast<int64_t>(ld_stream(p.perm + ee)) : ee;
+                w = ld_stream(p.values + vi);
+            }
+        }
+    };
+
+    int cur = 0;  // row of the batch that the stream is in
+    int cur_begin = 0, cur_end = __shfl_sync(FULL, rp, 1);
+    // writes out every row that ends at or before position t (several when empty rows follow); warp-uniform
+    auto flush = [&](int t) {
+        while (cur < nr && cur_end <= t) {
+            const int64_t row = r0 + cur;
+            if (raw) {
+                if (valid) store_vec<VEC>(p.scratch + gid * p.D + off, acc);
+            } else if (!((hub_rows >> cur) & 1u)) {
+                const bool had = cur_end > cur_begin;
+                if (valid && (had || !p.accumulate || p.bias || p.act)) {
+                    float s = p.alpha * (p.row_scale ? __ldg(p.row_scale + row) : 1.0f);
+                    if (p.wmode == YITU_W_NODE) s *= __ldg(p.norm_dst + row);
+                    float *dst = p.out + row * p.os + off;
+                    float r[VEC];
+                    if (p.accumulate) {
+                        load_vec<VEC>(r, dst);
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) r[q] = fmaf(s, acc[q], r[q]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) r[q] = s * acc[q];
+                    }
+                    finish_vec<VEC>(r, p, off);
+                    store_vec<VEC>(dst, r);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
+            ++cur;
+            cur_begin = cur_end;
+            cur_end = __shfl_sync(FULL, rp, min(cur + 1, 31));
+        }
+    };
+
+    auto gather = [&](float (&v)[VEC], int c) {
+        if (valid) {
+            if constexpr (IDX32)
+                load_vec<VEC>(v, p.x + (static_cast<uint32_t>(c) * static_cast<uint32_t>(p.xs) + static_cast<uint32_t>(off)));
+            else
+                load_vec<VEC>(v, p.x + static_cast<int64_t>(c) * p.xs + off);
+        } else {
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) v[q] = 0.0f;
+        }
+    };
+
+    int t0 = 0;
+    int my_col;
+    float my_w;
+    load_tile(t0, my_col, my_w);
+    while (t0 < len) {
+        const int n = min(32, len - t0);
+        const int t_next = t0 + 32;
+        int nx_col = 0;
+        float nx_w = 0.0f;
+        if (t_next < len) load_tile(t_next, nx_col, nx_w);
+        // bm: positions of this tile where a row of the batch begins; hm: positions inside hub rows
+        unsigned bm = 0u, hm = 0u;
+        if (lane >= 1 && lane < nr) {
+            const int d = rp - t0;
+            if (d >= 0 && d < n) bm = 1u << d;
+        }
+        bm = __reduce_or_sync(FULL, bm);
+        if constexpr (HUB) {
+            if (myhub) {
+                const int lo = max(rp - t0, 0), hi = min(rp_next - t0, n);
+                if (hi > lo) hm = (hi - lo >= 32 ? FULL : ((1u << (hi - lo)) - 1u)) << lo;
+            }
+            hm = __reduce_or_sync(FULL, hm);
+        }
+        const unsigned vm = (n == 32 ? FULL : ((1u << n) - 1u)) & ~hm;
+        if (HUB && vm == 0u) {
+            // every edge of the tile belongs to hub rows: continue behind the hub row that holds the tile's last edge
+            const int last = t0 + n - 1;
+            const unsigned who = __ballot_sync(FULL, myhub && rp <= last && rp_next > last);
+            t0 = __shfl_sync(FULL, rp_next, __ffs(who) - 1);
+            if (t0 == t_next) {
+                my_col = nx_col;
+                my_w = nx_w;
+            } else if (t0 < len) {
+                load_tile(t0, my_col, my_w);
+            }
+            continue;
+        }
+        for (int j = 0; j < n; j += EU) {
+            const unsigned gv = (vm >> j) & GM, gb = (bm >> j) & GM;
+            if (HUB && gv == 0u && gb == 0u) continue;  // a group wholly inside a hub row
+            int c[EU];
+            float w[EU];
+#pragma unroll
+            for (int u = 0; u < EU; ++u) {
+                c[u] = __shfl_sync(FULL, my_col, j + u);
+                w[u] = __shfl_sync(FULL, my_w, j + u);
+            }
+            float v[EU][VEC];
+            if (gv == GM && gb == 0u) {  // EU edges of one row: the common case
+#pragma unroll
+                for (int u = 0; u < EU; ++u) gather(v[u], c[u]);
+#pragma unroll
+                for (int u = 0; u < EU; ++u)
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) acc[q] = fmaf(w[u], v[u][q], acc[q]);
+            } else {  // a row ends inside the group, or some positions carry no edge: same loads, uniform predicates
+#pragma unroll
+                for (int u = 0; u < EU; ++u)
+                    if ((gv >> u) & 1u) gather(v[u], c[u]);
+#pragma unroll
+                for (int u = 0; u < EU; ++u) {
+                    if ((gb >> u) & 1u) flush(t0 + j + u);
+                    if ((gv >> u) & 1u) {
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) acc[q] = fmaf(w[u], v[u][q], acc[q]);
+                    }
+                }
+            }
+        }
+        t0 = t_next;
+        my_col = nx_col;
+        my_w = nx_w;
+    }
+    flush(INT32_MAX);
+}
+
 // Adds the chunk partials of each hub row in chunk order and applies the epilogue.
 __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__ SpmmParams p) {
     const int64_t chunk = blockIdx.x;
@@ -366,6 +562,53 @@ static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
         YITU_LAUNCH_CHECK();
     }
     return YITU_OK;
+}
+
+template <int VEC, int EU, int R>
+static int launch_stream(const SpmmParams &p, cudaStream_t st) {
+    const int64_t groups = p.n_chunks + (p.n_rows + R - 1) / R;
+    if (groups == 0) return YITU_OK;
+    const int threads = block_threads();
+    const int64_t gx = (groups + threads / 32 - 1) / (threads / 32);
+    YITU_REQUIRE(gx < (1ll << 31), YITU_ERR_LIMIT, "spmm grid too large (%lld)", (long long)gx);
+    const unsigned grid = static_cast<unsigned>(gx);
+    const bool idx32 = p.n_cols * p.xs < (1ll << 32);
+    const bool hub = p.n_chunks > 0;
+    if (hub) {
+        if (idx32) spmm_stream_kernel<VEC, EU, R, true, true><<<grid, threads, 0, st>>>(p);
+        else spmm_stream_kernel<VEC, EU, R, true, false><<<grid, threads, 0, st>>>(p);
+    } else {
+        if (idx32) spmm_stream_kernel<VEC, EU, R, false, true><<<grid, threads, 0, st>>>(p);
+        else spmm_stream_kernel<VEC, EU, R, false, false><<<grid, threads, 0, st>>>(p);
+    }
+    YITU_LAUNCH_CHECK();
+    if (hub) {
+        hub_reduce_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
+        YITU_LAUNCH_CHECK();
+    }
+    return YITU_OK;
+}
+
+// Development switches read from the environment at every call (measurement of one kernel form against another):
+// YITU_SPMM_STREAM=0 keeps the warp-per-row kernels for every shape; YITU_SPMM_STREAM_ROWS=8|16 and
+// YITU_SPMM_STREAM_EU pick an instantiation of the edge-stream kernel other than the default.
+static int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+template <int VEC, int EU_A, int EU_B>
+static int dispatch_stream(const SpmmParams &p, cudaStream_t st, int rows_dflt, int eu_dflt) {
+    const int rows = env_int("YITU_SPMM_STREAM_ROWS", rows_dflt);
+    const int eu = env_int("YITU_SPMM_STREAM_EU", eu_dflt);
+    if (eu == EU_B) {
+        if (rows == 8) return launch_stream<VEC, EU_B, 8>(p, st);
+        if (rows == 31) return launch_stream<VEC, EU_B, 31>(p, st);
+        return launch_stream<VEC, EU_B, 16>(p, st);
+    }
+    if (rows == 8) return launch_stream<VEC, EU_A, 8>(p, st);
+    if (rows == 31) return launch_stream<VEC, EU_A, 31>(p, st);
+    return launch_stream<VEC, EU_A, 16>(p, st);
 }
 
 template <int LPE, int EU>
@@ -445,6 +688,11 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     // aligned; measured 6.20 ms against 6.44 ms with 128-bit loads on the D=256 R-MAT workload.  Narrower rows would
     // need half-warp groups, which lose more than the wider loads gain.
     const auto aligned32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+    const bool stream_ok = !per_head && g.nnz < (1ll << 31) && env_int("YITU_SPMM_STREAM", 1) != 0;
+    if (stream_ok && D > 128 && D <= 256 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 &&
+        aligned32(a->x) && aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch)))
+        return dispatch_stream<8, 4, 8>(p, st, 16, 4);
+    if (stream_ok && D > 64 && D <= 128) return dispatch_stream<4, 8, 16>(p, st, 16, 8);
     if (D > 128 && D <= 512 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 && aligned32(a->x) &&
         aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch)) && (!per_head || a->n_feats % 8 == 0)) {
         if (D <= 256) return launch<32, 1, 8, 4>(p, per_head, st);

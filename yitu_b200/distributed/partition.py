@@ -39,63 +39,19 @@ class RowShard:
 class HaloPlan:
     """Which remote source rows a shard needs, and its column ids renumbered for the buffer
     [own rows | halo rows]: own source id s -> s - row_begin, remote id -> n_local + position in halo_ids.
+    halo_ids is sorted, hence grouped by owner: rows [owner_offsets[p], owner_offsets[p+1]) of the halo part
+    belong to rank p, in ascending id order — the layout both the reader-side gather and the owner-side push fill."""
 
-    With row_bounds (K+1 row offsets inside the shard) the halo list is ordered by the first row block that uses a
-    row, ascending ids within a block: halo_ids[chunk_offsets[b]:chunk_offsets[b+1]] are the rows block b needs in
-    addition to those of the blocks before it, so block b can be aggregated as soon as chunks 0..b have arrived."""
-
-    def __init__(self, shard, row_bounds=None):
+    def __init__(self, shard):
         lo, hi = shard.row_begin, shard.row_end
         cols = shard.indices
         own = (cols >= lo) & (cols < hi)
-        halo_sorted = torch.unique(cols[~own])  # sorted ascending, int32
-        self.n_halo = halo_sorted.numel()
-        pos = torch.searchsorted(halo_sorted, cols)
-        bounds_t = torch.tensor(shard.bounds, dtype=halo_sorted.dtype, device=cols.device)
-        # halo rows [owner_offsets[p], owner_offsets[p+1]) of the id-sorted list live on rank p
-        self.owner_offsets = torch.searchsorted(halo_sorted, bounds_t).tolist()
-        self.chunk_offsets = [0, self.n_halo]
-        self.row_bounds = None
-        if row_bounds is not None and len(row_bounds) > 2 and self.n_halo > 0:
-            k = len(row_bounds) - 1
-            edge_bounds = shard.indptr.long()[torch.tensor(row_bounds, device=cols.device)]
-            edge_ids = torch.arange(cols.numel(), device=cols.device)
-            block_of_edge = torch.searchsorted(edge_bounds, edge_ids, right=True) - 1
-            del edge_ids
-            first = torch.full((self.n_halo,), k, dtype=torch.int64, device=cols.device)
-            first.scatter_reduce_(0, pos[~own], block_of_edge[~own], reduce="amin")
-            del block_of_edge
-            first_sorted, perm = torch.sort(first, stable=True)  # new position j holds old position perm[j]
-            inv = torch.empty_like(perm)
-            inv[perm] = torch.arange(self.n_halo, device=cols.device)
-            self.halo_ids = halo_sorted[perm].contiguous()
-            pos = inv[pos.clamp(max=self.n_halo - 1)]
-            counts = torch.bincount(first_sorted, minlength=k + 1)[:k]
-            self.chunk_offsets = [0] + torch.cumsum(counts, 0).tolist()
-            self.row_bounds = list(row_bounds)
-        else:
-            self.halo_ids = halo_sorted
+        self.halo_ids = torch.unique(cols[~own])  # sorted ascending, int32
+        self.n_halo = self.halo_ids.numel()
+        pos = torch.searchsorted(self.halo_ids, cols)
+        bounds_t = torch.tensor(shard.bounds, dtype=self.halo_ids.dtype, device=cols.device)
+        self.owner_offsets = torch.searchsorted(self.halo_ids, bounds_t).tolist()
         self.local_indices = torch.where(own, cols - lo, pos.to(cols.dtype) + shard.n_local).to(torch.int32)
-        self.own_mask = own
-
-
-def split_local_halo(shard, plan):
-    """Split a shard's CSR by source into (own-source part, halo-source part) so the first can run while the
-    halo is still in flight.  Returns two (indptr, indices, values) triples; the halo part's column ids index
-    the halo buffer alone (0 .. n_halo)."""
-    own = plan.own_mask
-    csum = torch.zeros(own.numel() + 1, dtype=torch.int64, device=own.device)
-    torch.cumsum(own, 0, out=csum[1:])
-    ip = shard.indptr.long()
-    ip_own = csum[ip]
-    ip_halo = ip - ip_own
-    dt = shard.indptr.dtype
-    li = plan.local_indices
-    vals = shard.values
-    part_own = (ip_own.to(dt), li[own].contiguous(), None if vals is None else vals[own].contiguous())
-    part_halo = (ip_halo.to(dt), (li[~own] - shard.n_local).contiguous(),
-                 None if vals is None else vals[~own].contiguous())
-    return part_own, part_halo
 
 
 def allgather_columns(indices, bounds, max_rows):
@@ -104,3 +60,181 @@ def allgather_columns(indices, bounds, max_rows):
     b = torch.tensor(bounds, dtype=indices.dtype, device=indices.device)
     owner = torch.searchsorted(b, indices, right=True) - 1
     return (owner * max_rows + (indices - b[owner])).to(torch.int32)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Owner-side push with source-group passes: who sends what to whom, in which order the shards become usable,
+# and how a rank cuts its edges into aggregation passes that can start before the last byte has arrived.
+# ---------------------------------------------------------------------------------------------------------
+def owner_edge_counts(shard, world):
+    """Edges of the shard per owner of their source row: a list of `world` ints."""
+    b = torch.tensor(shard.bounds, dtype=shard.indices.dtype, device=shard.indices.device)
+    owner = torch.searchsorted(b, shard.indices, right=True) - 1
+    return torch.bincount(owner, minlength=world)[:world].tolist()
+
+
+class PushSchedule:
+    """Order in which the feature shards become usable, and each rank's aggregation passes.
+
+    Every owner pushes the rows its peers need from the first moment of a step, at the speed of its own NVLink
+    egress, so owner p is done after about egress_rows[p] * row_bytes / bandwidth.  Owners are sorted by that time
+    and cut into at most `max_phases` consecutive PHASES; the end of a phase ("every owner of the phase has
+    delivered everything") is one synchronisation point.  A rank aggregates in PASSES: pass 0 takes the edges whose
+    sources it owns itself (usable at once) together with the phases merged into it, each later pass takes the
+    next phases and accumulates into the output.  More passes start earlier but touch the output rows again.
+
+    One rank may be served FIRST (`priority`): every owner sends that rank's rows before anything else, and the
+    rank aggregates in a single pass as soon as they are in.  This is for the rank whose aggregation is the longest
+    (the shard with by far the most destination rows on a skewed graph): it cannot afford to wait for the slowest
+    owner, and a second pass over its many output rows costs more than it gains.
+
+    Phases, merges and the priority rank are chosen by a small exhaustive search over a linear cost model
+    (per edge, per destination row, per re-read output row); the model only has to rank the alternatives.
+
+    need_rows[q][p]   rows that rank q needs from owner p          (every rank holds the same matrix)
+    block_edges[q][p] edges of rank q whose source row owner p holds
+    rows[q]           destination rows of rank q
+    """
+
+    def __init__(self, need_rows, block_edges, rows, d, max_phases=3, egress_gbs=700.0, sync_ms=0.04,
+                 ns_per_edge=0.055, ns_per_row=0.25, ns_per_row_again=0.17, priority="auto"):
+        import itertools
+        P = len(rows)
+        self.world, self.d = P, int(d)
+        scale = d / 128.0
+        c_e, c_r, c_w = ns_per_edge * scale * 1e-6, ns_per_row * 1e-6, ns_per_row_again * scale * 1e-6
+        row_ms = 4.0 * d / (egress_gbs * 1e9) * 1e3  # one feature row over one link direction
+        need = [[0 if p == q else int(need_rows[q][p]) for p in range(P)] for q in range(P)]
+        self.egress_rows = [sum(need[q][p] for q in range(P)) for p in range(P)]
+        total_edges = [sum(int(e) for e in block_edges[q]) for q in range(P)]
+
+        def evaluate(phase_of, push_ms, prio, prio_ready):
+            n_ph = max(phase_of) + 1
+            ready = [0.0] * n_ph
+            for p in range(P):
+                ready[phase_of[p]] = max(ready[phase_of[p]], push_ms[p] + sync_ms)
+            per_rank, worst = [], 0.0
+            for q in range(P):
+                if q == prio:  # one pass, as soon as its rows are in
+                    t = prio_ready + c_e * total_edges[q] + c_r * rows[q]
+                    per_rank.append((t, None))
+                    worst = max(worst, t)
+                    continue
+                # items in order of availability: own sources, then the phases
+                edges = [0] * (n_ph + 1)
+                for p in range(P):
+                    edges[0 if p == q else 1 + phase_of[p]] += int(block_edges[q][p])
+                avail = [0.0] + ready
+                items = [i for i in range(n_ph + 1) if edges[i] > 0] or [0]
+                best_q = None
+                for cuts in range(1 << (len(items) - 1)):  # bit i set: a new pass starts before items[i+1]
+                    t, first, acc_e, last_avail, passes, cur = 0.0, True, 0, 0.0, [], []
+                    for i, it in enumerate(items):
+                        cur.append(it)
+                        acc_e += edges[it]
+                        last_avail = avail[it]
+                        if i == len(items) - 1 or (cuts >> i) & 1:
+                            t = max(t, last_avail) + c_e * acc_e + c_r * rows[q] + (0.0 if first else c_w * rows[q])
+                            passes.append(cur)
+                            first, acc_e, cur = False, 0, []
+                    if best_q is None or t < best_q[0] - 1e-9:
+                        best_q = (t, passes)
+                per_rank.append(best_q)
+                worst = max(worst, best_q[0])
+            return worst, per_rank
+
+        if priority == "auto":
+            heavy = max(range(P), key=lambda q: c_e * total_edges[q] + c_r * rows[q])
+            prio_options = [None, heavy] if P > 2 else [None]
+        else:
+            prio_options = [priority]
+        best = None
+        for prio in prio_options:
+            if prio is None:
+                first_ms, prio_ready = [0.0] * P, 0.0
+            else:
+                first_ms = [need[prio][p] * row_ms for p in range(P)]
+                prio_ready = max(max(first_ms), sum(need[prio]) * row_ms) + sync_ms  # slowest sender or its own ingress
+            push_ms = [first_ms[p] + (self.egress_rows[p] - (need[prio][p] if prio is not None else 0)) * row_ms
+                       for p in range(P)]
+            order = sorted(range(P), key=lambda p: (push_ms[p], p))
+            for k in range(1, min(max_phases, P) + 1):
+                for cut in itertools.combinations(range(1, P), k - 1):
+                    phase_of = [0] * P
+                    ph = 0
+                    for pos, p in enumerate(order):
+                        if ph < len(cut) and pos == cut[ph]:
+                            ph += 1
+                        phase_of[p] = ph
+                    worst, per_rank = evaluate(phase_of, push_ms, prio, prio_ready)
+                    if best is None or worst < best[0] - 1e-6:  # ties: no priority rank, fewer phases (searched first)
+                        best = (worst, phase_of, per_rank, prio, push_ms)
+        self.model_ms, self.phase_of_owner, per_rank, self.priority, self.push_ms = best
+        self.n_phases = max(self.phase_of_owner) + 1
+        # passes[q]: list of (owners whose edges the pass takes, phase it has to wait for: -1 nothing,
+        # PRIORITY the priority delivery, k >= 0 the end of phase k)
+        self.passes = []
+        for q in range(P):
+            if q == self.priority:
+                self.passes.append([(list(range(P)), self.PRIORITY)])
+                continue
+            out = []
+            for items in per_rank[q][1]:
+                owners = [p for p in range(P) if (0 if p == q else 1 + self.phase_of_owner[p]) in items]
+                out.append((owners, max(items) - 1))
+            self.passes.append(out)
+
+    PRIORITY = -2
+
+    def describe(self):
+        return {"phases": [[p for p in range(self.world) if self.phase_of_owner[p] == k] for k in range(self.n_phases)],
+                "priority_rank": self.priority,
+                "push_ms_model": [round(t, 3) for t in self.push_ms],
+                "passes_per_rank": [[{"owners": o, "after": {-1: "start", self.PRIORITY: "priority delivery"}.get(w, "phase %d" % w)}
+                                     for o, w in ps] for ps in self.passes],
+                "step_ms_model": round(self.model_ms, 3)}
+
+
+def source_passes(shard, plan, passes):
+    """Cut a shard's edges into the aggregation passes of a PushSchedule.  `passes` is this rank's list of
+    (owners, wait_phase).  Returns [(indptr, local_indices, values, wait_phase)] with every row present in every
+    pass (empty where the pass holds none of its edges); the column ids index the buffer [own rows | halo rows]."""
+    cols = shard.indices
+    b = torch.tensor(shard.bounds, dtype=cols.dtype, device=cols.device)
+    owner = torch.searchsorted(b, cols, right=True) - 1
+    pass_of_owner = torch.full((len(shard.bounds) - 1,), -1, dtype=torch.int64, device=cols.device)
+    for j, (owners, _) in enumerate(passes):
+        pass_of_owner[torch.tensor(owners, dtype=torch.int64, device=cols.device)] = j
+    pass_of_edge = pass_of_owner[owner]
+    del owner
+    ip = shard.indptr.long()
+    out = []
+    for j, (_, wait) in enumerate(passes):
+        if len(passes) == 1:
+            out.append((shard.indptr, plan.local_indices, shard.values, wait))
+            break
+        m = pass_of_edge == j
+        csum = torch.zeros(m.numel() + 1, dtype=torch.int64, device=m.device)
+        torch.cumsum(m, 0, out=csum[1:])
+        out.append((csum[ip].to(shard.indptr.dtype), plan.local_indices[m].contiguous(),
+                    None if shard.values is None else shard.values[m].contiguous(), wait))
+    return out
+
+
+def exchange_need_lists(plan, rank, world, group=None):
+    """Tell every owner which of its rows this rank needs.  Returns (need_rows, recv_ids, recv_counts):
+    need_rows[q][p] = rows rank q needs from owner p (the same matrix on every rank), recv_ids = the global ids
+    the peers need from THIS rank, concatenated by requesting rank, recv_counts[q] = how many of them rank q asked for."""
+    import torch.distributed as dist
+    off = plan.owner_offsets
+    send_counts = [off[p + 1] - off[p] for p in range(world)]
+    dev = plan.halo_ids.device
+    mine = torch.tensor(send_counts, dtype=torch.int64, device=dev)
+    rows = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(rows, mine, group=group)
+    need_rows = [r.tolist() for r in rows]
+    recv_counts = [need_rows[q][rank] for q in range(world)]
+    recv = torch.empty(sum(recv_counts), dtype=plan.halo_ids.dtype, device=dev)
+    dist.all_to_all_single(recv, plan.halo_ids.contiguous(), output_split_sizes=recv_counts,
+                           input_split_sizes=send_counts, group=group)
+    return need_rows, recv, recv_counts

@@ -1,12 +1,16 @@
-"""Execution of the row-partitioned SpMM on one rank (CUDA).
+"""Execution of the row-partitioned SpMM on one rank (CUDA).  Every rank keeps [own rows | halo rows] of the
+feature matrix in one buffer that its peers can map (CUDA IPC); three ways of filling the halo part:
 
-Per step:  [handshake: features of every rank are in place]  ->  fetch the halo rows this rank needs from its
-peers' shards (peer loads over NVLink through CUDA-IPC mappings, each needed row crosses the link once)  ->
-SpMM over [own rows | halo rows].  With overlap=True the shard's edges are split by source: the own-source part
-runs on the compute stream while the halo is fetched on a second stream; the halo-source part follows and
-accumulates.  mode="allgather" replaces the fetch by one NCCL all-gather of padded shards.
+  mode="push"       the OWNER of a row writes it into the halo buffers of the ranks that need it (peer stores
+                    over NVLink, each needed row crosses once), starting at the first moment of the step.  Shards
+                    become usable in phases (PushSchedule); a rank aggregates the edges of a phase as soon as that
+                    phase has landed and accumulates later phases into the same output, so most of the aggregation
+                    runs while the slowest owner is still sending.
+  mode="peer"       the READER fetches the rows with peer loads, then aggregates: two serial steps.
+  mode="allgather"  one NCCL all-gather of shards padded to the largest, then the aggregation.
 
-No collective carries feature data in the peer mode; no multicast load is used anywhere.
+No collective carries feature data in the push and peer modes (NCCL moves one float per synchronisation point);
+no multicast load is used anywhere.
 """
 import ctypes as C
 
@@ -15,7 +19,9 @@ import torch.distributed as dist
 
 from .. import ops
 from .._lib import check, lib
-from .partition import HaloPlan, allgather_columns, split_local_halo
+from ..ops import _ptr
+from .partition import (HaloPlan, PushSchedule, allgather_columns, exchange_need_lists, owner_edge_counts,
+                        source_passes)
 
 
 class SharedBuffer:
@@ -57,14 +63,19 @@ class SharedBuffer:
 
 
 class PartitionedSpmm:
-    def __init__(self, shard, d, device, group=None, mode="peer", overlap=True, weight_mode=ops.W_EDGE, row_blocks=1):
+    """One rank of the row-partitioned SpMM.  Write this rank's feature rows into `x_local`, call step(), read the
+    [n_local, d] result (a buffer reused between steps).  All ranks of `group` must construct, step and close
+    together.  x_local may be rewritten as soon as step() has been enqueued in the push and all-gather modes; in the
+    peer mode the peers read it during THEIR step, so rewrite it only after a step(fence=True) or a barrier."""
+
+    def __init__(self, shard, d, device, group=None, mode="push", weight_mode=ops.W_EDGE, max_phases=3,
+                 priority="auto"):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
         self.rank = shard.rank
         self.mode = mode if self.world > 1 else "local"  # "local": the shard is the whole graph, no exchange
-        self.row_blocks = int(row_blocks) if self.mode == "peer" else 1
-        self.overlap = overlap and self.mode == "peer" and self.row_blocks <= 1
         self.weight_mode = weight_mode
+        self.schedule = None
         n_local = shard.n_local
         self.out = torch.empty(n_local, d, dtype=torch.float32, device=self.device)
         self._token = torch.zeros(1, device=self.device)
@@ -79,19 +90,17 @@ class PartitionedSpmm:
             self.plan = None
             self.halo_bytes = (self.world - 1) * self.max_rows * d * 4
             return
-        row_bounds = None
-        if self.row_blocks > 1:
-            # edge-balanced row blocks inside the shard: block b is aggregated while the halo rows that only later
-            # blocks need are still in flight
-            probe = ops.PreparedGraph(shard.indptr, torch.empty(0, dtype=torch.int32, device=self.device), 0)
-            row_bounds = ops.partition_rows(probe, self.row_blocks).tolist()
-        self.plan = HaloPlan(shard, row_bounds)
+        if self.mode not in ("local", "peer", "push"):
+            raise RuntimeError("mode must be 'push', 'peer', 'allgather' or 'local', got %r" % (mode,))
+        self.plan = HaloPlan(shard)
         n_halo = self.plan.n_halo
         self.shared = SharedBuffer((n_local + n_halo) * d, self.device)
         self.xbuf = self.shared.tensor().view(n_local + n_halo, d)
         self.x_local, self.x_halo = self.xbuf[:n_local], self.xbuf[n_local:]
         self.halo_bytes = n_halo * d * 4
-        self.graph = ops.PreparedGraph(shard.indptr, self.plan.local_indices, n_local + n_halo)
+        self.graph = None
+        if self.mode != "push":
+            self.graph = ops.PreparedGraph(shard.indptr, self.plan.local_indices, n_local + n_halo)
         if self.world > 1:
             handles = [None] * self.world
             dist.all_gather_object(handles, self.shared.handle_bytes(), group=group)
@@ -99,33 +108,65 @@ class PartitionedSpmm:
                     for p in range(self.world)]
             self._ptrs = (C.c_void_p * self.world)(*ptrs)
             self._bounds = (C.c_int64 * (self.world + 1))(*shard.bounds)
-            self.side = torch.cuda.Stream(device=self.device, priority=-1)
-            if self.plan.row_bounds is not None:
-                self.blocks = []
-                rb = self.plan.row_bounds
-                ip_all = shard.indptr
-                for b in range(len(rb) - 1):
-                    e0, e1 = int(ip_all[rb[b]]), int(ip_all[rb[b + 1]])
-                    g_b = ops.PreparedGraph((ip_all[rb[b]:rb[b + 1] + 1] - e0).contiguous(),
-                                            self.plan.local_indices[e0:e1].contiguous(), n_local + n_halo)
-                    v_b = None if shard.values is None else shard.values[e0:e1].contiguous()
-                    self.blocks.append((g_b, v_b, self.out[rb[b]:rb[b + 1]], torch.cuda.Event()))
-            else:
-                self.row_blocks = 1
-            if self.overlap:
-                (ipo, ixo, vo), (iph, ixh, vh) = split_local_halo(shard, self.plan)
-                self.g_own = ops.PreparedGraph(ipo, ixo, n_local)
-                self.g_halo = ops.PreparedGraph(iph, ixh, n_halo)
-                self.v_own, self.v_halo = vo, vh
+            if self.mode == "push":
+                self._setup_push(ptrs, max_phases, priority)
+
+    # ------------------------------------------------------------------------------------------ push set-up
+    def _setup_push(self, ptrs, max_phases, priority):
+        sh, plan, world, rank, d = self.shard, self.plan, self.world, self.rank, self.d
+        need_rows, recv_ids, recv_counts = exchange_need_lists(plan, rank, world, self.group)
+        mine = torch.tensor(owner_edge_counts(sh, world), dtype=torch.int64, device=self.device)
+        blocks = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(blocks, mine, group=self.group)
+        rows = [sh.bounds[p + 1] - sh.bounds[p] for p in range(world)]
+        self.schedule = PushSchedule(need_rows, [b.tolist() for b in blocks], rows, d, max_phases=max_phases,
+                                     priority=priority)
+        offsets = [None] * world  # offsets[q][p]: first halo slot that rank q reserves for owner p's rows
+        dist.all_gather_object(offsets, list(plan.owner_offsets), group=self.group)
+        send_ids = (recv_ids - sh.row_begin).to(torch.int32)
+        starts = [sum(recv_counts[:q]) for q in range(world)]
+
+        def push_args(dests):
+            dests = [q for q in dests if q != rank and recv_counts[q] > 0]
+            if not dests:
+                return None
+            ids = torch.cat([send_ids[starts[q]:starts[q] + recv_counts[q]] for q in dests]).contiguous()
+            begin = [0]
+            for q in dests:
+                begin.append(begin[-1] + recv_counts[q])
+            # destination pointer = base of q's buffer + (its own rows + the slots before this owner's) rows
+            dst = [ptrs[q] + 4 * d * (rows[q] + offsets[q][rank]) for q in dests]
+            return (len(dests), (C.c_void_p * len(dests))(*dst), (C.c_int64 * (len(dests) + 1))(*begin), ids)
+
+        prio = self.schedule.priority
+        self._push_first = push_args([prio]) if prio is not None else None
+        self._push_rest = push_args([q for q in range(world) if q != prio])
+        self._passes = []
+        for ip, li, vals, wait in source_passes(sh, plan, self.schedule.passes[rank]):
+            self._passes.append((ops.PreparedGraph(ip, li, sh.n_local + plan.n_halo), vals, wait))
+        self.graph = self._passes[0][0]
+        self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self.sync_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        n_ph = self.schedule.n_phases
+        self._phase_tokens = [torch.zeros(1, device=self.device) for _ in range(n_ph + 1)]
+        self._ev_first, self._ev_rest, self._ev_prio = (torch.cuda.Event() for _ in range(3))
+        self._ev_phase = [torch.cuda.Event() for _ in range(n_ph)]
+
+    def _push(self, args):
+        n_dests, dst, begin, ids = args
+        st = torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            check(lib().yitu_halo_push_f32(n_dests, dst, begin, _ptr(ids), _ptr(self.x_local), self.d,
+                                           C.c_void_p(st.cuda_stream)))
 
     # ------------------------------------------------------------------------------------------
     def handshake(self):
-        """Stream-ordered all-reduce of one float: nobody reads a peer's shard before every rank's earlier work
-        (the writes of its features) has been enqueued and finished."""
+        """Stream-ordered all-reduce of one float: it completes on a rank only after every rank's earlier work on
+        its stream has finished (features written, previous aggregation done with the halo buffer)."""
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
-    def _mark(self, events, tag):
+    def _mark(self, events):
         if events is None:
             return None
         ev = torch.cuda.Event(enable_timing=True)
@@ -133,82 +174,91 @@ class PartitionedSpmm:
         return ev
 
     def fetch_halo(self, events=None):
+        """Peer mode: gather this rank's halo rows from the owners' shards (peer loads)."""
         if self.mode != "peer" or self.plan.n_halo == 0:
             return
-        a = self._mark(events, "fetch")
-        self._fetch_halo()
-        if events is not None:
-            events.append(("fetch", a, self._mark(events, "fetch")))
-
-    def _fetch_halo(self, first=0, last=None):
-        """Gather halo rows [first, last) of the plan's list into their slots of the halo buffer."""
-        last = self.plan.n_halo if last is None else last
-        if last <= first:
-            return
+        a = self._mark(events)
         st = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
-            check(lib().yitu_halo_gather_f32(self.world, self._ptrs, self._bounds,
-                                             C.c_void_p(self.plan.halo_ids.data_ptr() + 4 * first), last - first, self.d,
-                                             C.c_void_p(self.x_halo.data_ptr() + 4 * self.d * first),
-                                             C.c_void_p(st.cuda_stream)))
+            check(lib().yitu_halo_gather_f32(self.world, self._ptrs, self._bounds, _ptr(self.plan.halo_ids),
+                                             self.plan.n_halo, self.d, _ptr(self.x_halo), C.c_void_p(st.cuda_stream)))
+        if events is not None:
+            events.append(("fetch", a, self._mark(events)))
 
     def _spmm(self, g, x, vals, accumulate=False, events=None):
-        a = self._mark(events, "spmm")
+        a = self._mark(events)
         out = ops.spmm(g, x, mode=self.weight_mode if vals is not None else ops.W_NONE, edge_values=vals,
                        out=self.out, accumulate=accumulate)
         if events is not None:
-            events.append(("spmm", a, self._mark(events, "spmm")))
+            events.append(("spmm", a, self._mark(events)))
         return out
+
+    def _step_push(self, events):
+        sched = self.schedule
+        main = torch.cuda.current_stream(self.device)
+        ps, ss = self.push_stream, self.sync_stream
+        self.handshake()  # every shard is written, every halo buffer is free
+        ps.wait_stream(main)
+        ss.wait_stream(main)
+        with torch.cuda.stream(ps):
+            a = self._mark(events)
+            if self._push_first is not None:
+                self._push(self._push_first)
+            self._ev_first.record(ps)
+            if self._push_rest is not None:
+                self._push(self._push_rest)
+            self._ev_rest.record(ps)
+            if events is not None:
+                events.append(("push", a, self._mark(events)))
+        with torch.cuda.stream(ss):
+            # one synchronisation point per delivery: a rank joins once ITS sends of that delivery have left
+            if sched.priority is not None:
+                ss.wait_event(self._ev_first)
+                dist.all_reduce(self._phase_tokens[-1], group=self.group)
+                self._ev_prio.record(ss)
+            for k in range(sched.n_phases):
+                if k == sched.phase_of_owner[self.rank]:
+                    ss.wait_event(self._ev_rest)
+                dist.all_reduce(self._phase_tokens[k], group=self.group)
+                self._ev_phase[k].record(ss)
+        for j, (g, vals, wait) in enumerate(self._passes):
+            if wait == PushSchedule.PRIORITY:
+                main.wait_event(self._ev_prio)
+            elif wait >= 0:
+                main.wait_event(self._ev_phase[wait])
+            self._spmm(g, self.xbuf, vals, accumulate=j > 0, events=events)
+        main.wait_stream(ps)  # this rank's shard has been read: it may be rewritten once the step returns
+        return self.out
 
     def step(self, events=None, fence=False):
         """One aggregation over this rank's rows; returns the [n_local, d] output (reused between steps).
-        `events`, if a list, receives (tag, start, end) CUDA-event triples around every SpMM and halo fetch.
-        fence=True adds a second handshake once this rank's halo has arrived, so that no rank's later work (which may
-        overwrite its feature shard, as a training step does) starts before every peer has finished reading it."""
+        `events`, if a list, receives (tag, start, end) CUDA-event triples around every SpMM, halo fetch and push.
+        fence=True (peer mode) adds a second handshake once this rank's halo has arrived, so that no rank's later work
+        (which may overwrite its feature shard, as a training step does) starts before every peer has finished
+        reading it; the push mode needs no fence (a rank's shard is read by that rank alone)."""
         sh = self.shard
         if self.mode == "local":
             return self._spmm(self.graph, self.x_local, sh.values, events=events)
+        if self.mode == "push":
+            return self._step_push(events)
         self.handshake()
         if self.mode == "allgather":
             dist.all_gather_into_tensor(self.rep, self._slot, group=self.group)
             return self._spmm(self.graph, self.rep, sh.values, events=events)
+        self.fetch_halo(events)
         if fence:
-            self.fetch_halo(events)
             self.handshake()
-            return self._spmm(self.graph, self.xbuf, sh.values, events=events)
-        if self.row_blocks > 1:
-            main = torch.cuda.current_stream(self.device)
-            self.side.wait_stream(main)
-            off = self.plan.chunk_offsets
-            with torch.cuda.stream(self.side):
-                for b, (_, _, _, ready) in enumerate(self.blocks):
-                    a = self._mark(events, "fetch")
-                    self._fetch_halo(off[b], off[b + 1])
-                    if events is not None:
-                        events.append(("fetch", a, self._mark(events, "fetch")))
-                    ready.record(self.side)
-            for g_b, v_b, out_b, ready in self.blocks:
-                main.wait_event(ready)
-                a = self._mark(events, "spmm")
-                ops.spmm(g_b, self.xbuf, mode=self.weight_mode if v_b is not None else ops.W_NONE, edge_values=v_b,
-                         out=out_b)
-                if events is not None:
-                    events.append(("spmm", a, self._mark(events, "spmm")))
-            return self.out
-        if not self.overlap:
-            self.fetch_halo(events)
-            return self._spmm(self.graph, self.xbuf, sh.values, events=events)
-        main = torch.cuda.current_stream(self.device)
-        self.side.wait_stream(main)
-        with torch.cuda.stream(self.side):
-            self.fetch_halo(events)
-        self._spmm(self.g_own, self.x_local, self.v_own, events=events)
-        main.wait_stream(self.side)
-        return self._spmm(self.g_halo, self.x_halo, self.v_halo, accumulate=True, events=events)
+        return self._spmm(self.graph, self.xbuf, sh.values, events=events)
 
     def close(self):
+        """Collective: waits for this rank's work and for every peer (nobody may still be reading or writing a
+        mapped buffer) before the mappings are closed and the buffer is freed."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
         if getattr(self, "shared", None) is not None:
             self.shared.close()
+            self.shared = None
 
 
 class _PartitionedAggregateFunction(torch.autograd.Function):
@@ -235,7 +285,7 @@ class PartitionedAggregate:
     Built from the whole graph on every rank (indptr / indices / values are the global CSR, as in the reference's
     partitioning step, which also starts from the full graph)."""
 
-    def __init__(self, indptr, indices, values, d, device, group=None, bounds=None, mode="peer"):
+    def __init__(self, indptr, indices, values, d, device, group=None, bounds=None, mode="push"):
         from .partition import RowShard, partition_bounds
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -247,9 +297,9 @@ class PartitionedAggregate:
         t_values = None if values is None else values[t_perm.long()]
         wm = ops.W_EDGE if values is not None else ops.W_NONE
         self.fwd = PartitionedSpmm(RowShard(indptr, indices, values, self.bounds, rank), d, device, group, mode,
-                                   overlap=False, weight_mode=wm)
+                                   weight_mode=wm)
         self.bwd = PartitionedSpmm(RowShard(t_indptr, t_rows, t_values, self.bounds, rank), d, device, group, mode,
-                                   overlap=False, weight_mode=wm)
+                                   weight_mode=wm)
 
     def __call__(self, x_local):
         return _PartitionedAggregateFunction.apply(x_local, self)

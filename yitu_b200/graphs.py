@@ -165,6 +165,16 @@ def randn_features(seed, n, d, device="cpu", chunk_rows=1 << 20, row_begin=0):
     return out
 
 
+def randn_rows(seed, row_ids, d):
+    """Rows `row_ids` (an int64 tensor, any order, repeats allowed) of the matrix randn_features(seed, ., d) makes,
+    on the device of row_ids: lets a checker produce the features of arbitrary source nodes without the matrix."""
+    idx = (row_ids.to(torch.int64)[:, None] * d + torch.arange(d, dtype=torch.int64, device=row_ids.device)).reshape(-1)
+    bits = _draw(seed, idx, 977)
+    u1 = ((bits & 0xFFFFFF).to(torch.float32) + 1.0) * (1.0 / 16777216.0)
+    u2 = (((bits >> 24) & 0xFFFFFF).to(torch.float32)) * (1.0 / 16777216.0)
+    return (torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(6.283185307179586 * u2)).view(-1, d)
+
+
 def uniform_values(seed, shape, lo, hi, device="cpu"):
     n = 1
     for s in shape:

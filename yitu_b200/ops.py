@@ -4,6 +4,7 @@ per-graph cache of derived structures (hub-row schedule, transposed graph).
 torch is plumbing here (device memory, the current stream); every aggregation runs in libyitu_b200.so.
 """
 import ctypes as C
+import weakref
 
 import torch
 
@@ -44,6 +45,27 @@ def require_cuda(t, name, dtype=None):
         raise RuntimeError("%s must be contiguous" % name)
     if dtype is not None and t.dtype != dtype:
         raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return t
+
+
+def expect(t, name, shape=None, numel=None, dtype=torch.float32, device=None):
+    """Host-side argument check of the tensor-level wrappers (no device synchronisation): the kernels receive raw
+    pointers, so a tensor that is short, of another dtype, strided, or on another device must be stopped here,
+    as a RuntimeError, before it becomes an out-of-bounds read on the GPU.  None passes (optional arguments)."""
+    if t is None:
+        return None
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError("%s must be a tensor, got %s" % (name, type(t).__name__))
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if device is not None and t.device != device:
+        raise RuntimeError("%s is on %s, the graph is on %s" % (name, t.device, device))
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise RuntimeError("%s must have shape %s, got %s" % (name, tuple(shape), tuple(t.shape)))
+    if numel is not None and t.numel() != numel:
+        raise RuntimeError("%s must hold %d values, got %d" % (name, numel, t.numel()))
     return t
 
 
@@ -132,18 +154,28 @@ class PreparedGraph:
         return self._seg_mean
 
 
+_PREPARED = weakref.WeakValueDictionary()  # memory identity of (indptr, indices) + n_cols + mask -> PreparedGraph
+
+
 def prepared(indptr, indices, n_cols, index_mask=0):
-    """PreparedGraph cached on the row-pointer tensor object (dies with it; rebuilt if either tensor is
-    modified in place or paired with another index tensor)."""
-    stamp = (indices.data_ptr(), indices.numel(), indices._version, indptr._version)
-    cache = getattr(indptr, "_yitu_prepared", None)
-    if cache is None or cache[0] != stamp:
-        cache = (stamp, {})
-        indptr._yitu_prepared = cache
-    key = (int(n_cols), int(index_mask))
-    if key not in cache[1]:
-        cache[1][key] = PreparedGraph(indptr, indices, n_cols, index_mask)
-    return cache[1][key]
+    """PreparedGraph of a CSR, found by the MEMORY the two tensors occupy (address, length, in-place version counter,
+    device), not by the Python tensor objects: callers in the reference's style hand over a fresh tensor object per
+    call (a view, an attribute lookup that re-wraps the same storage) and must not pay for a new transpose and hub
+    schedule each time.  The table holds its entries weakly; every tensor object that was passed in keeps the entry
+    alive (it also pins the memory, so an address cannot be reused while its entry exists), and the derived structures
+    die with the last of them.  An in-place modification bumps the version counter and leads to a rebuild."""
+    key = (indptr.data_ptr(), indptr.numel(), indptr._version, indices.data_ptr(), indices.numel(), indices._version,
+           str(indptr.device), indptr.dtype, int(n_cols), int(index_mask))
+    g = _PREPARED.get(key)
+    if g is None:
+        g = PreparedGraph(indptr, indices, n_cols, index_mask)
+        _PREPARED[key] = g
+    held = getattr(indptr, "_yitu_prepared", None)
+    if held is None or held[0] != key[:8]:
+        held = (key[:8], {})
+        indptr._yitu_prepared = held
+    held[1][key[8:]] = g
+    return g
 
 
 def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, norm_dst=None, norm_src=None,
@@ -154,17 +186,31 @@ def spmm(graph, x, *, n_heads=1, mode=W_NONE, edge_values=None, edge_perm=None, 
     x: [n_cols, H*F] or [n_cols, H, F] float32 CUDA; returns a tensor shaped like x with n_rows rows.
     x_shared_heads (per-head edge values only): x is [n_cols, F] and every head reads the same row; the result is
     [n_rows, H, F]."""
-    if x.dtype != torch.float32:
-        raise RuntimeError("features must be float32, got %s" % x.dtype)
-    if x.size(0) != graph.n_cols:
-        raise RuntimeError("features have %d rows, the graph has %d source nodes" % (x.size(0), graph.n_cols))
+    if not isinstance(x, torch.Tensor) or x.dtype != torch.float32:
+        raise RuntimeError("features must be a float32 tensor, got %s" % getattr(x, "dtype", type(x).__name__))
+    if x.dim() < 2 or x.size(0) != graph.n_cols:
+        raise RuntimeError("features have shape %s, the graph has %d source nodes" % (tuple(x.shape), graph.n_cols))
+    dev = graph.device
+    if not x.is_contiguous():
+        x = x.contiguous()
+    expect(x, "features", device=dev)
+    per_edge = {W_EDGE: graph.nnz, W_EDGE_HEAD: graph.nnz * n_heads}.get(mode)
+    if per_edge is not None and edge_values is None:
+        raise RuntimeError("this weight mode needs edge_values")
+    expect(edge_values, "edge_values", numel=per_edge, device=dev)
+    expect(edge_perm, "edge_perm", numel=graph.nnz, dtype=torch.int32, device=dev)
+    if mode == W_NODE and (norm_dst is None or norm_src is None):
+        raise RuntimeError("W_NODE needs norm_dst and norm_src")
+    expect(norm_dst, "norm_dst", numel=graph.n_rows, device=dev)
+    expect(norm_src, "norm_src", numel=graph.n_cols, device=dev)
+    expect(row_scale, "row_scale", numel=graph.n_rows, device=dev)
     x2 = x.reshape(x.size(0), -1)
     x_width = x2.size(1)
     D = x_width * n_heads if x_shared_heads else x_width
     if D % n_heads:
         raise RuntimeError("feature width %d is not a multiple of n_heads=%d" % (D, n_heads))
-    if bias is not None and (bias.numel() != D or bias.dtype != torch.float32 or not bias.is_contiguous()):
-        raise RuntimeError("bias must be a contiguous float32 tensor of %d values" % D)
+    expect(bias, "bias", numel=D, device=dev)
+    expect(out, "out", numel=graph.n_rows * D, device=dev)
     if out is None:
         shape = (graph.n_rows, n_heads, x_width) if x_shared_heads else (graph.n_rows,) + tuple(x.shape[1:])
         out = torch.empty(shape, dtype=torch.float32, device=x.device)
@@ -217,9 +263,18 @@ def _hub_plan(graph, chunk_edges):
     return C.pointer(pl[0]), pl[0].n_chunks, pl
 
 
+def _heads_feats(graph, x, name):
+    """(H, F) of a [n_cols, H, F] float32 source-feature tensor on the graph's device."""
+    if not isinstance(x, torch.Tensor) or x.dim() != 3:
+        raise RuntimeError("%s must be a [n_src, heads, feats] tensor" % name)
+    expect(x, name, shape=(graph.n_cols, x.size(1), x.size(2)), device=graph.device)
+    return x.size(1), x.size(2)
+
+
 def edge_dot(graph, grad_out, x, chunk_edges=DEFAULT_CHUNK_EDGES):
     """grad_a[e,h] = <grad_out[row_e,h,:], x[col_e,h,:]>; grad_out [n_rows,H,F], x [n_cols,H,F]."""
-    H, F = x.size(1), x.size(2)
+    H, F = _heads_feats(graph, x, "x")
+    expect(grad_out, "grad_out", shape=(graph.n_rows, H, F), device=graph.device)
     grad_a = torch.empty((graph.nnz, H), dtype=torch.float32, device=x.device)
     plan, _, keep = _hub_plan(graph, chunk_edges)
     with torch.cuda.device(x.device):
@@ -237,8 +292,10 @@ def spmm_bwd_supported(n_heads, n_feats):
 def spmm_bwd(graph, values, x, grad_out, chunk_edges=DEFAULT_CHUNK_EDGES):
     """(grad_values [nnz,H], grad_x [n_cols,H,F]) of the multi-head SpMM with per-edge values, in one pass over the
     transposed graph (yitu_spmm_bwd_f32); shapes outside spmm_bwd_supported take edge_dot + the transposed spmm."""
-    H, F = x.size(1), x.size(2)
+    H, F = _heads_feats(graph, x, "x")
     dev = x.device
+    expect(values, "values", shape=(graph.nnz, H), device=dev)
+    expect(grad_out, "grad_out", shape=(graph.n_rows, H, F), device=dev)
     t_indptr, t_rows, t_perm = graph.transpose()
     a = SpmmBwdArgs()
     a.graph = graph.csr
@@ -258,9 +315,22 @@ def spmm_bwd(graph, values, x, grad_out, chunk_edges=DEFAULT_CHUNK_EDGES):
     return grad_values, grad_x
 
 
+def _query_key(graph, query, key, batched):
+    """Checks query [B, n_rows, H] (batched) or [n_rows, H] and key [n_cols, H]; returns (B, H)."""
+    if not isinstance(key, torch.Tensor) or key.dim() != 2:
+        raise RuntimeError("key must be a [n_src, heads] tensor")
+    H = key.size(1)
+    expect(key, "key", shape=(graph.n_cols, H), device=graph.device)
+    if not isinstance(query, torch.Tensor) or query.dim() != (3 if batched else 2):
+        raise RuntimeError("query must be a %s tensor" % ("[segments, n_dst, heads]" if batched else "[n_dst, heads]"))
+    B = query.size(0) if batched else 1
+    expect(query, "query", shape=(B, graph.n_rows, H) if batched else (graph.n_rows, H), device=graph.device)
+    return B, H
+
+
 def edge_softmax_fwd(graph, query, key, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDGES):
     """attn [nnz,H]; query [B,n_rows,H], key [n_cols,H]."""
-    B, H = query.size(0), key.size(1)
+    B, H = _query_key(graph, query, key, batched=True)
     attn = torch.zeros((graph.nnz, H), dtype=torch.float32, device=key.device)
     plan, _, keep = _hub_plan(graph, chunk_edges)
     with torch.cuda.device(key.device):
@@ -272,7 +342,9 @@ def edge_softmax_fwd(graph, query, key, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDG
 
 def edge_softmax_bwd(graph, query, key, attn, grad_attn, slope=0.2, chunk_edges=DEFAULT_CHUNK_EDGES):
     """(grad_query [B,n_rows,H], grad_key [n_cols,H])."""
-    B, H = query.size(0), key.size(1)
+    B, H = _query_key(graph, query, key, batched=True)
+    expect(attn, "attn", shape=(graph.nnz, H), device=graph.device)
+    expect(grad_attn, "grad_attn", shape=(graph.nnz, H), device=graph.device)
     grad_q = torch.empty_like(query)
     edge_grad = torch.zeros_like(attn)
     grad_k = torch.empty_like(key)
@@ -311,7 +383,9 @@ def gat_fwd(graph, query, key, x, slope=0.2, head_mean=False, activation=None, c
     head_mean: out is act(mean over heads), [n_rows,F], and a fourth tensor comes back: the per-head result
     [n_rows,H,F] that gat_bwd needs (None with keep_heads=False: inference, nothing is written but the mean).
     Rows longer than chunk_edges are split over several warps (0: never)."""
-    H, F = x.size(1), x.size(2)
+    H, F = _heads_feats(graph, x, "x")
+    if _query_key(graph, query, key, batched=False)[1] != H:
+        raise RuntimeError("query / key have %d heads, x has %d" % (key.size(1), H))
     dev = x.device
     shape = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
     out = torch.empty(shape, dtype=torch.float32, device=dev)
@@ -337,13 +411,20 @@ def gat_bwd(graph, query, key, x, out, row_max, row_sum, grad_out, slope=0.2, he
             chunk_edges=DEFAULT_CHUNK_EDGES):
     """(grad_query, grad_key, grad_x) of gat_fwd; grad_out is the gradient of the pre-activation output
     ([n_rows,F] with head_mean, which also needs out_heads, the fourth result of gat_fwd)."""
-    H, F = x.size(1), x.size(2)
+    H, F = _heads_feats(graph, x, "x")
+    if _query_key(graph, query, key, batched=False)[1] != H:
+        raise RuntimeError("query / key have %d heads, x has %d" % (key.size(1), H))
     dev = x.device
-    expect = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
-    if tuple(grad_out.shape) != expect or not grad_out.is_contiguous():
-        raise RuntimeError("grad_out must be contiguous with shape %s, got %s" % (expect, tuple(grad_out.shape)))
+    want = (graph.n_rows, F) if head_mean else (graph.n_rows, H, F)
+    if not isinstance(grad_out, torch.Tensor) or tuple(grad_out.shape) != want or not grad_out.is_contiguous():
+        raise RuntimeError("grad_out must be contiguous with shape %s, got %s" % (want, tuple(getattr(grad_out, "shape", ()))))
+    expect(grad_out, "grad_out", device=dev)
     if head_mean and out_heads is None:
         raise RuntimeError("the backward of a head-mean forward needs out_heads (the fourth result of gat_fwd)")
+    expect(out, "out", shape=want, device=dev)
+    expect(out_heads, "out_heads", shape=(graph.n_rows, H, F), device=dev)
+    expect(row_max, "row_max", shape=(graph.n_rows, H), device=dev)
+    expect(row_sum, "row_sum", shape=(graph.n_rows, H), device=dev)
     t_indptr, t_rows, t_perm = graph.transpose()
     b = GatBwdArgs()
     b.fwd = _gat_args(graph, query, key, x, out, row_max, row_sum, slope, head_mean, None, out_heads)

@@ -10,10 +10,21 @@ from .._lib import check, lib
 class Block:
     """size = [n_dst, n_src]; adj_sparse = [indptr int32, indices int32]; optional right_norm = 1/in_degree."""
 
-    def __init__(self, size: list, adj: list, right_norm=None):
+    def __init__(self, size: list, adj: list, right_norm=None, stitched=None):
         self.size = size
         self.adj_sparse = adj
         self.right_norm = right_norm
+        # True when the column ids carry a relation id in their top 8 bits (stitch_csr sets it); None = not known
+        # yet, found out once by is_stitched()
+        self.stitched = stitched
+
+    def is_stitched(self):
+        """Whether any column id carries a segment id (bits 24..31).  stitch_csr marks its result; for a Block built
+        from raw tensors the ids are inspected once (one device read) and the answer is kept."""
+        if self.stitched is None:
+            ix = self.adj_sparse[1]
+            self.stitched = bool(ix.numel()) and bool((ix >> 24).ne(0).any())
+        return self.stitched
 
     def to(self, device):
         self.adj_sparse = [self.adj_sparse[0].to(device), self.adj_sparse[1].to(device)]
@@ -46,10 +57,13 @@ def stitch_csr(block_list: List[Block]):
     if all(blk.adj_sparse[0].is_cuda and blk.adj_sparse[1].is_cuda for blk in block_list):
         # tables already on a GPU: stitch there (the result stays on that device)
         from .. import ops
-        ip, ix = ops.stitch_csr_device([blk.adj_sparse[0].to(torch.int32).contiguous() for blk in block_list],
-                                       [blk.adj_sparse[1].to(torch.int32).contiguous() for blk in block_list],
-                                       [blk.size[1] for blk in block_list])
-        return Block(size=[n_rows, sum(blk.size[1] for blk in block_list)], adj=[ip, ix])
+        try:
+            ip, ix = ops.stitch_csr_device([blk.adj_sparse[0].to(torch.int32).contiguous() for blk in block_list],
+                                           [blk.adj_sparse[1].to(torch.int32).contiguous() for blk in block_list],
+                                           [blk.size[1] for blk in block_list])
+        except RuntimeError as e:  # the reference asserts
+            raise AssertionError(str(e))
+        return Block(size=[n_rows, sum(blk.size[1] for blk in block_list)], adj=[ip, ix], stitched=len(block_list) > 1)
     ips = [blk.adj_sparse[0].to("cpu", torch.int32).contiguous() for blk in block_list]
     ids = [blk.adj_sparse[1].to("cpu", torch.int32).contiguous() for blk in block_list]
     n_cols = torch.tensor([blk.size[1] for blk in block_list], dtype=torch.int64)
@@ -62,4 +76,4 @@ def stitch_csr(block_list: List[Block]):
                                          C.c_void_p(out_ip.data_ptr()), C.c_void_p(out_id.data_ptr())))
     except RuntimeError as e:  # the reference asserts
         raise AssertionError(str(e))
-    return Block(size=[n_rows, int(n_cols.sum())], adj=[out_ip, out_id])
+    return Block(size=[n_rows, int(n_cols.sum())], adj=[out_ip, out_id], stitched=len(block_list) > 1)

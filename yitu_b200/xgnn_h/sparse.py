@@ -128,11 +128,13 @@ def fused_gat(block: block.Block, query: torch.Tensor, key: torch.Tensor, x: tor
     """Attention + aggregation of a GAT layer (YiTu_GNN/YiTu_H/test/common/model.py:96-105) for an unstitched
     block: query [n_dst,H], key [n_src,H], x [n_src,H,F] -> [n_dst,H,F]; with head_mean the layer's
     torch.mean(dim=1) (model.py:106) and the model's activation (model.py:126-129) are fused: -> [n_dst,F].
-    Shapes the fused kernels do not cover take the two-operator route."""
+    Shapes the fused kernels do not cover, and stitched blocks (relation ids in the top index bits, which the fused
+    kernels would take for column ids), take the two-operator route."""
     assert x.dim() == 3 and query.dim() == 2
     if activation not in _TORCH_ACT:
         raise RuntimeError("activation must be None, 'relu' or 'elu', got %r" % (activation,))
-    if graph_ext.gat_supported(block.adj_sparse[0], block.adj_sparse[1], x.size(1), x.size(2)):
+    if not block.is_stitched() and graph_ext.gat_supported(block.adj_sparse[0], block.adj_sparse[1], x.size(1),
+                                                            x.size(2)):
         return FusedGATFunction.apply(block.adj_sparse, query.contiguous(), key.contiguous(), x.contiguous(),
                                       head_mean, activation)
     out = gspmm(block, fused_gsddmm(block, query, key), x)
