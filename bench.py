@@ -67,6 +67,15 @@ def load_traffic(key, kernel):
     return rec["bytes"], rec.get("source")
 
 
+def spmm_kernel_name(nnz, n_rows, d):
+    """The SpMM instantiation that yitu_spmm_csr_f32 picks for scalar weights and aligned rows of d floats: the
+    edge-stream kernel below 16 edges per row on average, the warp-per-row kernel otherwise."""
+    stream = nnz < 16 * n_rows and 64 < d <= 256
+    if d > 128:
+        return "spmm_stream_kernel<8,4,16,true,true>" if stream else "spmm_kernel<32,1,8,4,false,true>"
+    return "spmm_stream_kernel<4,8,16,true,true>" if stream else "spmm_kernel<32,1,4,16,false,true>"
+
+
 def roofline(kernel, algorithmic_bytes, avg_launch_ms, traffic_key, compulsory_bytes=None):
     peak, peak_kind = load_peaks()
     achieved = algorithmic_bytes / (avg_launch_ms * 1e-3) / 1e9
@@ -161,6 +170,7 @@ class SpmmWorkload:
         self.kernel_bytes = self.nnz * (4 * d + 8) + (n + 1) * 4 + 4 * n * d
         self.compulsory_bytes = self.nnz * 8 + (n + 1) * 4 + 2 * 4 * n * d  # every source row and output row once
         self.traffic_key = "spmm_rmat_d256"
+        self.dominant_kernel = spmm_kernel_name(self.nnz, n, d)
 
     def step(self, kernel_events=None):
         t, ops = self.torch, self.ops

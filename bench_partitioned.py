@@ -301,7 +301,8 @@ def run(args):
         per_rank = [[float(v) for v in s.tolist()] for s in all_stats]
         egress = [sum(s[7 + o] for s in per_rank) for o in range(world)]
         move_max = max(s[1] for s in per_rank)
-        roof = bench.roofline("spmm_stream_kernel<4,8,16,true,true>" + (" (rank 0 shard, all passes)" if world > 1 else ""),
+        roof = bench.roofline(bench.spmm_kernel_name(int(per_rank[0][3]), int(per_rank[0][4]), d) +
+                              (" (rank 0 shard, all passes)" if world > 1 else ""),
                               k_bytes, k_ms, "spmm_partitioned_d128" if world == 1 and not args.scale else None)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

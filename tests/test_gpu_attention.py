@@ -469,3 +469,60 @@ def test_standalone_attention_ops_on_hub_rows(oracle, H, B, chunk):
         ga1, gx1 = ops.spmm_bwd(graph, _dev(ref), _dev(x), _dev(gout), chunk_edges=chunk)
         assert_close(ga1.cpu().numpy(), rga, rtol=2e-5, what="one-pass grad_values on hub rows")
         assert_close(gx1.cpu().numpy(), rgx, rtol=2e-5, what="one-pass grad_x on hub rows")
+
+
+def test_full_size_gat_backward_sampled_rows_against_float64():
+    """Benchmark-size fused GAT backward (2^20 nodes, 34.6 M edges, 8 heads x 32): gradients of sampled nodes against
+    float64 values formed edge by edge from the definition (the mathematics of YiTu_GNN/YiTu_H/src/sddmm_cuda.cu:36-67
+    and spmm_cuda.cu:24-42): grad_query of sampled destination rows; grad_x and grad_key of sampled source nodes, each
+    of which needs the softmax of every destination row it feeds."""
+    from conftest import record_error
+    from yitu_b200 import graphs, ops
+    n, H, F = 1 << 20, 8, 32
+    indptr, indices = graphs.gat_uniform(device="cuda", n=n, e=1 << 25)
+    g = ops.PreparedGraph(indptr, indices, n)
+    x = graphs.randn_features(1, n, H * F, device="cuda").view(n, H, F)
+    q = graphs.uniform_values(2, (n, H), -2, 2, device="cuda")
+    k = graphs.uniform_values(3, (n, H), -2, 2, device="cuda")
+    go = graphs.randn_features(4, n, H * F, device="cuda").view(n, H, F)
+    out, rmax, rsum = ops.gat_fwd(g, q, k, x)
+    gq, gk, gx = ops.gat_bwd(g, q, k, x, out, rmax, rsum, go)
+    t_indptr, t_rows, _ = g.transpose()
+
+    cache = {}
+
+    def row_terms(r):
+        """(cols, attention a [deg,H], d score / d(q+k) dz [deg,H]) of destination row r in float64."""
+        if r not in cache:
+            b, e = int(indptr[r]), int(indptr[r + 1])
+            cols = indices[b:e].long()
+            z = q[r].double()[None, :] + k[cols].double()
+            a = torch.softmax(torch.nn.functional.leaky_relu(z, 0.2), dim=0)
+            dp = (go[r].double()[None] * x[cols].double()).sum(-1)           # [deg,H]
+            ds = a * (dp - (a * dp).sum(0, keepdim=True))
+            cache[r] = (cols, a, ds * torch.where(z > 0, 1.0, 0.2))
+        return cache[r]
+
+    gen = torch.Generator().manual_seed(3)
+    dst_rows = torch.randint(0, n, (100,), generator=gen).tolist()
+    truth_q = torch.stack([row_terms(r)[2].sum(0) for r in dst_rows])
+    src_nodes = torch.randint(0, n, (48,), generator=gen).tolist()
+    truth_x, truth_k = [], []
+    for c in src_nodes:
+        tx = torch.zeros(H, F, dtype=torch.float64, device="cuda")
+        tk = torch.zeros(H, dtype=torch.float64, device="cuda")
+        for r in t_rows[int(t_indptr[c]):int(t_indptr[c + 1])].tolist():
+            cols, a, dz = row_terms(r)
+            pos = int((cols == c).nonzero()[0])
+            tx += a[pos][:, None] * go[r].double()
+            tk += dz[pos]
+        truth_x.append(tx)
+        truth_k.append(tk)
+    for name, got, truth in (("grad_query", gq[torch.tensor(dst_rows).cuda()], truth_q),
+                             ("grad_x", gx[torch.tensor(src_nodes).cuda()], torch.stack(truth_x)),
+                             ("grad_key", gk[torch.tensor(src_nodes).cuda()], torch.stack(truth_k))):
+        err = (got.double() - truth).abs()
+        scale = float(truth.abs().max())
+        assert float((err - 2e-5 * (truth.abs() + scale)).max()) <= 0, "%s off by %g (scale %g)" % (name, float(err.max()), scale)
+        big = truth.abs() >= 0.01 * scale
+        record_error("full-size-gat-backward", float(err.max()) / scale, float((err[big] / truth.abs()[big]).max()))

@@ -244,3 +244,52 @@ def test_fused_gat_forward_and_backward_replay_from_a_cuda_graph():
     torch.cuda.synchronize()
     for got, ref in zip(captured, step()):
         assert torch.equal(got, ref)
+
+
+def test_full_size_hetero_rgcn_sampled_rows_against_float64():
+    """The heterogeneous benchmark configuration at full size (4 node types of 1 000 000 / 500 000 / 250 000 / 100 000
+    nodes, 8 bipartite R-MAT relations x 4 M sampled edges, 64 features): per destination type ONE pass over the
+    stitched relations gives sum_r mean_{edges of relation r}(x_r W_r^T + b_r) - the layer mathematics of
+    YiTu_GNN/YiTu_H/test/common/model.py:15-30,142-171 with the sum instead of the division by the relation count.
+    Sampled destination rows, among them the longest of every type, against float64 formed from the UNSTITCHED
+    relation blocks."""
+    from conftest import record_error
+    from yitu_b200 import graphs
+    from yitu_b200.nn.layers import StitchedRGCNConv
+    from yitu_b200.xgnn_h import Block
+    dev = torch.device("cuda", 0)
+    sizes = graphs.HETERO_TYPES
+    rels = graphs.hetero_rgcn(device=dev)
+    by_dst = {}
+    for i, r in enumerate(rels):
+        by_dst.setdefault(r[1], []).append(i)
+    assert sorted(by_dst) == [0, 1, 2, 3] and all(len(v) == 2 for v in by_dst.values())
+    gen = torch.Generator().manual_seed(5)
+    for dt, ids in sorted(by_dst.items()):
+        torch.manual_seed(100 + dt)
+        relations = [("r%d" % i, Block([sizes[dt], sizes[rels[i][0]]], [rels[i][2], rels[i][3]])) for i in ids]
+        layer = StitchedRGCNConv(relations, 64, 64, reduce="sum").to(dev)
+        xs = {"r%d" % i: graphs.randn_features(20 + i, sizes[rels[i][0]], 64, device=dev) for i in ids}
+        with torch.no_grad():
+            out = layer(xs)
+        assert out.shape == (sizes[dt], 64)
+        deg_total = sum((rels[i][2][1:] - rels[i][2][:-1]) for i in ids)
+        rows = torch.cat([torch.topk(deg_total, 4).indices.cpu(), torch.randint(0, sizes[dt], (60,), generator=gen)]).tolist()
+        truth = torch.zeros(len(rows), 64, dtype=torch.float64, device=dev)
+        for i in ids:
+            fc = layer.fcs["r%d" % i]
+            w, b_ = fc.weight.double(), fc.bias.double()
+            ip, ix = rels[i][2], rels[i][3]
+            for j, r in enumerate(rows):
+                b0, e0 = int(ip[r]), int(ip[r + 1])
+                if e0 > b0:
+                    h = xs["r%d" % i][ix[b0:e0].long()].double() @ w.t() + b_
+                    truth[j] += h.mean(0)
+        err = (out[torch.tensor(rows, device=dev)].double() - truth).abs()
+        scale = float(truth.abs().max())
+        # 2e-5: a dense fp32 GEMM precedes the aggregation (same bar as the other layer tests)
+        assert float((err - 2e-5 * (truth.abs() + scale)).max()) <= 0, "type %d off by %g" % (dt, float(err.max()))
+        big = truth.abs() >= 0.01 * scale
+        record_error("full-size-hetero-rgcn", float(err.max()) / scale, float((err[big] / truth.abs()[big]).max()))
+        del layer, xs, out
+        torch.cuda.empty_cache()

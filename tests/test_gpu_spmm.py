@@ -17,8 +17,12 @@ def _dev(a, dtype=None):
 
 @pytest.mark.parametrize("D", [1, 3, 16, 20, 32, 48, 64, 100, 128, 200, 256, 512, 640])
 @pytest.mark.parametrize("mode", ["none", "node", "edge"])
-def test_spmm_modes_and_widths(oracle, D, mode):
+@pytest.mark.parametrize("kernel", ["auto", "rows", "stream"])
+def test_spmm_modes_and_widths(oracle, monkeypatch, D, mode, kernel):
     from yitu_b200 import ops
+    if kernel != "auto" and not 64 < D <= 256:
+        pytest.skip("one kernel form for this width")
+    monkeypatch.setenv("YITU_SPMM_STREAM", {"auto": "1", "rows": "0", "stream": "2"}[kernel])
     rng = np.random.default_rng(D * 7 + len(mode))
     n_rows, n_cols = 211, 173
     indptr, indices = random_csr(rng, n_rows, n_cols, density=0.05, hubs=3, hub_deg=150)
@@ -114,6 +118,7 @@ def test_stream_kernel_row_patterns(oracle, monkeypatch, pattern, D):
     ref_node = oracle.spmm(indptr, indices, x, wmode=oracle.W_NODE, norm_dst=nd, norm_src=ns)
     ref_acc = oracle.spmm(indptr, indices, x, alpha=0.5, out=base)
     ref_acc_epi = np.maximum(oracle.spmm(indptr, indices, x, out=base) + bias, 0)
+    monkeypatch.setenv("YITU_SPMM_STREAM", "2")  # this kernel whatever the average row length
     for rows, eu in ((16, None), (8, None), (31, None), (16, 16 if D <= 128 else 8)):
         monkeypatch.setenv("YITU_SPMM_STREAM_ROWS", str(rows))
         if eu is None:
