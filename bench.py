@@ -887,6 +887,8 @@ def main():
     ap.add_argument("--halo", default="push,peer",
                     help="partitioned, N>1: exchange modes to try for 3 steps each, the fastest is timed "
                          "(push | push1..push4 | pushnp | peer | allgather)")
+    ap.add_argument("--verbose-trials", action="store_true",
+                    help="partitioned: keep schedule and per-rank timeline of the exchange modes that lost the trial")
     ap.add_argument("--row-cost", type=int, default=0,
                     help="partitioned: balance edges + ROW_COST * rows instead of edges alone (not the prescribed split)")
     args = ap.parse_args()

@@ -116,6 +116,24 @@ def verify_rows(shard, out, d, n_random=96, chunk=1 << 16):
     return len(rows), float(err.max()) / max(scale, 1e-30), ok
 
 
+def step_timeline(runner, rank, world):
+    """Where the time of a push-mode step goes on every rank: one step with events; offsets in ms from the moment
+    the step's opening handshake completed on that rank."""
+    dev = runner.device
+    ev = []
+    runner.step(ev)
+    torch.cuda.synchronize(dev)
+    t0 = [a for tag, a, _ in ev if tag == "start"][0]
+    mine = {"rank": rank,
+            "push": [[round(t0.elapsed_time(a), 3), round(t0.elapsed_time(b), 3)] for tag, a, b in ev if tag == "push"],
+            "ready": {tag[6:]: round(a.elapsed_time(b), 3) for tag, a, b in ev if tag.startswith("ready:")},
+            "passes": [[round(t0.elapsed_time(a), 3), round(t0.elapsed_time(b), 3)] for tag, a, b in ev if tag == "spmm"],
+            "end": [round(a.elapsed_time(b), 3) for tag, a, b in ev if tag == "end"][0]}
+    out = [None] * world
+    dist.all_gather_object(out, mine)
+    return out
+
+
 def run(args):
     import bench  # the repo-root script: clock sampler, peak numbers, the secondary workloads
     from yitu_b200 import graphs
@@ -147,7 +165,7 @@ def run(args):
     x_shard = graphs.randn_features(FEATURE_SEED, shard.n_local, d, device=dev, row_begin=shard.row_begin)
 
     modes = ["local"] if world == 1 else [m for m in args.halo.split(",") if m]
-    runners, trial, verify = {}, {}, {}
+    runners, trial, verify, timelines, schedules = {}, {}, {}, {}, {}
     for mode in modes:
         kw = {}
         name = mode
@@ -172,6 +190,9 @@ def run(args):
         verify[name] = {"rows": int(stat[0]), "max_rel_err": float(stat[1]), "ok": float(stat[2]) == 0.0,
                         "bar": "|err| <= 1e-5*(|truth| + max|truth|), float64 truth, every rank checks its own rows"}
         trial[name] = _time_steps(r, 3, world)
+        if mode == "push":
+            timelines[name] = step_timeline(r, rank, world)
+            schedules[name] = r.schedule.describe()
     bad = [k for k, v in verify.items() if not v["ok"]]
     if bad:
         if rank == 0:
@@ -220,6 +241,8 @@ def run(args):
         dist.all_gather(all_stats, stats)
     else:
         all_stats = [stats]
+
+    timeline = timelines.get(best)
 
     # end to end: pinned host shard in, result shard back to pinned host memory, every step.  The copies of
     # neighbouring steps overlap the aggregation: step k+1's features arrive in a staging buffer on a copy-in stream
@@ -310,7 +333,9 @@ def run(args):
                 "config": {"workload": workload_name(n, e, d), "nnz": nnz,
                            "parallelism": "row_partition_%d" % world,
                            "balance": "edges" if not args.row_cost else "edges + %d * rows" % args.row_cost,
-                           "halo": best, "trial_ms": trial, "schedule": schedule,
+                           "halo": best, "trial_ms": trial, "schedule": schedule, "timeline_ms": timeline,
+                           "other_trials": {k: {"schedule": schedules[k], "timeline_ms": timelines[k]}
+                                            for k in timelines if k != best} if args.verbose_trials else None,
                            "l2": "inputs_larger_than_l2", "rows_per_rank": [int(s[4]) for s in per_rank],
                            "edges_per_rank": [int(s[3]) for s in per_rank],
                            "halo_bytes_per_rank": [int(s[2]) for s in per_rank],

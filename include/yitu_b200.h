@@ -346,7 +346,21 @@ int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host, 
  * HOST memory (n_dests <= 16, n_dests+1 offsets).  Takes the role of the per-destination sends of
  * YiTu_GNN/distributed/communication.py:230-264. */
 int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, const int64_t *list_begin_host,
-                       const int32_t *ids, const float *x, int64_t row_floats, yitu_stream_t stream);
+                       const int32_t *ids, const float *x, int64_t row_floats, uint64_t *work_counter,
+                       yitu_stream_t stream);
+/* work_counter: 8 bytes of device memory owned by the caller, used by one push at a time (the call zeroes it on
+ * `stream`; the kernel hands out its items from it). */
+
+/* Delivery flags between GPUs, for the owner-side push.  yitu_flags_signal stores `value` (use the step number:
+ * flags only ever grow) into n 64-bit flags, typically one in each reader's memory (peer mappings), in stream order
+ * - after a push on the same stream it tells those readers that the rows are in place.  yitu_flags_wait makes
+ * `stream` wait until flags[i] >= value for every i in `mask` (the first 32 flags of a local array), for at most
+ * timeout_ns (required, <= 10 s); on expiry it stores 1 + (index of a missing flag) into *error_flag (device int32,
+ * set once, never cleared by the library) and lets the stream continue.  No counterpart in the reference, whose
+ * ranks meet in collectives (YiTu_GNN/distributed/communication.py:230-264). */
+int yitu_flags_signal(int32_t n, uint64_t *const *targets_host, uint64_t value, yitu_stream_t stream);
+int yitu_flags_wait(const uint64_t *flags, uint32_t mask, uint64_t value, int64_t timeout_ns, int32_t *error_flag,
+                    yitu_stream_t stream);
 
 /* Feature shards that peers can read.  yitu_shared_alloc allocates `bytes` of device memory on the current
  * device (one cudaMalloc, so the pointer is an allocation base) and fills `handle_out` with its 64-byte CUDA IPC

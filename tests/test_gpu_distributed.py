@@ -58,6 +58,7 @@ def _worker(rank, world, port, errors):
                     assert torch.equal(r.x_halo, xs[r.plan.halo_ids.long()]), "halo rows must be the owners' rows"
             if mode == "push":
                 assert sum(g.nnz for g, _, _ in r._passes) == shard.nnz
+                r.check()  # no wait for a delivery ran out
             r.close()
         # differentiable form: forward over this rank's rows of A, backward over the same rows of A^T
         from yitu_b200.distributed import PartitionedAggregate
@@ -130,6 +131,7 @@ def test_push_exchange_and_passes_with_four_ranks_emulated_on_one_gpu():
         bufs[r][:s.n_local] = x[s.row_begin:s.row_end]
     need = [[plans[q].owner_offsets[p + 1] - plans[q].owner_offsets[p] for p in range(world)] for q in range(world)]
     st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)
     for p in range(world):  # owner p pushes to every reader q
         dests = [q for q in range(world) if q != p and need[q][p] > 0]
         ids = torch.cat([plans[q].halo_ids[plans[q].owner_offsets[p]:plans[q].owner_offsets[p + 1]] for q in dests])
@@ -140,7 +142,7 @@ def test_push_exchange_and_passes_with_four_ranks_emulated_on_one_gpu():
         dst_ptrs = [bufs[q].data_ptr() + 4 * d * (shards[q].n_local + plans[q].owner_offsets[p]) for q in dests]
         check(lib().yitu_halo_push_f32(len(dests), (C.c_void_p * len(dests))(*dst_ptrs),
                                        (C.c_int64 * (len(dests) + 1))(*begin), C.c_void_p(ids.data_ptr()),
-                                       C.c_void_p(bufs[p].data_ptr()), d, st))
+                                       C.c_void_p(bufs[p].data_ptr()), d, C.c_void_p(counter.data_ptr()), st))
     torch.cuda.synchronize(dev)
     for q in range(world):
         assert torch.equal(bufs[q][shards[q].n_local:], x[plans[q].halo_ids.long()]), "rank %d: halo slots" % q
@@ -157,6 +159,34 @@ def test_push_exchange_and_passes_with_four_ranks_emulated_on_one_gpu():
                 ops.spmm(g, bufs[q], mode=ops.W_EDGE, edge_values=vals, out=out, accumulate=j > 0)
             err = float((out - ref[s.row_begin:s.row_end]).abs().max())
             assert err <= 1e-5 * float(ref.abs().max()), "rank %d %s: max err %g" % (q, kw, err)
+
+
+def test_delivery_flags_signal_then_wait_and_bounded_timeout():
+    """The flag kernels on one GPU, one stream, in an order in which nothing waits for a later launch: a signal
+    followed by a wait for the value just stored returns at once; a wait for a value that nothing stores gives up
+    after its time limit, records which flag was missing, and leaves the stream and the context usable."""
+    import ctypes as C
+    import time
+    sys.path.insert(0, ROOT)
+    from yitu_b200._lib import check, lib
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(32, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    targets = (C.c_void_p * 3)(*[flags.data_ptr() + 8 * i for i in (0, 2, 5)])
+    check(lib().yitu_flags_signal(3, targets, 7, st))
+    check(lib().yitu_flags_wait(C.c_void_p(flags.data_ptr()), 0b100101, 7, 1_000_000_000, C.c_void_p(err.data_ptr()), st))
+    check(lib().yitu_flags_wait(C.c_void_p(flags.data_ptr()), 0b000101, 3, 1_000_000_000, C.c_void_p(err.data_ptr()), st))
+    torch.cuda.synchronize(dev)
+    assert flags.tolist()[:6] == [7, 0, 7, 0, 0, 7] and int(err) == 0
+    t0 = time.perf_counter()
+    check(lib().yitu_flags_wait(C.c_void_p(flags.data_ptr()), 0b1000, 7, 5_000_000, C.c_void_p(err.data_ptr()), st))  # 5 ms
+    torch.cuda.synchronize(dev)
+    assert time.perf_counter() - t0 < 1.0, "the wait must give up after its limit"
+    assert int(err) == 1 + 3, "flag 3 was the missing one"
+    assert float(torch.ones(4, device=dev).sum()) == 4.0  # the context is alive
+    with pytest.raises(RuntimeError):  # an unbounded wait is refused
+        check(lib().yitu_flags_wait(C.c_void_p(flags.data_ptr()), 1, 8, 0, C.c_void_p(err.data_ptr()), st))
 
 
 def test_partitioned_aggregate_single_gpu_autograd():

@@ -1,6 +1,7 @@
 // Halo fetch for the row-partitioned SpMM: copies the listed rows of a feature matrix that is sharded over
 // several GPUs into a dense local buffer, reading remote shards with ordinary loads through NVLink peer
 // mappings.  One warp per row, 128-bit accesses; bound by NVLink bandwidth for remote rows.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -108,17 +109,23 @@ struct PushParams {
     const float *x;        // this rank's feature shard
     int64_t row_floats;
     int64_t stripes, per_stripe;
+    unsigned long long *counter;  // next unclaimed item (zeroed before the launch)
 };
 
 template <int ROWS>
 __global__ void __launch_bounds__(256) halo_push_kernel(const __grid_constant__ PushParams p) {
-    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     const int64_t nvec = p.row_floats >> 2;
     const int64_t n_items = p.begin[p.n_dests];
     const int64_t total = p.stripes * p.per_stripe;
-    for (int64_t j0 = warp * ROWS; j0 < total; j0 += n_warps * ROWS) {
+    // Items are claimed ROWS at a time from a global counter, not dealt out in advance: on B200 the warps of a
+    // statically partitioned grid finished between 55 % and 100 % of the kernel's duration (SMs differ in their
+    // distance to the NVLink ports), and the slowest decided when the shard had left.
+    for (;;) {
+        unsigned long long claim = 0;
+        if (lane == 0) claim = atomicAdd(p.counter, static_cast<unsigned long long>(ROWS));
+        const int64_t j0 = static_cast<int64_t>(__shfl_sync(0xffffffffu, claim, 0));
+        if (j0 >= total) break;
         const float4 *src[ROWS];
         float4 *dst[ROWS];
         bool ok[ROWS];
@@ -153,7 +160,8 @@ __global__ void __launch_bounds__(256) halo_push_kernel(const __grid_constant__ 
 }  // namespace yitu
 
 extern "C" int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, const int64_t *list_begin_host,
-                                  const int32_t *ids, const float *x, int64_t row_floats, yitu_stream_t stream) {
+                                  const int32_t *ids, const float *x, int64_t row_floats, uint64_t *work_counter,
+                                  yitu_stream_t stream) {
     YITU_REQUIRE(n_dests >= 0 && n_dests <= 16, YITU_ERR_LIMIT, "n_dests=%d (0..16)", n_dests);
     YITU_REQUIRE(row_floats > 0 && row_floats % 4 == 0, YITU_ERR_INVALID_ARG, "row_floats must be a multiple of 4");
     if (n_dests == 0) return YITU_OK;
@@ -172,13 +180,98 @@ extern "C" int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, 
     const int64_t n_items = p.begin[n_dests];
     if (n_items == 0) return YITU_OK;
     YITU_REQUIRE(ids && x && aligned16(x), YITU_ERR_INVALID_ARG, "NULL or misaligned ids/x");
+    YITU_REQUIRE(work_counter != nullptr, YITU_ERR_INVALID_ARG, "work_counter is NULL (8 bytes of device memory)");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    YITU_CUDA(cudaMemsetAsync(work_counter, 0, sizeof(uint64_t), st));
     p.ids = ids; p.x = x; p.row_floats = row_floats;
+    p.counter = reinterpret_cast<unsigned long long *>(work_counter);
     p.stripes = n_items >= (1 << 16) ? 1024 : 1;
     p.per_stripe = (n_items + p.stripes - 1) / p.stripes;
     constexpr int kRows = 4;
     const int64_t blocks = (n_items + 8 * kRows - 1) / (8 * kRows);
-    const unsigned grid = static_cast<unsigned>(blocks < 148 * 2 ? blocks : 148 * 2);
-    halo_push_kernel<kRows><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    // development switch: CTAs of the push kernel (default two per SM of a 148-SM part)
+    const char *env = getenv("YITU_PUSH_CTAS");
+    const int64_t max_blocks = (env && *env) ? atoll(env) : 148 * 2;
+    const unsigned grid = static_cast<unsigned>(blocks < max_blocks ? blocks : (max_blocks > 0 ? max_blocks : 1));
+    halo_push_kernel<kRows><<<grid, 256, 0, st>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// "My rows are with you": a 64-bit flag per (reader, owner) pair in the reader's memory.  The owner raises it, in
+// stream order after its push kernel, by storing the step number through the peer mapping; the reader's stream
+// waits for it with a one-warp kernel before the aggregation pass that needs those rows.  A collective cannot do
+// this job while the push runs: its kernel needs a free SM, and the push kernel's resident CTAs occupy every SM until
+// they are done (measured: a one-float all-reduce issued at the start of the exchange completed after 5.7 ms; the
+// same all-reduce with half the SMs left free, after 0.19 ms).  The two kernels below need no shared memory and 32
+// threads, and run beside anything.
+// The wait is bounded: after `timeout_ns` the kernel records which flag was missing and returns, so a peer that
+// never signals costs a wrong result that the host can see, not a hung GPU.
+// ---------------------------------------------------------------------------------------------------------
+namespace yitu {
+
+struct SignalParams {
+    unsigned long long *target[16];
+    int n;
+    unsigned long long value;
+};
+
+__global__ void flags_signal_kernel(const __grid_constant__ SignalParams p) {
+    const int i = threadIdx.x;
+    if (i < p.n) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.target[i]), "l"(p.value) : "memory");
+    }
+}
+
+__global__ void flags_wait_kernel(const unsigned long long *flags, unsigned mask, unsigned long long value,
+                                  long long timeout_ns, int *error) {
+    const int i = threadIdx.x;
+    if (!((mask >> i) & 1u)) return;
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + i) : "memory");
+        if (v >= value) return;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (static_cast<long long>(now - start) > timeout_ns) {
+            atomicCAS(error, 0, 1 + i);  // first missing flag, 1-based
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
+}  // namespace yitu
+
+extern "C" int yitu_flags_signal(int32_t n, uint64_t *const *targets_host, uint64_t value, yitu_stream_t stream) {
+    YITU_REQUIRE(n >= 0 && n <= 16, YITU_ERR_LIMIT, "n=%d (0..16)", n);
+    if (n == 0) return YITU_OK;
+    YITU_REQUIRE(targets_host != nullptr, YITU_ERR_INVALID_ARG, "NULL target table");
+    SignalParams p{};
+    p.n = n;
+    p.value = value;
+    for (int i = 0; i < n; ++i) {
+        YITU_REQUIRE(targets_host[i] && (reinterpret_cast<uintptr_t>(targets_host[i]) & 7) == 0, YITU_ERR_INVALID_ARG,
+                     "target %d NULL or misaligned", i);
+        p.target[i] = reinterpret_cast<unsigned long long *>(targets_host[i]);
+    }
+    flags_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    YITU_LAUNCH_CHECK();
+    return YITU_OK;
+}
+
+extern "C" int yitu_flags_wait(const uint64_t *flags, uint32_t mask, uint64_t value, int64_t timeout_ns,
+                               int32_t *error_flag, yitu_stream_t stream) {
+    if (mask == 0) return YITU_OK;
+    YITU_REQUIRE(flags && error_flag, YITU_ERR_INVALID_ARG, "NULL flags / error_flag");
+    YITU_REQUIRE(timeout_ns > 0 && timeout_ns <= 10000000000ll, YITU_ERR_INVALID_ARG,
+                 "timeout_ns=%lld: the wait must be bounded (at most 10 s)", (long long)timeout_ns);
+    flags_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const unsigned long long *>(flags), mask, value, timeout_ns, error_flag);
     YITU_LAUNCH_CHECK();
     return YITU_OK;
 }

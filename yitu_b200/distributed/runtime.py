@@ -5,7 +5,9 @@ feature matrix in one buffer that its peers can map (CUDA IPC); three ways of fi
                     over NVLink, each needed row crosses once), starting at the first moment of the step.  Shards
                     become usable in phases (PushSchedule); a rank aggregates the edges of a phase as soon as that
                     phase has landed and accumulates later phases into the same output, so most of the aggregation
-                    runs while the slowest owner is still sending.
+                    runs while the slowest owner is still sending.  Deliveries are announced by 64-bit flags that
+                    the owner stores into the reader's memory after its push; the reader's stream waits for the
+                    flags of the owners a pass needs (bounded wait), so no collective runs inside a step.
   mode="peer"       the READER fetches the rows with peer loads, then aggregates: two serial steps.
   mode="allgather"  one NCCL all-gather of shards padded to the largest, then the aggregation.
 
@@ -27,19 +29,38 @@ from .partition import (HaloPlan, PushSchedule, allgather_columns, exchange_need
 class SharedBuffer:
     """Device memory that other processes on the same node can map (yitu_shared_alloc / yitu_shared_open)."""
 
+    FLAG_BYTES = 256  # 32 delivery flags of 64 bits behind the floats: [0..15] "all rows", [16..31] "priority rows"
+
+    @staticmethod
+    def flags_offset(n_floats):
+        """Byte offset of the flag block in a buffer of n_floats floats (256-byte aligned)."""
+        return (max(int(n_floats), 1) * 4 + 255) // 256 * 256
+
     def __init__(self, n_floats, device):
         self.device = torch.device(device)
         self.n_floats = int(n_floats)
         self.ptr = C.c_void_p()
         self.handle = (C.c_ubyte * 64)()
+        self.flags_off = self.flags_offset(self.n_floats)
         with torch.cuda.device(self.device):
-            check(lib().yitu_shared_alloc(max(self.n_floats, 1) * 4, C.byref(self.ptr), self.handle))
+            check(lib().yitu_shared_alloc(self.flags_off + self.FLAG_BYTES, C.byref(self.ptr), self.handle))
+            self.flags_tensor().zero_()
         self.__cuda_array_interface__ = {"shape": (self.n_floats,), "typestr": "<f4", "data": (self.ptr.value, False),
                                          "version": 2}
         self._opened = []
 
     def tensor(self):
         return torch.as_tensor(self, device=self.device)
+
+    def flags_tensor(self):
+        """The 32 delivery flags as an int64 tensor (a view of the same allocation)."""
+        class _View:
+            pass
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": (32,), "typestr": "<i8", "data": (self.ptr.value + self.flags_off, False),
+                                      "version": 2}
+        self._flags_view = v
+        return torch.as_tensor(v, device=self.device)
 
     def handle_bytes(self):
         return bytes(self.handle)
@@ -125,8 +146,12 @@ class PartitionedSpmm:
         dist.all_gather_object(offsets, list(plan.owner_offsets), group=self.group)
         send_ids = (recv_ids - sh.row_begin).to(torch.int32)
         starts = [sum(recv_counts[:q]) for q in range(world)]
+        # where rank q keeps its delivery flags: behind its [own | halo] rows
+        flags_at = [ptrs[q] + SharedBuffer.flags_offset((rows[q] + sum(need_rows[q])) * d) for q in range(world)]
 
-        def push_args(dests):
+        def push_args(dests, kind):
+            """(push arguments, signal arguments) for the destinations that need rows of this rank; kind 0 raises
+            the reader's "all rows of owner `rank` are here" flag, kind 1 its "priority rows" flag."""
             dests = [q for q in dests if q != rank and recv_counts[q] > 0]
             if not dests:
                 return None
@@ -136,28 +161,51 @@ class PartitionedSpmm:
                 begin.append(begin[-1] + recv_counts[q])
             # destination pointer = base of q's buffer + (its own rows + the slots before this owner's) rows
             dst = [ptrs[q] + 4 * d * (rows[q] + offsets[q][rank]) for q in dests]
-            return (len(dests), (C.c_void_p * len(dests))(*dst), (C.c_int64 * (len(dests) + 1))(*begin), ids)
+            flags = [flags_at[q] + 8 * (16 * kind + rank) for q in dests]
+            return ((len(dests), (C.c_void_p * len(dests))(*dst), (C.c_int64 * (len(dests) + 1))(*begin), ids),
+                    (len(dests), (C.c_void_p * len(dests))(*flags)))
 
         prio = self.schedule.priority
-        self._push_first = push_args([prio]) if prio is not None else None
-        self._push_rest = push_args([q for q in range(world) if q != prio])
+        self._push_first = push_args([prio], 1) if prio is not None else None
+        self._push_rest = push_args([q for q in range(world) if q != prio], 0)
         self._passes = []
-        for ip, li, vals, wait in source_passes(sh, plan, self.schedule.passes[rank]):
-            self._passes.append((ops.PreparedGraph(ip, li, sh.n_local + plan.n_halo), vals, wait))
+        for (ip, li, vals, wait), (owners, _) in zip(source_passes(sh, plan, self.schedule.passes[rank]),
+                                                     self.schedule.passes[rank]):
+            mask = 0
+            for p in owners:
+                if p != rank and need_rows[rank][p] > 0:
+                    mask |= 1 << p
+            self._passes.append((ops.PreparedGraph(ip, li, sh.n_local + plan.n_halo), vals, mask))
         self.graph = self._passes[0][0]
         self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
-        self.sync_stream = torch.cuda.Stream(device=self.device, priority=-1)
-        n_ph = self.schedule.n_phases
-        self._phase_tokens = [torch.zeros(1, device=self.device) for _ in range(n_ph + 1)]
-        self._ev_first, self._ev_rest, self._ev_prio = (torch.cuda.Event() for _ in range(3))
-        self._ev_phase = [torch.cuda.Event() for _ in range(n_ph)]
+        self._flags = self.shared.flags_tensor()
+        self._flag_base = 16 if rank == prio else 0  # the priority reader waits for the priority deliveries
+        self._work_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self._wait_error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._step = 0
+        self.wait_timeout_ns = 2_000_000_000
 
     def _push(self, args):
-        n_dests, dst, begin, ids = args
-        st = torch.cuda.current_stream(self.device)
+        (n_dests, dst, begin, ids), (n_flags, flags) = args
+        st = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         with torch.cuda.device(self.device):
             check(lib().yitu_halo_push_f32(n_dests, dst, begin, _ptr(ids), _ptr(self.x_local), self.d,
-                                           C.c_void_p(st.cuda_stream)))
+                                           _ptr(self._work_counter), st))
+            check(lib().yitu_flags_signal(n_flags, flags, self._step, st))
+
+    def _wait_for(self, mask):
+        if mask:
+            st = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            with torch.cuda.device(self.device):
+                check(lib().yitu_flags_wait(C.c_void_p(self._flags.data_ptr() + 8 * self._flag_base), mask, self._step,
+                                            self.wait_timeout_ns, _ptr(self._wait_error), st))
+
+    def check(self):
+        """Synchronises and raises if a wait for a peer's delivery ever ran out (the results of that step are wrong)."""
+        torch.cuda.synchronize(self.device)
+        if self.mode == "push" and int(self._wait_error) != 0:
+            raise RuntimeError("rank %d: the rows of rank %d did not arrive within %.1f s" % (
+                self.rank, int(self._wait_error) - 1, self.wait_timeout_ns * 1e-9))
 
     # ------------------------------------------------------------------------------------------
     def handshake(self):
@@ -194,40 +242,32 @@ class PartitionedSpmm:
         return out
 
     def _step_push(self, events):
-        sched = self.schedule
         main = torch.cuda.current_stream(self.device)
-        ps, ss = self.push_stream, self.sync_stream
+        ps = self.push_stream
+        self._step += 1
         self.handshake()  # every shard is written, every halo buffer is free
+        t0 = self._mark(events)
+        if events is not None:
+            events.append(("start", t0, t0))
         ps.wait_stream(main)
-        ss.wait_stream(main)
         with torch.cuda.stream(ps):
+            # this rank's rows leave from the first moment of the step; each push is followed by the flags that tell
+            # its destinations "the rows of this owner are in place"
             a = self._mark(events)
             if self._push_first is not None:
                 self._push(self._push_first)
-            self._ev_first.record(ps)
             if self._push_rest is not None:
                 self._push(self._push_rest)
-            self._ev_rest.record(ps)
             if events is not None:
                 events.append(("push", a, self._mark(events)))
-        with torch.cuda.stream(ss):
-            # one synchronisation point per delivery: a rank joins once ITS sends of that delivery have left
-            if sched.priority is not None:
-                ss.wait_event(self._ev_first)
-                dist.all_reduce(self._phase_tokens[-1], group=self.group)
-                self._ev_prio.record(ss)
-            for k in range(sched.n_phases):
-                if k == sched.phase_of_owner[self.rank]:
-                    ss.wait_event(self._ev_rest)
-                dist.all_reduce(self._phase_tokens[k], group=self.group)
-                self._ev_phase[k].record(ss)
-        for j, (g, vals, wait) in enumerate(self._passes):
-            if wait == PushSchedule.PRIORITY:
-                main.wait_event(self._ev_prio)
-            elif wait >= 0:
-                main.wait_event(self._ev_phase[wait])
+        for j, (g, vals, mask) in enumerate(self._passes):
+            self._wait_for(mask)  # the owners whose rows this pass gathers
+            if events is not None:
+                events.append(("ready:pass%d" % j, t0, self._mark(events)))
             self._spmm(g, self.xbuf, vals, accumulate=j > 0, events=events)
         main.wait_stream(ps)  # this rank's shard has been read: it may be rewritten once the step returns
+        if events is not None:
+            events.append(("end", t0, self._mark(events)))
         return self.out
 
     def step(self, events=None, fence=False):
@@ -256,6 +296,7 @@ class PartitionedSpmm:
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(group=self.group)
+        self._flags = None
         if getattr(self, "shared", None) is not None:
             self.shared.close()
             self.shared = None
