@@ -69,8 +69,8 @@ def load_traffic(key, kernel):
 
 def spmm_kernel_name(nnz, n_rows, d):
     """The SpMM instantiation that yitu_spmm_csr_f32 picks for scalar weights and aligned rows of d floats: the
-    edge-stream kernel below 16 edges per row on average, the warp-per-row kernel otherwise."""
-    stream = nnz < 16 * n_rows and 64 < d <= 256
+    edge-stream kernel below 24 edges per row on average, the warp-per-row kernel otherwise."""
+    stream = nnz < 24 * n_rows and 64 < d <= 256
     if d > 128:
         return "spmm_stream_kernel<8,4,16,true,true>" if stream else "spmm_kernel<32,1,8,4,false,true>"
     return "spmm_stream_kernel<4,8,16,true,true>" if stream else "spmm_kernel<32,1,4,16,false,true>"

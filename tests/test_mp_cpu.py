@@ -1,5 +1,6 @@
 """Host logic of the executing message-passing DSL without a GPU: expression recording, pattern detection (what would
-be sent to the fused kernels) and the generic edge-by-edge evaluation, which is plain torch and runs on the CPU."""
+be sent to the fused kernels), the errors for expressions no kernel evaluates, and the deferral of reductions on the
+graphs of a HeteroGraph (what would be stitched)."""
 import numpy as np
 import pytest
 import torch
@@ -36,52 +37,74 @@ def test_expressions_are_recorded_and_patterns_detected():
     assert g.edge['attn2'].is_gat_attention() is None
     g.message_func(mp.Fn.edge_softmax('e', 'attn3'))     # no activation at all
     assert g.edge['attn3'].is_gat_attention() is None
-    assert torch.is_tensor(torch.exp(g.edge['e']))        # any other torch function forces the value
     with pytest.raises(RuntimeError):
         g.message_func({'func': 'v_sub_u', 'u': 'k', 'v': 'q', 'out': 'z'})
     assert mp.Fn.u_mul_e('u', 'attn', 'm') == {'func': 'u_mul_e', 'u': 'u', 'e': 'attn', 'out': 'm'}
 
 
-@pytest.mark.parametrize("slope", [0.05, None])
-def test_generic_evaluation_matches_dense_attention(slope):
-    """Slopes other than the kernels' 0.2 are evaluated edge by edge with torch: same mathematics as dense softmax."""
+def test_expressions_without_a_kernel_raise_and_name_themselves():
+    """No fallback: an expression that no kernel evaluates is a RuntimeError naming the expression."""
     from yitu_b200.xgnn_h import mp
     rng = np.random.default_rng(1)
-    n_dst, n_src, H, F = 25, 35, 3, 5
-    indptr, indices = random_csr(rng, n_dst, n_src, density=0.25, empty_rows=False)
-    g = _graph(indptr, indices, n_src)
-    q = torch.randn(n_dst, H, dtype=torch.float64, requires_grad=True)
-    k = torch.randn(n_src, H, dtype=torch.float64)
-    x = torch.randn(n_src, H, F, dtype=torch.float64)
-    g.src_node['q'], g.dst_node['k'], g.src_node['u'] = q, k, x
+    indptr, indices = random_csr(rng, 25, 35, density=0.25)
+    g = _graph(indptr, indices, 35)
+    g.src_node['q'], g.dst_node['k'], g.src_node['u'] = torch.randn(25, 3), torch.randn(35, 3), torch.randn(35, 3, 5)
     g.message_func(mp.Fn.u_add_v('k', 'q', 'e'))
-    g.edge['c'] = nn.LeakyReLU(slope)(g.edge['e']) if slope is not None else g.edge['e']
+    g.edge['c'] = nn.LeakyReLU(0.05)(g.edge['e'])           # not the slope the kernels fix
     g.message_func(mp.Fn.edge_softmax('c', 'attn'))
-    # the attention, multiplied edge by edge and summed per destination, without any CUDA operator
-    attn = g.edge['attn'].materialize()
-    rows, cols = g._edge_endpoints()
-    out = torch.zeros(n_dst, H, F, dtype=torch.float64).index_add_(0, rows, x[cols] * attn.unsqueeze(-1))
-    a = torch.zeros(n_dst, n_src, dtype=torch.float64)
-    a[np.repeat(np.arange(n_dst), np.diff(indptr)), indices] = 1.0
-    s = q[:, None, :] + k[None, :, :]
-    if slope is not None:
-        s = torch.nn.functional.leaky_relu(s, slope)
-    w = torch.softmax(s.masked_fill(a[:, :, None] == 0, float('-inf')), dim=1)
-    ref = torch.einsum('dsh,shf->dhf', w, x)
-    assert torch.allclose(out, ref, atol=1e-12)
-    out.sum().backward()          # the generic path is differentiable through torch
-    assert q.grad is not None and torch.isfinite(q.grad).all()
+    with pytest.raises(RuntimeError, match=r"edge_softmax\(e=leaky_relu\(e=u_add_v"):
+        g.edge['attn'].materialize()
+    with pytest.raises(RuntimeError, match="no kernel evaluates"):
+        torch.exp(g.edge['e'])                                # a bare per-edge sum has no kernel either
+    g.message_func(mp.Fn.u_mul_e('u', 'attn', 'm'))
+    with pytest.raises(RuntimeError, match="no kernel evaluates"):
+        g.reduce_func(mp.Fn.aggregate_sum('m', 'v'))
+    with pytest.raises(RuntimeError, match=r"aggregate_sum\(u_add_v"):
+        g.reduce_func(mp.Fn.aggregate_sum('e', 'v'))
 
 
-def test_generic_sum_of_two_dimensional_messages():
-    from yitu_b200.xgnn_h import mp
-    rng = np.random.default_rng(2)
-    indptr, indices = random_csr(rng, 20, 30, density=0.2)
-    g = _graph(indptr, indices, 30)
-    x = torch.randn(30, 7)
-    g.src_node['x'] = x
-    g.message_func(mp.Fn.copy_u('x', 'm'))
-    g.reduce_func(mp.Fn.aggregate_sum('m', 'y'))
-    a = torch.zeros(20, 30)
-    a[np.repeat(np.arange(20), np.diff(indptr)), indices] = 1.0
-    assert torch.allclose(g.dst_node['y'], a @ x, atol=1e-5)
+class _DslGCN(nn.Module):
+    """The DSL calls of the reference's GCNLayer (YiTu_GNN/YiTu_H/test/common/model.py:15-30)."""
+
+    def __init__(self, fin, fout):
+        super().__init__()
+        self.fc = nn.Linear(fin, fout)
+
+    def forward(self, graph, norm, x):
+        from yitu_b200.xgnn_h import mp
+        h = self.fc(x[0] if isinstance(x, (list, tuple)) else x)
+        graph.src_node['u'] = h.view(size=[-1, 1, h.size(-1)])
+        graph.message_func(mp.Fn.copy_u('u', 'm'))
+        graph.reduce_func(mp.Fn.aggregate_sum('m', 'v'))
+        return torch.multiply(norm, torch.squeeze(graph.dst_node['v'], dim=1))
+
+
+def test_reductions_of_a_hetero_graph_are_deferred_and_joined_per_destination_type():
+    """Recording only (no kernel runs on the CPU): on graphs of a HeteroGraph reduce_func returns a deferred result;
+    squeeze, the norm multiplication, the sum over the relations of a destination type and the division by their
+    number are absorbed, so that one stitched pass can compute them."""
+    from yitu_b200.nn import HeteroGraphConv
+    from yitu_b200.xgnn_h import Block, mp
+    rng = np.random.default_rng(3)
+    sizes = {"a": 30, "b": 20}
+    rels = {("a", "aa", "a"): random_csr(rng, 30, 30, 0.2), ("b", "ba", "a"): random_csr(rng, 30, 20, 0.2),
+            ("a", "ab", "b"): random_csr(rng, 20, 30, 0.2)}
+    h = mp.HeteroGraph.from_blocks({k: Block([sizes[k[2]], sizes[k[0]]], [torch.from_numpy(ip), torch.from_numpy(ix)])
+                                    for k, (ip, ix) in rels.items()})
+    assert all(g.hetero is h and g.relation == k for k, g in h)
+    conv = HeteroGraphConv({k[1]: _DslGCN(6, 4) for k in rels})
+    xs = {t: torch.randn(n, 6) for t, n in sizes.items()}
+    norms = {str(k): torch.rand(sizes[k[2]], 1) for k in rels}
+    out = conv(h, xs, norms)
+    assert set(out) == {"a", "b"}
+    da, db = out["a"], out["b"]
+    assert isinstance(da, mp.DeferredAgg) and isinstance(db, mp.DeferredAgg)
+    assert len(da.terms) == 2 and da.post == ("squeeze1",) and da.alpha == pytest.approx(0.5)
+    assert [t.graph.relation for t in da.terms] == [("a", "aa", "a"), ("b", "ba", "a")]
+    assert all(t.kind == "sum" and t.scale is not None and t.scale.shape == (30,) for t in da.terms)
+    assert torch.equal(da.terms[1].scale, norms[str(("b", "ba", "a"))].reshape(-1))
+    assert len(db.terms) == 1 and db.alpha == 1.0 and tuple(db.shape) == (20, 4) and tuple(da.shape) == (30, 4)
+    # results of different destination types cannot be joined
+    h.stitch = False   # eager mode would call the kernels at once: on the CPU that fails loudly, it does not defer
+    with pytest.raises(Exception):
+        conv(h, xs, norms)

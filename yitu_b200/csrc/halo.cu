@@ -112,47 +112,61 @@ struct PushParams {
     unsigned long long *counter;  // next unclaimed item (zeroed before the launch)
 };
 
+// CTAs of 1024 threads at 64 registers per thread: each fills the register file of its SM, so the push kernel owns
+// exactly gridDim.x SMs and nothing else runs on them.  That is on purpose.  Stores into a saturated NVLink back up
+// into the memory pipeline of the SM that issued them, and every other warp on that SM then waits behind them:
+// with two 256-thread push CTAs on EVERY SM an aggregation running beside the push crawled (the own-source pass of
+// a rank took 4.8 ms beside its push and 0.6 ms alone).  About twenty SMs move more than one link direction
+// carries; the other SMs keep a free memory pipeline for the aggregation.
 template <int ROWS>
-__global__ void __launch_bounds__(256) halo_push_kernel(const __grid_constant__ PushParams p) {
+__global__ void __launch_bounds__(1024, 1) halo_push_kernel(const __grid_constant__ PushParams p) {
+    static_assert(32 % ROWS == 0, "a claim of 32 items is copied in groups of ROWS");
     const int lane = threadIdx.x & 31;
     const int64_t nvec = p.row_floats >> 2;
     const int64_t n_items = p.begin[p.n_dests];
     const int64_t total = p.stripes * p.per_stripe;
-    // Items are claimed ROWS at a time from a global counter, not dealt out in advance: on B200 the warps of a
-    // statically partitioned grid finished between 55 % and 100 % of the kernel's duration (SMs differ in their
-    // distance to the NVLink ports), and the slowest decided when the shard had left.
+    // A warp claims 32 items at a time from a global counter (not dealt out in advance: on B200 the warps of a
+    // statically partitioned grid finished between 55 % and 100 % of the kernel's duration - SMs differ in their
+    // distance to the NVLink ports - and the slowest decided when the shard had left).  Lane l resolves item l of the
+    // claim (one coalesced read of the ids, the destination looked up once); the rows are then copied ROWS at a
+    // time, source and destination addresses handed round by shuffles, all loads of a group issued before its stores.
     for (;;) {
         unsigned long long claim = 0;
-        if (lane == 0) claim = atomicAdd(p.counter, static_cast<unsigned long long>(ROWS));
+        if (lane == 0) claim = atomicAdd(p.counter, 32ull);
         const int64_t j0 = static_cast<int64_t>(__shfl_sync(0xffffffffu, claim, 0));
         if (j0 >= total) break;
-        const float4 *src[ROWS];
-        float4 *dst[ROWS];
-        bool ok[ROWS];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const int64_t j = j0 + r;
-            // striped visiting order: consecutive items of the grid come from all over the list, hence from every
-            // destination, so every link out of this GPU is busy from the first moment to the last
-            const int64_t i = (j % p.stripes) * p.per_stripe + j / p.stripes;
-            ok[r] = j < total && i < n_items;
-            src[r] = nullptr;
-            dst[r] = nullptr;
-            if (ok[r]) {
-                int d = 0;
-                while (d + 1 < p.n_dests && i >= p.begin[d + 1]) ++d;
-                src[r] = reinterpret_cast<const float4 *>(p.x + static_cast<int64_t>(__ldg(p.ids + i)) * p.row_floats);
-                dst[r] = reinterpret_cast<float4 *>(p.dst[d] + (i - p.begin[d]) * p.row_floats);
-            }
+        // striped visiting order: consecutive items come from all over the list, hence from every destination, so
+        // every link out of this GPU is busy from the first moment to the last
+        const int64_t j = j0 + lane;
+        const int64_t i = (j % p.stripes) * p.per_stripe + j / p.stripes;
+        const bool mine = j < total && i < n_items;
+        const float4 *my_src = nullptr;
+        float4 *my_dst = nullptr;
+        if (mine) {
+            int d = 0;
+            while (d + 1 < p.n_dests && i >= p.begin[d + 1]) ++d;
+            my_src = reinterpret_cast<const float4 *>(p.x + static_cast<int64_t>(__ldg(p.ids + i)) * p.row_floats);
+            my_dst = reinterpret_cast<float4 *>(p.dst[d] + (i - p.begin[d]) * p.row_floats);
         }
-        for (int64_t v = lane; v < nvec; v += 32) {
-            float4 val[ROWS];
+        const unsigned have = __ballot_sync(0xffffffffu, mine);
+        for (int g = 0; g < 32; g += ROWS) {
+            if (((have >> g) & ((1u << ROWS) - 1u)) == 0u) continue;
+            const float4 *src[ROWS];
+            float4 *dst[ROWS];
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r)
-                if (ok[r]) val[r] = __ldg(src[r] + v);
+            for (int r = 0; r < ROWS; ++r) {
+                src[r] = reinterpret_cast<const float4 *>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), g + r));
+                dst[r] = reinterpret_cast<float4 *>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), g + r));
+            }
+            for (int64_t v = lane; v < nvec; v += 32) {
+                float4 val[ROWS];
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r)
-                if (ok[r]) dst[r][v] = val[r];
+                for (int r = 0; r < ROWS; ++r)
+                    if (src[r]) val[r] = __ldg(src[r] + v);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if (src[r]) dst[r][v] = val[r];
+            }
         }
     }
 }
@@ -187,13 +201,13 @@ extern "C" int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, 
     p.counter = reinterpret_cast<unsigned long long *>(work_counter);
     p.stripes = n_items >= (1 << 16) ? 1024 : 1;
     p.per_stripe = (n_items + p.stripes - 1) / p.stripes;
-    constexpr int kRows = 4;
-    const int64_t blocks = (n_items + 8 * kRows - 1) / (8 * kRows);
-    // development switch: CTAs of the push kernel (default two per SM of a 148-SM part)
+    constexpr int kRows = 8;
+    const int64_t blocks = (n_items + 32 * 32 - 1) / (32 * 32);
+    // SMs given to the push (one CTA each); YITU_PUSH_CTAS is a development switch for measuring other counts
     const char *env = getenv("YITU_PUSH_CTAS");
-    const int64_t max_blocks = (env && *env) ? atoll(env) : 148 * 2;
+    const int64_t max_blocks = (env && *env) ? atoll(env) : 24;
     const unsigned grid = static_cast<unsigned>(blocks < max_blocks ? blocks : (max_blocks > 0 ? max_blocks : 1));
-    halo_push_kernel<kRows><<<grid, 256, 0, st>>>(p);
+    halo_push_kernel<kRows><<<grid, 1024, 0, st>>>(p);
     YITU_LAUNCH_CHECK();
     return YITU_OK;
 }

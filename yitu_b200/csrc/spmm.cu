@@ -696,14 +696,14 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     // aligned; measured 6.20 ms against 6.44 ms with 128-bit loads on the D=256 R-MAT workload.  Narrower rows would
     // need half-warp groups, which lose more than the wider loads gain.
     const auto aligned32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
-    // Edge-stream kernel for graphs of short rows (fewer than 16 edges per row on average), the warp-per-row kernel
+    // Edge-stream kernel for graphs of short rows (fewer than 24 edges per row on average), the warp-per-row kernel
     // otherwise.  Measured on B200 with 128 features and 65.1 M edges: 7.27 M rows (9 edges per row) 5.60 ms
     // against 6.40 ms; 82 k rows (800 per row, nearly all in hub chunks) 3.85 ms against 3.43 ms - the stream kernel
     // holds more state per warp (80 registers, 24 resident warps against 32) and that costs on long rows; at 31 edges
     // per row the two are equal (34.77 / 34.83 ms on 520.8 M edges).
     const int stream_mode = env_int("YITU_SPMM_STREAM", 1);
     const bool stream_ok = !per_head && g.nnz < (1ll << 31) &&
-                           (stream_mode == 2 || (stream_mode == 1 && g.nnz < 16 * g.n_rows));
+                           (stream_mode == 2 || (stream_mode == 1 && g.nnz < 24 * g.n_rows));
     if (stream_ok && D > 128 && D <= 256 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 &&
         aligned32(a->x) && aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch)))
         return dispatch_stream<8, 4, 8>(p, st, 16, 4);
