@@ -169,8 +169,8 @@ def run(args):
     for mode in modes:
         kw = {}
         name = mode
-        if mode.startswith("push"):  # "push", "push1".."push4": at most that many phases; "pushnp": no priority rank
-            kw = dict(max_phases=int(mode[4:]) if mode[4:].isdigit() else 3,
+        if mode.startswith("push"):  # "push", "push1".."push4": at most that many passes; "pushnp": no priority rank
+            kw = dict(max_passes=int(mode[4:]) if mode[4:].isdigit() else 3,
                       priority=None if mode.endswith("np") else "auto")
             mode = "push"
         r = PartitionedSpmm(shard, d, dev, mode=mode, **kw)
@@ -216,7 +216,17 @@ def run(args):
     value = nnz * d / (ms_step * 1e-3) / 1e9
 
     spmm_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "spmm"]
-    move_ms = [a.elapsed_time(b) for tag, a, b in events if tag in ("fetch", "push")]
+    move_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "fetch"]
+    if runner.mode == "push":
+        # per step: from the start of the step to the end of this rank's last push kernel (the priority delivery and
+        # the main push run side by side)
+        t0, ends = None, {}
+        for tag, a, b in events:
+            if tag == "start":
+                t0 = a
+            elif tag == "push" and t0 is not None:
+                ends[id(t0)] = max(ends.get(id(t0), 0.0), t0.elapsed_time(b))
+        move_ms = list(ends.values())
     n_spmm = len(spmm_ms) / args.steps
     n_move = sum(1 for tag, _, _ in events if tag == "fetch") / args.steps
     if runner.mode == "push":

@@ -347,9 +347,11 @@ int yitu_halo_gather_f32(int32_t n_shards, const float *const *shard_ptrs_host, 
  * YiTu_GNN/distributed/communication.py:230-264. */
 int yitu_halo_push_f32(int32_t n_dests, float *const *dst_ptrs_host, const int64_t *list_begin_host,
                        const int32_t *ids, const float *x, int64_t row_floats, uint64_t *work_counter,
-                       yitu_stream_t stream);
+                       int32_t n_sms, yitu_stream_t stream);
 /* work_counter: 8 bytes of device memory owned by the caller, used by one push at a time (the call zeroes it on
- * `stream`; the kernel hands out its items from it). */
+ * `stream`; the kernel hands out its items from it).  n_sms: SMs the push occupies, one 1024-thread CTA each, which
+ * nothing else shares (0 = default, 24: enough to fill one NVLink direction); a push that is paced by its
+ * destination's ingress rather than by this GPU's egress needs fewer. */
 
 /* Delivery flags between GPUs, for the owner-side push.  yitu_flags_signal stores `value` (use the step number:
  * flags only ever grow) into n 64-bit flags, typically one in each reader's memory (peer mappings), in stream order

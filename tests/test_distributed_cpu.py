@@ -103,23 +103,22 @@ def _worker(rank, world, port, errors):
         blocks = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(blocks, mine)
         rows_per_rank = [bounds[p + 1] - bounds[p] for p in range(world)]
-        for max_phases, prio in ((3, "auto"), (1, None), (2, world - 1)):
-            sched = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_phases=max_phases,
+        for max_passes, prio in ((3, "auto"), (1, None), (2, world - 1), (4, None)):
+            sched = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_passes=max_passes,
                                  priority=prio)
             seen = [None] * world
             dist.all_gather_object(seen, sched.describe())
             assert all(s_ == seen[0] for s_ in seen), "every rank must derive the same schedule"
-            assert sched.n_phases <= max_phases and sorted(sched.phase_of_owner)[0] == 0
             my = sched.passes[rank]
+            assert 1 <= len(my) <= max_passes
             assert sorted(p for owners, _ in my for p in owners) == list(range(world)), "each owner in exactly one pass"
             assert rank in my[0][0], "own sources belong to the first pass"
             if prio == world - 1 and rank == prio:
                 assert my == [(list(range(world)), PushSchedule.PRIORITY)]
-            waits = [w_ for _, w_ in my]
-            assert waits == sorted(waits) or waits[0] == PushSchedule.PRIORITY
-            for owners, wait in my:  # a pass may only use shards whose phase has ended by the time it starts
-                for p in owners:
-                    assert p == rank or wait == PushSchedule.PRIORITY or sched.phase_of_owner[p] <= wait
+            elif sched.priority is None:
+                # owners are taken in the order of their modelled delivery: a later pass never holds an earlier owner
+                order = [max(sched.push_ms[p] for p in owners if p != rank) for owners, _ in my if set(owners) - {rank}]
+                assert order == sorted(order)
             total = np.zeros_like(ref, dtype=np.float64)
             nnz_sum = 0
             for ip_j, li_j, v_j, _ in source_passes(shard, plan, my):

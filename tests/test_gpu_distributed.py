@@ -43,7 +43,7 @@ def _worker(rank, world, port, errors):
         bounds = partition_bounds(indptr, world)
         shard = RowShard(indptr, indices, values, bounds, rank)
         lo, hi = shard.row_begin, shard.row_end
-        for mode, kw in (("push", {}), ("push", dict(max_phases=1, priority=None)), ("push", dict(priority=1)),
+        for mode, kw in (("push", {}), ("push", dict(max_passes=1, priority=None)), ("push", dict(priority=1)),
                          ("peer", {}), ("allgather", {})):
             r = PartitionedSpmm(shard, d, dev, mode=mode, **kw)
             for step in range(3):  # new features every step: a stale halo row would show
@@ -142,13 +142,13 @@ def test_push_exchange_and_passes_with_four_ranks_emulated_on_one_gpu():
         dst_ptrs = [bufs[q].data_ptr() + 4 * d * (shards[q].n_local + plans[q].owner_offsets[p]) for q in dests]
         check(lib().yitu_halo_push_f32(len(dests), (C.c_void_p * len(dests))(*dst_ptrs),
                                        (C.c_int64 * (len(dests) + 1))(*begin), C.c_void_p(ids.data_ptr()),
-                                       C.c_void_p(bufs[p].data_ptr()), d, C.c_void_p(counter.data_ptr()), st))
+                                       C.c_void_p(bufs[p].data_ptr()), d, C.c_void_p(counter.data_ptr()), 0 if p % 2 else 3, st))
     torch.cuda.synchronize(dev)
     for q in range(world):
         assert torch.equal(bufs[q][shards[q].n_local:], x[plans[q].halo_ids.long()]), "rank %d: halo slots" % q
     blocks = [owner_edge_counts(s, world) for s in shards]
     rows = [s.n_local for s in shards]
-    for kw in (dict(), dict(max_phases=1, priority=None), dict(max_phases=4, priority=world - 1)):
+    for kw in (dict(), dict(max_passes=1, priority=None), dict(max_passes=4, priority=world - 1)):
         sched = PushSchedule(need, blocks, rows, d, **kw)
         for q, s in enumerate(shards):
             out = torch.full((s.n_local, d), float("nan"), device=dev)

@@ -99,7 +99,7 @@ SYMBOLS = {
     "yitu_shared_close": (C.c_int, [c_vp]),
     "yitu_shared_free": (C.c_int, [c_vp]),
     "yitu_halo_gather_f32": (C.c_int, [c_i32, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
-    "yitu_halo_push_f32": (C.c_int, [c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "yitu_halo_push_f32": (C.c_int, [c_i32, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, c_vp]),
     "yitu_flags_signal": (C.c_int, [c_i32, c_vp, C.c_uint64, c_vp]),
     "yitu_flags_wait": (C.c_int, [c_vp, C.c_uint32, C.c_uint64, c_i64, c_vp, c_vp]),
 }

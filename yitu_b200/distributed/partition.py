@@ -74,30 +74,33 @@ def owner_edge_counts(shard, world):
 
 
 class PushSchedule:
-    """Order in which the feature shards become usable, and each rank's aggregation passes.
+    """When each owner's rows are with its readers, and how each rank cuts its aggregation into passes.
 
     Every owner pushes the rows its peers need from the first moment of a step, at the speed of its own NVLink
-    egress, so owner p is done after about egress_rows[p] * row_bytes / bandwidth.  Owners are sorted by that time
-    and cut into at most `max_phases` consecutive PHASES; the end of a phase ("every owner of the phase has
-    delivered everything") is one synchronisation point.  A rank aggregates in PASSES: pass 0 takes the edges whose
-    sources it owns itself (usable at once) together with the phases merged into it, each later pass takes the
-    next phases and accumulates into the output.  More passes start earlier but touch the output rows again.
+    egress, so owner p has delivered after about egress_rows[p] * row_bytes / bandwidth; readers learn of it through
+    per-(reader, owner) flags, so each reader plans for itself.  A rank aggregates in PASSES: its owners sorted by
+    delivery time are cut into at most `max_passes` consecutive groups; pass 0 also takes the edges whose sources the
+    rank owns (usable at once); a pass starts when its last owner has delivered and accumulates into the output of
+    the passes before it.  More passes start earlier but pay the per-row cost of a pass again.
 
     One rank may be served FIRST (`priority`): every owner sends that rank's rows before anything else, and the
     rank aggregates in a single pass as soon as they are in.  This is for the rank whose aggregation is the longest
     (the shard with by far the most destination rows on a skewed graph): it cannot afford to wait for the slowest
-    owner, and a second pass over its many output rows costs more than it gains.
+    owner, and a second pass over its many rows costs more than it gains.
 
-    Phases, merges and the priority rank are chosen by a small exhaustive search over a linear cost model
-    (per edge, per destination row, per re-read output row); the model only has to rank the alternatives.
+    Cuts and the priority rank are chosen by exhaustive search over a linear cost model, per edge and per
+    destination row of a pass; the constants are fitted to B200 measurements of the 128-feature workload
+    (0.055 ns per edge, 0.35 ns per row, 690 GB/s out of one GPU) and only have to rank the alternatives.
 
     need_rows[q][p]   rows that rank q needs from owner p          (every rank holds the same matrix)
     block_edges[q][p] edges of rank q whose source row owner p holds
     rows[q]           destination rows of rank q
     """
 
-    def __init__(self, need_rows, block_edges, rows, d, max_phases=3, egress_gbs=700.0, sync_ms=0.04,
-                 ns_per_edge=0.055, ns_per_row=0.25, ns_per_row_again=0.17, priority="auto"):
+    PRIORITY = -2
+
+    def __init__(self, need_rows, block_edges, rows, d, max_passes=3, egress_gbs=690.0, sync_ms=0.03,
+                 ns_per_edge=0.055, ns_per_row=0.35, ns_per_row_again=0.03, priority="auto"):
         import itertools
         P = len(rows)
         self.world, self.d = P, int(d)
@@ -108,40 +111,35 @@ class PushSchedule:
         self.egress_rows = [sum(need[q][p] for q in range(P)) for p in range(P)]
         total_edges = [sum(int(e) for e in block_edges[q]) for q in range(P)]
 
-        def evaluate(phase_of, push_ms, prio, prio_ready):
-            n_ph = max(phase_of) + 1
-            ready = [0.0] * n_ph
-            for p in range(P):
-                ready[phase_of[p]] = max(ready[phase_of[p]], push_ms[p] + sync_ms)
-            per_rank, worst = [], 0.0
-            for q in range(P):
-                if q == prio:  # one pass, as soon as its rows are in
-                    t = prio_ready + c_e * total_edges[q] + c_r * rows[q]
-                    per_rank.append((t, None))
-                    worst = max(worst, t)
-                    continue
-                # items in order of availability: own sources, then the phases
-                edges = [0] * (n_ph + 1)
-                for p in range(P):
-                    edges[0 if p == q else 1 + phase_of[p]] += int(block_edges[q][p])
-                avail = [0.0] + ready
-                items = [i for i in range(n_ph + 1) if edges[i] > 0] or [0]
-                best_q = None
-                for cuts in range(1 << (len(items) - 1)):  # bit i set: a new pass starts before items[i+1]
-                    t, first, acc_e, last_avail, passes, cur = 0.0, True, 0, 0.0, [], []
-                    for i, it in enumerate(items):
-                        cur.append(it)
-                        acc_e += edges[it]
-                        last_avail = avail[it]
-                        if i == len(items) - 1 or (cuts >> i) & 1:
-                            t = max(t, last_avail) + c_e * acc_e + c_r * rows[q] + (0.0 if first else c_w * rows[q])
-                            passes.append(cur)
-                            first, acc_e, cur = False, 0, []
-                    if best_q is None or t < best_q[0] - 1e-9:
-                        best_q = (t, passes)
-                per_rank.append(best_q)
-                worst = max(worst, best_q[0])
-            return worst, per_rank
+        def plan_reader(q, push_ms):
+            """Best cuts for reader q: (finish time, [(owners, time the pass may start)])."""
+            owners = sorted((p for p in range(P) if p != q and block_edges[q][p] > 0), key=lambda p: (push_ms[p], p))
+            idle = [p for p in range(P) if p != q and block_edges[q][p] <= 0]  # nothing to gather from them
+            best_q = None
+            n = len(owners)
+            for k in range(1, min(max_passes, max(n, 1)) + 1):
+                for cut in itertools.combinations(range(1, n), k - 1) if n else [()]:
+                    groups = [owners[a:b] for a, b in zip((0,) + cut, cut + (n,))] if n else [[]]
+                    # own sources: a pass of their own when that is worth it, else part of the first group
+                    for own_alone in ((False, True) if n and block_edges[q][q] > 0 and k < max_passes else (False,)):
+                        t, plan = 0.0, []
+                        if own_alone:
+                            t = c_e * int(block_edges[q][q]) + c_r * rows[q]
+                            plan.append(([q], 0.0))
+                        for gi, grp in enumerate(groups):
+                            edges = sum(int(block_edges[q][p]) for p in grp)
+                            members = list(grp)
+                            if gi == 0 and not own_alone:
+                                edges += int(block_edges[q][q])
+                                members = [q] + members
+                            start = max([push_ms[p] + sync_ms for p in grp] + [0.0])
+                            t = max(t, start) + c_e * edges + c_r * rows[q] + (c_w * rows[q] if plan else 0.0)
+                            plan.append((members, start))
+                        if best_q is None or t < best_q[0] - 1e-9:
+                            best_q = (t, plan)
+            t, plan = best_q
+            plan[0] = (plan[0][0] + idle, plan[0][1])
+            return t, plan
 
         if priority == "auto":
             heavy = max(range(P), key=lambda q: c_e * total_edges[q] + c_r * rows[q])
@@ -157,47 +155,34 @@ class PushSchedule:
                 prio_ready = max(max(first_ms), sum(need[prio]) * row_ms) + sync_ms  # slowest sender or its own ingress
             push_ms = [first_ms[p] + (self.egress_rows[p] - (need[prio][p] if prio is not None else 0)) * row_ms
                        for p in range(P)]
-            order = sorted(range(P), key=lambda p: (push_ms[p], p))
-            for k in range(1, min(max_phases, P) + 1):
-                for cut in itertools.combinations(range(1, P), k - 1):
-                    phase_of = [0] * P
-                    ph = 0
-                    for pos, p in enumerate(order):
-                        if ph < len(cut) and pos == cut[ph]:
-                            ph += 1
-                        phase_of[p] = ph
-                    worst, per_rank = evaluate(phase_of, push_ms, prio, prio_ready)
-                    if best is None or worst < best[0] - 1e-6:  # ties: no priority rank, fewer phases (searched first)
-                        best = (worst, phase_of, per_rank, prio, push_ms)
-        self.model_ms, self.phase_of_owner, per_rank, self.priority, self.push_ms = best
-        self.n_phases = max(self.phase_of_owner) + 1
-        # passes[q]: list of (owners whose edges the pass takes, phase it has to wait for: -1 nothing,
-        # PRIORITY the priority delivery, k >= 0 the end of phase k)
-        self.passes = []
-        for q in range(P):
-            if q == self.priority:
-                self.passes.append([(list(range(P)), self.PRIORITY)])
-                continue
-            out = []
-            for items in per_rank[q][1]:
-                owners = [p for p in range(P) if (0 if p == q else 1 + self.phase_of_owner[p]) in items]
-                out.append((owners, max(items) - 1))
-            self.passes.append(out)
-
-    PRIORITY = -2
+            worst, plans = 0.0, []
+            for q in range(P):
+                if q == prio:  # one pass, as soon as its rows are in
+                    t, plan = prio_ready + c_e * total_edges[q] + c_r * rows[q], [(list(range(P)), prio_ready)]
+                else:
+                    t, plan = plan_reader(q, push_ms)
+                plans.append(plan)
+                worst = max(worst, t)
+            if best is None or worst < best[0] - 1e-6:  # ties: no priority rank
+                best = (worst, plans, prio, push_ms)
+        self.model_ms, plans, self.priority, self.push_ms = best
+        # passes[q]: list of (owners whose edges the pass takes, PRIORITY for the priority rank's single pass, else
+        # the pass number)
+        self.passes = [[(owners, self.PRIORITY if q == self.priority else j) for j, (owners, _) in enumerate(plan)]
+                       for q, plan in enumerate(plans)]
+        self._starts = [[round(t, 3) for _, t in plan] for plan in plans]
 
     def describe(self):
-        return {"phases": [[p for p in range(self.world) if self.phase_of_owner[p] == k] for k in range(self.n_phases)],
-                "priority_rank": self.priority,
+        return {"priority_rank": self.priority,
                 "push_ms_model": [round(t, 3) for t in self.push_ms],
-                "passes_per_rank": [[{"owners": o, "after": {-1: "start", self.PRIORITY: "priority delivery"}.get(w, "phase %d" % w)}
-                                     for o, w in ps] for ps in self.passes],
+                "passes_per_rank": [[{"owners": o, "may_start_ms_model": t} for (o, _), t in zip(ps, ts)]
+                                    for ps, ts in zip(self.passes, self._starts)],
                 "step_ms_model": round(self.model_ms, 3)}
 
 
 def source_passes(shard, plan, passes):
     """Cut a shard's edges into the aggregation passes of a PushSchedule.  `passes` is this rank's list of
-    (owners, wait_phase).  Returns [(indptr, local_indices, values, wait_phase)] with every row present in every
+    (owners, tag).  Returns [(indptr, local_indices, values, tag)] with every row present in every
     pass (empty where the pass holds none of its edges); the column ids index the buffer [own rows | halo rows]."""
     cols = shard.indices
     b = torch.tensor(shard.bounds, dtype=cols.dtype, device=cols.device)

@@ -2,10 +2,10 @@
 feature matrix in one buffer that its peers can map (CUDA IPC); three ways of filling the halo part:
 
   mode="push"       the OWNER of a row writes it into the halo buffers of the ranks that need it (peer stores
-                    over NVLink, each needed row crosses once), starting at the first moment of the step.  Shards
-                    become usable in phases (PushSchedule); a rank aggregates the edges of a phase as soon as that
-                    phase has landed and accumulates later phases into the same output, so most of the aggregation
-                    runs while the slowest owner is still sending.  Deliveries are announced by 64-bit flags that
+                    over NVLink, each needed row crosses once), starting at the first moment of the step.  A rank
+                    aggregates in passes (PushSchedule): the edges whose sources have arrived first, then, into the
+                    same output, those of the owners that deliver later, so most of the aggregation runs while the
+                    slowest owner is still sending.  Deliveries are announced by 64-bit flags that
                     the owner stores into the reader's memory after its push; the reader's stream waits for the
                     flags of the owners a pass needs (bounded wait), so no collective runs inside a step.
   mode="peer"       the READER fetches the rows with peer loads, then aggregates: two serial steps.
@@ -89,7 +89,7 @@ class PartitionedSpmm:
     together.  x_local may be rewritten as soon as step() has been enqueued in the push and all-gather modes; in the
     peer mode the peers read it during THEIR step, so rewrite it only after a step(fence=True) or a barrier."""
 
-    def __init__(self, shard, d, device, group=None, mode="push", weight_mode=ops.W_EDGE, max_phases=3,
+    def __init__(self, shard, d, device, group=None, mode="push", weight_mode=ops.W_EDGE, max_passes=3,
                  priority="auto"):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
@@ -130,17 +130,17 @@ class PartitionedSpmm:
             self._ptrs = (C.c_void_p * self.world)(*ptrs)
             self._bounds = (C.c_int64 * (self.world + 1))(*shard.bounds)
             if self.mode == "push":
-                self._setup_push(ptrs, max_phases, priority)
+                self._setup_push(ptrs, max_passes, priority)
 
     # ------------------------------------------------------------------------------------------ push set-up
-    def _setup_push(self, ptrs, max_phases, priority):
+    def _setup_push(self, ptrs, max_passes, priority):
         sh, plan, world, rank, d = self.shard, self.plan, self.world, self.rank, self.d
         need_rows, recv_ids, recv_counts = exchange_need_lists(plan, rank, world, self.group)
         mine = torch.tensor(owner_edge_counts(sh, world), dtype=torch.int64, device=self.device)
         blocks = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(blocks, mine, group=self.group)
         rows = [sh.bounds[p + 1] - sh.bounds[p] for p in range(world)]
-        self.schedule = PushSchedule(need_rows, [b.tolist() for b in blocks], rows, d, max_phases=max_phases,
+        self.schedule = PushSchedule(need_rows, [b.tolist() for b in blocks], rows, d, max_passes=max_passes,
                                      priority=priority)
         offsets = [None] * world  # offsets[q][p]: first halo slot that rank q reserves for owner p's rows
         dist.all_gather_object(offsets, list(plan.owner_offsets), group=self.group)
@@ -178,19 +178,24 @@ class PartitionedSpmm:
             self._passes.append((ops.PreparedGraph(ip, li, sh.n_local + plan.n_halo), vals, mask))
         self.graph = self._passes[0][0]
         self.push_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self.first_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self._flags = self.shared.flags_tensor()
         self._flag_base = 16 if rank == prio else 0  # the priority reader waits for the priority deliveries
-        self._work_counter = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self._work_counter = torch.zeros(2, dtype=torch.int64, device=self.device)
         self._wait_error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._step = 0
         self.wait_timeout_ns = 2_000_000_000
 
-    def _push(self, args):
+    # SMs of the priority delivery: every owner sends to the one priority rank at once, so that rank's ingress (one link
+    # direction shared by all of them) paces the transfer; a few SMs per owner keep it fed, and the main push keeps its own
+    FIRST_SMS = 6
+
+    def _push(self, args, counter=0, n_sms=0):
         (n_dests, dst, begin, ids), (n_flags, flags) = args
         st = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         with torch.cuda.device(self.device):
             check(lib().yitu_halo_push_f32(n_dests, dst, begin, _ptr(ids), _ptr(self.x_local), self.d,
-                                           _ptr(self._work_counter), st))
+                                           C.c_void_p(self._work_counter.data_ptr() + 8 * counter), n_sms, st))
             check(lib().yitu_flags_signal(n_flags, flags, self._step, st))
 
     def _wait_for(self, mask):
@@ -250,12 +255,19 @@ class PartitionedSpmm:
         if events is not None:
             events.append(("start", t0, t0))
         ps.wait_stream(main)
+        # this rank's rows leave from the first moment of the step; each push is followed by the flags that tell its
+        # destinations "the rows of this owner are in place".  The priority delivery runs BESIDE the main push, on its
+        # own stream and SMs: the priority rank's ingress limits it, and the owner's egress must not idle meanwhile.
+        if self._push_first is not None:
+            fs = self.first_stream
+            fs.wait_stream(main)
+            with torch.cuda.stream(fs):
+                a = self._mark(events)
+                self._push(self._push_first, counter=1, n_sms=self.FIRST_SMS)
+                if events is not None:
+                    events.append(("push", a, self._mark(events)))
         with torch.cuda.stream(ps):
-            # this rank's rows leave from the first moment of the step; each push is followed by the flags that tell
-            # its destinations "the rows of this owner are in place"
             a = self._mark(events)
-            if self._push_first is not None:
-                self._push(self._push_first)
             if self._push_rest is not None:
                 self._push(self._push_rest)
             if events is not None:
@@ -266,6 +278,8 @@ class PartitionedSpmm:
                 events.append(("ready:pass%d" % j, t0, self._mark(events)))
             self._spmm(g, self.xbuf, vals, accumulate=j > 0, events=events)
         main.wait_stream(ps)  # this rank's shard has been read: it may be rewritten once the step returns
+        if self._push_first is not None:
+            main.wait_stream(self.first_stream)
         if events is not None:
             events.append(("end", t0, self._mark(events)))
         return self.out
