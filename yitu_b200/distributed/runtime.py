@@ -15,6 +15,7 @@ No collective carries feature data in the push and peer modes (NCCL moves one fl
 no multicast load is used anywhere.
 """
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -188,7 +189,7 @@ class PartitionedSpmm:
 
     # SMs of the priority delivery: every owner sends to the one priority rank at once, so that rank's ingress (one link
     # direction shared by all of them) paces the transfer; a few SMs per owner keep it fed, and the main push keeps its own
-    FIRST_SMS = 6
+    FIRST_SMS = int(os.environ.get("YITU_PUSH_FIRST_SMS", "12"))  # development switch: the environment overrides
 
     def _push(self, args, counter=0, n_sms=0):
         (n_dests, dst, begin, ids), (n_flags, flags) = args
