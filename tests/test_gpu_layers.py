@@ -278,7 +278,7 @@ def test_full_size_hetero_rgcn_sampled_rows_against_float64():
         truth = torch.zeros(len(rows), 64, dtype=torch.float64, device=dev)
         for i in ids:
             fc = layer.fcs["r%d" % i]
-            w, b_ = fc.weight.double(), fc.bias.double()
+            w, b_ = fc.weight.detach().double(), fc.bias.detach().double()
             ip, ix = rels[i][2], rels[i][3]
             for j, r in enumerate(rows):
                 b0, e0 = int(ip[r]), int(ip[r + 1])

@@ -195,10 +195,10 @@ def test_dsl_generic_reduction_and_hetero_container():
 
 
 def _hetero_case(rng, dev):
-    """Three node types, five relations; type "a" is reached by three of them, "b" by two, "c" by none."""
+    """Three node types, six relations; type "a" is reached by three of them, "b" by two, "c" by one."""
     from yitu_b200.xgnn_h import Block, mp
     sizes = {"a": 150, "b": 90, "c": 60}
-    keys = [("a", "aa", "a"), ("b", "ba", "a"), ("c", "ca", "a"), ("a", "ab", "b"), ("c", "cb", "b")]
+    keys = [("a", "aa", "a"), ("b", "ba", "a"), ("c", "ca", "a"), ("a", "ab", "b"), ("c", "cb", "b"), ("a", "ac", "c")]
     blocks, norms, dense = {}, {}, {}
     for k in keys:
         ip, ix = random_csr(rng, sizes[k[2]], sizes[k[0]], density=0.08)
@@ -260,15 +260,15 @@ def test_reference_rgcn_model_is_stitched_automatically(reference_models, monkey
     calls = _count_aggregations(monkeypatch)
     out = model(h, norms, xs)
     y = {t: torch.as_tensor(v + 0.0) for t, v in out.items()}     # first real use computes the deferred results
-    assert set(y) == {"a", "b"} and y["a"].shape == (150, 5) and y["b"].shape == (90, 5)
-    assert calls["spmm"] == 4, "two layers x two destination types: one stitched aggregation each, got %r" % calls
+    assert set(y) == {"a", "b", "c"} and y["a"].shape == (150, 5) and y["b"].shape == (90, 5)
+    assert calls["spmm"] == 6, "two layers x three destination types: one aggregation each, got %r" % calls
     (y["a"].sum() + y["b"].sum()).backward()
     grads = [p.grad.clone() for p in model.parameters() if p.grad is not None]
     model.zero_grad()
     h.stitch = False
     calls2 = _count_aggregations(monkeypatch)
     out2 = model(h, norms, xs)
-    assert calls2["spmm"] == 10, "unstitched: one aggregation per relation and layer"
+    assert calls2["spmm"] == 12, "unstitched: one aggregation per relation and layer"
     for t in y:
         assert _close(y[t], out2[t])
     (out2["a"].sum() + out2["b"].sum()).backward()
@@ -299,7 +299,8 @@ def test_reference_rgat_model_is_stitched_automatically(reference_models, monkey
     calls = _count_aggregations(monkeypatch)
     out = model(h, xs)
     y = {t: v + 0.0 for t, v in out.items()}
-    assert calls["edge_softmax_fwd"] == 4 and calls["spmm"] == 4 and calls["gat_fwd"] == 0, calls
+    # types "a" and "b": segmented softmax + SpMM over the stitched relations; type "c" has one relation: fused kernel
+    assert calls["edge_softmax_fwd"] == 4 and calls["spmm"] == 4 and calls["gat_fwd"] == 2, calls
     (y["a"].sum() + y["b"].sum()).backward()
     grads = [p.grad.clone() for p in model.parameters() if p.grad is not None]
     model.zero_grad()
@@ -308,8 +309,12 @@ def test_reference_rgat_model_is_stitched_automatically(reference_models, monkey
     for t in y:
         assert _close(y[t], out2[t], 5e-5)
     (out2["a"].sum() + out2["b"].sum()).backward()
-    for g1, g2 in zip(grads, [p.grad for p in model.parameters() if p.grad is not None]):
-        assert _close(g1, g2, 2e-4)
+    grads2 = [p.grad for p in model.parameters() if p.grad is not None]
+    top = max(float(g.abs().max()) for g in grads2)
+    for g1, g2 in zip(grads, grads2):
+        # gradients that are zero by symmetry (a shift of all scores of a row leaves the softmax unchanged, so the
+        # bias of linear_q gets none) hold rounding noise only: measured against the largest gradient instead
+        assert float((g1 - g2).abs().max()) <= 2e-4 * max(float(g2.abs().max()), 1e-3 * top)
 
 
 def test_stitched_graph_with_the_attention_pattern_takes_the_two_operator_route(monkeypatch):
