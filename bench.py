@@ -889,6 +889,10 @@ def main():
                          "(push | push1..push4 | pushnp | peer | allgather)")
     ap.add_argument("--verbose-trials", action="store_true",
                     help="partitioned: keep schedule and per-rank timeline of the exchange modes that lost the trial")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="partitioned, 1 GPU: aggregate only shard --shard of a SHARD_OF-way split (the kernel one rank of a "
+                         "multi-GPU run executes, without the exchange: for single-GPU profiling)")
+    ap.add_argument("--shard", type=int, default=0)
     ap.add_argument("--row-cost", type=int, default=0,
                     help="partitioned: balance edges + ROW_COST * rows instead of edges alone (not the prescribed split)")
     args = ap.parse_args()

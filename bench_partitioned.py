@@ -116,6 +116,35 @@ def verify_rows(shard, out, d, n_random=96, chunk=1 << 16):
     return len(rows), float(err.max()) / max(scale, 1e-30), ok
 
 
+class ShardOnOneGpu:
+    """One rank's share of a P-way split, aggregated on ONE GPU from the whole feature matrix (global column ids, no
+    exchange): the kernel of that rank of a multi-GPU run, in a form that a single-GPU profiler can capture."""
+    mode, schedule, halo_bytes, plan = "local", None, 0, None
+
+    def __init__(self, shard, n, d, device):
+        from yitu_b200 import graphs, ops
+        self.ops, self.device, self.shard = ops, device, shard
+        self.graph = ops.PreparedGraph(shard.indptr, shard.indices, n)
+        self.x = graphs.randn_features(FEATURE_SEED, n, d, device=device)
+        self.x_local = self.x[shard.row_begin:shard.row_end]
+        self.out = torch.empty(shard.n_local, d, device=device)
+
+    def step(self, events=None):
+        a = b = None
+        if events is not None:
+            a = torch.cuda.Event(enable_timing=True)
+            a.record()
+        out = self.ops.spmm(self.graph, self.x, mode=self.ops.W_EDGE, edge_values=self.shard.values, out=self.out)
+        if events is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            events.append(("spmm", a, b))
+        return out
+
+    def close(self):
+        pass
+
+
 def step_timeline(runner, rank, world):
     """Where the time of a push-mode step goes on every rank: one step with events; offsets in ms from the moment
     the step's opening handshake completed on that rank."""
@@ -158,8 +187,11 @@ def run(args):
 
     indptr, indices, values = graphs.spmm_partitioned(device=dev, n=n, e=e)
     nnz = indices.numel()
-    bounds = partition_bounds(indptr, world, row_cost=args.row_cost)
-    shard = RowShard(indptr, indices, values, bounds, rank)
+    one_shard = world == 1 and args.shard_of > 1
+    bounds = partition_bounds(indptr, args.shard_of if one_shard else world, row_cost=args.row_cost)
+    shard = RowShard(indptr, indices, values, bounds, args.shard if one_shard else rank)
+    if one_shard:
+        nnz = shard.nnz  # the unit count of this run is the shard's
     del indptr, indices, values
     torch.cuda.empty_cache()
     x_shard = graphs.randn_features(FEATURE_SEED, shard.n_local, d, device=dev, row_begin=shard.row_begin)
@@ -173,7 +205,7 @@ def run(args):
             kw = dict(max_passes=int(mode[4:]) if mode[4:].isdigit() else 3,
                       priority=None if mode.endswith("np") else "auto")
             mode = "push"
-        r = PartitionedSpmm(shard, d, dev, mode=mode, **kw)
+        r = ShardOnOneGpu(shard, n, d, dev) if one_shard else PartitionedSpmm(shard, d, dev, mode=mode, **kw)
         r.x_local.copy_(x_shard)
         runners[name] = r
         out = None
@@ -300,24 +332,26 @@ def run(args):
             main.wait_stream(s_out)
             main.wait_stream(s_in)
 
-    e2e_runner = E2E()
-    for _ in range(2):
-        e2e_runner.step()
-    e2e_runner.drain()
-    e2e_steps = max(3, min(args.steps, 6))
-
-    class Timed:
-        device = dev
-
-        def step(self, events=None):
+    e2e_ms, timed, e2e_runner = None, None, None
+    if not args.no_e2e:
+        e2e_runner = E2E()
+        for _ in range(2):
             e2e_runner.step()
-            if self.left == 1:
-                e2e_runner.drain()  # the last result has to be on the host before the clock stops
-            self.left -= 1
+        e2e_runner.drain()
+        e2e_steps = max(3, min(args.steps, 6))
 
-    timed = Timed()
-    timed.left = e2e_steps
-    e2e_ms = _time_steps(timed, e2e_steps, world)
+        class Timed:
+            device = dev
+
+            def step(self, events=None):
+                e2e_runner.step()
+                if self.left == 1:
+                    e2e_runner.drain()  # the last result has to be on the host before the clock stops
+                self.left -= 1
+
+        timed = Timed()
+        timed.left = e2e_steps
+        e2e_ms = _time_steps(timed, e2e_steps, world)
     bytes_io = torch.tensor([h_x.numel() * 4.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(bytes_io)
@@ -336,11 +370,12 @@ def run(args):
         move_max = max(s[1] for s in per_rank)
         roof = bench.roofline(bench.spmm_kernel_name(int(per_rank[0][3]), int(per_rank[0][4]), d) +
                               (" (rank 0 shard, all passes)" if world > 1 else ""),
-                              k_bytes, k_ms, "spmm_partitioned_d128" if world == 1 and not args.scale else None)
+                              k_bytes, k_ms, "spmm_partitioned_d128" if world == 1 and not args.scale and not one_shard else None)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
-                "config": {"workload": workload_name(n, e, d), "nnz": nnz,
+                "config": {"workload": workload_name(n, e, d) + ("_shard%d_of_%d" % (args.shard, args.shard_of) if one_shard else ""),
+                           "nnz": nnz,
                            "parallelism": "row_partition_%d" % world,
                            "balance": "edges" if not args.row_cost else "edges + %d * rows" % args.row_cost,
                            "halo": best, "trial_ms": trial, "schedule": schedule, "timeline_ms": timeline,
@@ -365,9 +400,10 @@ def run(args):
                              if best.startswith("push") else
                              "reader-side peer loads: halo bytes of a rank / duration of its gather kernel (best rank)")},
                 "cpu_baseline": None,
-                "e2e": {"value": nnz * d / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": int(bytes_io), "d2h_bytes_per_step": int(bytes_io),
-                        "mode": "pipelined: copy-in / aggregation / copy-out of neighbouring steps overlap"},
+                "e2e": None if e2e_ms is None else {
+                    "value": nnz * d / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(bytes_io), "d2h_bytes_per_step": int(bytes_io),
+                    "mode": "pipelined: copy-in / aggregation / copy-out of neighbouring steps overlap"},
                 "gpu_launches": int(round(sum(s[5] for s in per_rank))) * args.steps, "clocks": clocks}
         if not args.no_cpu_baseline:
             try:
@@ -375,7 +411,7 @@ def run(args):
                                                                           min_seconds=10.0 if world == 1 else 0.0)
             except Exception as exc:  # never lose the line to the extra measurement
                 line["cpu_baseline"] = {"error": str(exc)[:200]}
-        if world == 1 and not args.scale and not args.no_sub_records:
+        if world == 1 and not args.scale and not args.no_sub_records and not one_shard:
             for key, fn in (("spmm_c2", bench.sub_record_spmm), ("gat_layer", bench.sub_record_gat),
                             ("rgcn_layer", bench.sub_record_rgcn)):
                 try:
