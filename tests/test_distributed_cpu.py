@@ -114,7 +114,11 @@ def _worker(rank, world, port, errors):
             assert sorted(p for owners, _ in my for p in owners) == list(range(world)), "each owner in exactly one pass"
             assert rank in my[0][0], "own sources belong to the first pass"
             if prio == world - 1 and rank == prio:
-                assert my == [(list(range(world)), PushSchedule.PRIORITY)]
+                # its own sources while it waits for its delivery, then every other owner in one pass
+                assert my == [([rank], PushSchedule.PRIORITY), ([p for p in range(world) if p != rank], PushSchedule.PRIORITY)]
+                single = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_passes=max_passes,
+                                      priority=prio, priority_own_first=False)
+                assert single.passes[rank] == [(list(range(world)), PushSchedule.PRIORITY)]
             elif sched.priority is None:
                 # owners are taken in the order of their modelled delivery: a later pass never holds an earlier owner
                 order = [max(sched.push_ms[p] for p in owners if p != rank) for owners, _ in my if set(owners) - {rank}]

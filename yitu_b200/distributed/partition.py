@@ -84,7 +84,8 @@ class PushSchedule:
     the passes before it.  More passes start earlier but pay the per-row cost of a pass again.
 
     One rank may be served FIRST (`priority`): every owner sends that rank's rows before anything else, and the
-    rank aggregates in a single pass as soon as they are in.  This is for the rank whose aggregation is the longest
+    rank aggregates them in a single pass as soon as they are in (the edges whose sources it owns itself in a pass
+    of their own while it waits, with `priority_own_first`).  This is for the rank whose aggregation is the longest
     (the shard with by far the most destination rows on a skewed graph): it cannot afford to wait for the slowest
     owner, and a second pass over its many rows costs more than it gains.
 
@@ -100,7 +101,7 @@ class PushSchedule:
     PRIORITY = -2
 
     def __init__(self, need_rows, block_edges, rows, d, max_passes=3, egress_gbs=690.0, sync_ms=0.03,
-                 ns_per_edge=0.055, ns_per_row=0.35, ns_per_row_again=0.03, priority="auto"):
+                 ns_per_edge=0.055, ns_per_row=0.35, ns_per_row_again=0.03, priority="auto", priority_own_first=True):
         import itertools
         P = len(rows)
         self.world, self.d = P, int(d)
@@ -157,7 +158,12 @@ class PushSchedule:
                        for p in range(P)]
             worst, plans = 0.0, []
             for q in range(P):
-                if q == prio:  # one pass, as soon as its rows are in
+                if q == prio and priority_own_first and 0 < block_edges[q][q] < total_edges[q]:
+                    # the edges whose sources it owns while it waits for its delivery, then everything else in one pass
+                    t_own = c_e * int(block_edges[q][q]) + c_r * rows[q]
+                    t = max(prio_ready, t_own) + c_e * (total_edges[q] - int(block_edges[q][q])) + (c_r + c_w) * rows[q]
+                    plan = [([q], 0.0), ([p for p in range(P) if p != q], prio_ready)]
+                elif q == prio:  # one pass, as soon as its rows are in
                     t, plan = prio_ready + c_e * total_edges[q] + c_r * rows[q], [(list(range(P)), prio_ready)]
                 else:
                     t, plan = plan_reader(q, push_ms)

@@ -91,7 +91,7 @@ class PartitionedSpmm:
     peer mode the peers read it during THEIR step, so rewrite it only after a step(fence=True) or a barrier."""
 
     def __init__(self, shard, d, device, group=None, mode="push", weight_mode=ops.W_EDGE, max_passes=3,
-                 priority="auto"):
+                 priority="auto", priority_own_first=True):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
         self.rank = shard.rank
@@ -131,10 +131,10 @@ class PartitionedSpmm:
             self._ptrs = (C.c_void_p * self.world)(*ptrs)
             self._bounds = (C.c_int64 * (self.world + 1))(*shard.bounds)
             if self.mode == "push":
-                self._setup_push(ptrs, max_passes, priority)
+                self._setup_push(ptrs, max_passes, priority, priority_own_first)
 
     # ------------------------------------------------------------------------------------------ push set-up
-    def _setup_push(self, ptrs, max_passes, priority):
+    def _setup_push(self, ptrs, max_passes, priority, priority_own_first=True):
         sh, plan, world, rank, d = self.shard, self.plan, self.world, self.rank, self.d
         need_rows, recv_ids, recv_counts = exchange_need_lists(plan, rank, world, self.group)
         mine = torch.tensor(owner_edge_counts(sh, world), dtype=torch.int64, device=self.device)
@@ -142,7 +142,7 @@ class PartitionedSpmm:
         dist.all_gather(blocks, mine, group=self.group)
         rows = [sh.bounds[p + 1] - sh.bounds[p] for p in range(world)]
         self.schedule = PushSchedule(need_rows, [b.tolist() for b in blocks], rows, d, max_passes=max_passes,
-                                     priority=priority)
+                                     priority=priority, priority_own_first=priority_own_first)
         offsets = [None] * world  # offsets[q][p]: first halo slot that rank q reserves for owner p's rows
         dist.all_gather_object(offsets, list(plan.owner_offsets), group=self.group)
         send_ids = (recv_ids - sh.row_begin).to(torch.int32)
