@@ -403,6 +403,51 @@ class RgcnWorkload:
                         g.n_rows, g.nnz, self.nnz))
 
 
+class UniformWorkload:
+    """Not one of the configurations: the SpMM of the headline (128 features, fp32 edge weights, int64 row pointers) on a
+    UNIFORM random graph, 2^23 nodes and 2^27 sampled edges.  Every source row is referenced about 16 times from all
+    over the row range, so the 126 MB L2 cannot keep a hot set (the feature matrix is 4.3 GB) and the algorithmic
+    bytes ARE the DRAM bytes: this is the machine's random-row gather ceiling, the figure the R-MAT numbers (where
+    the L2 serves the hub rows) should be read against."""
+    name = "spmm_uniform_n8388608_e134217728_d128"
+
+    def __init__(self, device, n=1 << 23, e=1 << 27, d=128):
+        import torch
+        from yitu_b200 import graphs, ops
+        self.torch, self.ops, self.n, self.d = torch, ops, n, d
+        src, dst = graphs.uniform_edges(9, n, n, e, device=device)
+        self.indptr, self.indices = graphs.csr_by_destination(src, dst, n, n, ptr_dtype=torch.int64)
+        del src, dst
+        self.nnz = self.indices.numel()
+        inv = 1.0 / graphs.in_degrees(self.indptr).clamp(min=1.0)
+        self.values = torch.repeat_interleave(inv, self.indptr[1:] - self.indptr[:-1])
+        self.g = ops.PreparedGraph(self.indptr, self.indices, n)
+        self.g.plan()
+        self.x = graphs.randn_features(1, n, d, device=device)
+        self.out = torch.empty_like(self.x)
+        self.units_per_step = self.nnz * d
+        self.kernel_bytes = self.nnz * (4 * d + 8) + (n + 1) * 8 + 4 * n * d
+        self.compulsory_bytes = self.nnz * 8 + (n + 1) * 8 + 2 * 4 * n * d
+        self.traffic_key = "spmm_uniform_d128"
+        self.dominant_kernel = spmm_kernel_name(self.nnz, n, d)
+
+    def step(self, kernel_events=None):
+        t, ops = self.torch, self.ops
+        if kernel_events is not None:
+            a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            a.record()
+        ops.spmm(self.g, self.x, mode=ops.W_EDGE, edge_values=self.values, out=self.out)
+        if kernel_events is not None:
+            b.record()
+            kernel_events.append((a, b))
+
+    def verify(self):
+        t, ops = self.torch, self.ops
+        out = ops.spmm(self.g, t.ones(self.n, 4, device=self.x.device), mode=ops.W_EDGE, edge_values=self.values)[:, 0]
+        has = (self.indptr[1:] > self.indptr[:-1]).float()
+        assert float((out - has).abs().max()) < 1e-5, "SpMM self-check failed (weights 1/in-degree of a row sum to one)"
+
+
 def cpu_baseline(sample, repeats=5, min_seconds=10.0):
     """Times the CPU restatement (oracle/yitu_oracle.c, OpenMP over destination rows) on the sample."""
     from oracle import oracle as O
@@ -499,6 +544,15 @@ def sub_record_spmm(dev, steps=5):
     ms, k_ms, _ = _measure(wl, steps)
     return {"workload": wl.name, "nnz": wl.nnz, "ms_per_step": ms, "value": wl.units_per_step / (ms * 1e-3) / 1e9,
             "unit": UNIT, "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, k_ms, wl.traffic_key, wl.compulsory_bytes)}
+
+
+def sub_record_uniform(dev, steps=5):
+    """The headline's kernel where the L2 cannot help: the random-row gather ceiling of the machine (see UniformWorkload)."""
+    wl = UniformWorkload(dev)
+    ms, k_ms, _ = _measure(wl, steps)
+    return {"workload": wl.name, "nnz": wl.nnz, "ms_per_step": ms, "value": wl.units_per_step / (ms * 1e-3) / 1e9,
+            "unit": UNIT, "note": "uniform random graph: no hot rows, algorithmic bytes = DRAM bytes",
+            "roofline": roofline(wl.dominant_kernel, wl.kernel_bytes, k_ms, wl.traffic_key, wl.compulsory_bytes)}
 
 
 def sub_record_gat(dev, steps=5):

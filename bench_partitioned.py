@@ -414,7 +414,7 @@ def run(args):
                 line["cpu_baseline"] = {"error": str(exc)[:200]}
         if world == 1 and not args.scale and not args.no_sub_records and not one_shard:
             for key, fn in (("spmm_c2", bench.sub_record_spmm), ("gat_layer", bench.sub_record_gat),
-                            ("rgcn_layer", bench.sub_record_rgcn)):
+                            ("rgcn_layer", bench.sub_record_rgcn), ("spmm_uniform", bench.sub_record_uniform)):
                 try:
                     line[key] = fn(dev)
                 except Exception as exc:
