@@ -13,6 +13,7 @@ second, whole job).  A step is one pass of the workload's hot path over the resi
                       weights, D=256: forward A*X and the transposed product A^T*G (2 * nnz * D edge-feats)
   gat          1 GPU  uniform random N=2^20, 2^25 edges + self loops, 8 heads x 32: fused GAT forward+backward
   rgcn         1 GPU  4 node types, 8 bipartite R-MAT relations x 4M edges, D=64: mean per relation, sum per type
+  uniform      1 GPU  (not a configuration) uniform random N=2^23, 2^27 edges, D=128: no hot rows, the gather ceiling
 
 Default at every N: partitioned - ONE series at 1/2/4/8 GPUs, the same graph throughout.  The N=1 line also
 carries the other three configurations as sub-records (spmm_c2, gat_layer, rgcn_layer), each with its own time and
@@ -430,6 +431,8 @@ class UniformWorkload:
         self.compulsory_bytes = self.nnz * 8 + (n + 1) * 8 + 2 * 4 * n * d
         self.traffic_key = "spmm_uniform_d128"
         self.dominant_kernel = spmm_kernel_name(self.nnz, n, d)
+        self.launches_per_step = 1 + (1 if self.g.plan() else 0)
+        self.kernel_launches_per_step = 1
 
     def step(self, kernel_events=None):
         t, ops = self.torch, self.ops
@@ -440,6 +443,25 @@ class UniformWorkload:
         if kernel_events is not None:
             b.record()
             kernel_events.append((a, b))
+
+    def e2e_setup(self):
+        t = self.torch
+        self.h_x = self.x.cpu().pin_memory()
+        self.h_out = t.empty(self.x.shape, dtype=t.float32).pin_memory()
+        self.h2d = self.d2h = self.x.numel() * 4
+
+    def e2e_step(self):
+        ops = self.ops
+        x = self.h_x.to(self.x.device, non_blocking=True)
+        self.h_out.copy_(ops.spmm(self.g, x, mode=ops.W_EDGE, edge_values=self.values), non_blocking=True)
+
+    def cpu_sample(self, seconds_hint=15.0):
+        hi = self.n // 8
+        ip = self.indptr[:hi + 1].cpu().numpy().astype("int64")
+        e1 = int(ip[-1])
+        return dict(indptr=ip, indices=self.indices[:e1].cpu().numpy(), values=self.values[:e1].cpu().numpy(),
+                    x=self.x.cpu().numpy(), nnz=e1, d=self.d,
+                    sample="rows [0,%d) of %d (%d of %d edges), forward SpMM, full feature matrix" % (hi, self.n, e1, self.nnz))
 
     def verify(self):
         t, ops = self.torch, self.ops
@@ -496,7 +518,7 @@ def scipy_sanity(sample, max_edges=4_000_000):
             "sample": "rows [0,%d) (%d edges)" % (rows, e), "seconds": round(dt, 3)}
 
 
-WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload}
+WORKLOADS = {"spmm": SpmmWorkload, "gat": GatWorkload, "rgcn": RgcnWorkload, "uniform": UniformWorkload}
 
 
 def cpu_baseline_partitioned(dev, n, e, d, repeats=5, min_seconds=10.0):
@@ -847,8 +869,8 @@ def run_single(args):
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     dev = torch.device("cuda", torch.cuda.current_device())
     kw = {}
-    if args.scale and args.workload in ("spmm", "gat"):
-        base_n, base_e = (1 << 21, 1 << 26) if args.workload == "spmm" else (1 << 20, 1 << 25)
+    if args.scale and args.workload in ("spmm", "gat", "uniform"):
+        base_n, base_e = {"spmm": (1 << 21, 1 << 26), "gat": (1 << 20, 1 << 25), "uniform": (1 << 23, 1 << 27)}[args.workload]
         kw = dict(n=base_n >> args.scale, e=base_e >> args.scale)
     wl = WORKLOADS[args.workload](dev, **kw)
 
@@ -932,7 +954,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "partitioned", "refgpu", "layers", "reorder"])
+    ap.add_argument("--workload", default=None, choices=["spmm", "gat", "rgcn", "uniform", "partitioned", "refgpu", "layers", "reorder"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=int, default=0, help="shrink the graph by 2^SCALE (profiling / development)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
