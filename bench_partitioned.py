@@ -204,7 +204,7 @@ def run(args):
         if mode.startswith("push"):  # "push", "push1".."push4": at most that many passes; "pushnp": no priority rank; "pushsp": the priority
             # rank aggregates in a single pass
             kw = dict(max_passes=int(mode[4:]) if mode[4:].isdigit() else 3,
-                      priority=None if mode.endswith("np") else "auto", priority_own_first=not mode.endswith("sp"))
+                      priority=None if mode.endswith("np") else "auto", priority_own_first=False if mode.endswith("sp") else "auto")
             mode = "push"
         r = ShardOnOneGpu(shard, n, d, dev) if one_shard else PartitionedSpmm(shard, d, dev, mode=mode, **kw)
         r.x_local.copy_(x_shard)

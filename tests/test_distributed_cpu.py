@@ -115,7 +115,11 @@ def _worker(rank, world, port, errors):
             assert rank in my[0][0], "own sources belong to the first pass"
             if prio == world - 1 and rank == prio:
                 # its own sources while it waits for its delivery, then every other owner in one pass
-                assert my == [([rank], PushSchedule.PRIORITY), ([p for p in range(world) if p != rank], PushSchedule.PRIORITY)]
+                forced = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_passes=max_passes,
+                                      priority=prio, priority_own_first=True)
+                assert forced.passes[rank] == [([rank], PushSchedule.PRIORITY),
+                                               ([p for p in range(world) if p != rank], PushSchedule.PRIORITY)]
+                assert my in (forced.passes[rank], [(list(range(world)), PushSchedule.PRIORITY)])
                 single = PushSchedule(need_rows, [b_.tolist() for b_ in blocks], rows_per_rank, d, max_passes=max_passes,
                                       priority=prio, priority_own_first=False)
                 assert single.passes[rank] == [(list(range(world)), PushSchedule.PRIORITY)]

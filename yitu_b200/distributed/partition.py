@@ -89,9 +89,10 @@ class PushSchedule:
     (the shard with by far the most destination rows on a skewed graph): it cannot afford to wait for the slowest
     owner, and a second pass over its many rows costs more than it gains.
 
-    Cuts and the priority rank are chosen by exhaustive search over a linear cost model, per edge and per
-    destination row of a pass; the constants are fitted to B200 measurements of the 128-feature workload
-    (0.055 ns per edge, 0.35 ns per row, 690 GB/s out of one GPU) and only have to rank the alternatives.
+    Cuts and the priority rank are chosen by exhaustive search over a cost model of a pass (`pass_ms`: the cost
+    of an edge grows from 0.05 ns on long rows to 0.17 ns where a row holds an edge or less) and of a push
+    (690 GB/s out of one GPU), fitted to B200 measurements of the 128-feature workload; the model only has to rank
+    the alternatives.
 
     need_rows[q][p]   rows that rank q needs from owner p          (every rank holds the same matrix)
     block_edges[q][p] edges of rank q whose source row owner p holds
@@ -101,16 +102,24 @@ class PushSchedule:
     PRIORITY = -2
 
     def __init__(self, need_rows, block_edges, rows, d, max_passes=3, egress_gbs=690.0, sync_ms=0.03,
-                 ns_per_edge=0.055, ns_per_row=0.35, ns_per_row_again=0.03, priority="auto", priority_own_first=True):
+                 priority="auto", priority_own_first="auto"):
         import itertools
         P = len(rows)
         self.world, self.d = P, int(d)
         scale = d / 128.0
-        c_e, c_r, c_w = ns_per_edge * scale * 1e-6, ns_per_row * 1e-6, ns_per_row_again * scale * 1e-6
         row_ms = 4.0 * d / (egress_gbs * 1e9) * 1e3  # one feature row over one link direction
         need = [[0 if p == q else int(need_rows[q][p]) for p in range(P)] for q in range(P)]
         self.egress_rows = [sum(need[q][p] for q in range(P)) for p in range(P)]
         total_edges = [sum(int(e) for e in block_edges[q]) for q in range(P)]
+
+        def pass_ms(edges, n_rows, first):
+            """Aggregation pass over `edges` edges spread over n_rows destination rows, fitted to the edge-stream and
+            warp-per-row kernels on B200 at 128 features: 0.05 ns per edge of a long row, up to 0.17 ns where rows hold
+            an edge or less (short rows are cold gathers), plus writing (first pass) or visiting the rows."""
+            if edges <= 0:
+                return 0.0
+            per_edge = 0.05 + 0.12 * (n_rows / float(edges)) ** 0.7
+            return (edges * per_edge * scale + n_rows * (0.09 * scale if first else 0.047)) * 1e-6
 
         def plan_reader(q, push_ms):
             """Best cuts for reader q: (finish time, [(owners, time the pass may start)])."""
@@ -125,7 +134,7 @@ class PushSchedule:
                     for own_alone in ((False, True) if n and block_edges[q][q] > 0 and k < max_passes else (False,)):
                         t, plan = 0.0, []
                         if own_alone:
-                            t = c_e * int(block_edges[q][q]) + c_r * rows[q]
+                            t = pass_ms(int(block_edges[q][q]), rows[q], True)
                             plan.append(([q], 0.0))
                         for gi, grp in enumerate(groups):
                             edges = sum(int(block_edges[q][p]) for p in grp)
@@ -134,7 +143,7 @@ class PushSchedule:
                                 edges += int(block_edges[q][q])
                                 members = [q] + members
                             start = max([push_ms[p] + sync_ms for p in grp] + [0.0])
-                            t = max(t, start) + c_e * edges + c_r * rows[q] + (c_w * rows[q] if plan else 0.0)
+                            t = max(t, start) + pass_ms(edges, rows[q], not plan)
                             plan.append((members, start))
                         if best_q is None or t < best_q[0] - 1e-9:
                             best_q = (t, plan)
@@ -143,7 +152,7 @@ class PushSchedule:
             return t, plan
 
         if priority == "auto":
-            heavy = max(range(P), key=lambda q: c_e * total_edges[q] + c_r * rows[q])
+            heavy = max(range(P), key=lambda q: pass_ms(total_edges[q], rows[q], True))
             prio_options = [None, heavy] if P > 2 else [None]
         else:
             prio_options = [priority]
@@ -158,13 +167,15 @@ class PushSchedule:
                        for p in range(P)]
             worst, plans = 0.0, []
             for q in range(P):
-                if q == prio and priority_own_first and 0 < block_edges[q][q] < total_edges[q]:
-                    # the edges whose sources it owns while it waits for its delivery, then everything else in one pass
-                    t_own = c_e * int(block_edges[q][q]) + c_r * rows[q]
-                    t = max(prio_ready, t_own) + c_e * (total_edges[q] - int(block_edges[q][q])) + (c_r + c_w) * rows[q]
-                    plan = [([q], 0.0), ([p for p in range(P) if p != q], prio_ready)]
-                elif q == prio:  # one pass, as soon as its rows are in
-                    t, plan = prio_ready + c_e * total_edges[q] + c_r * rows[q], [(list(range(P)), prio_ready)]
+                if q == prio:
+                    # one pass as soon as its rows are in - or the edges whose sources it owns while it waits, then
+                    # everything else in one pass; whichever the model ends earlier
+                    t, plan = prio_ready + pass_ms(total_edges[q], rows[q], True), [(list(range(P)), prio_ready)]
+                    own = int(block_edges[q][q])
+                    if priority_own_first and 0 < own < total_edges[q]:
+                        t2 = max(prio_ready, pass_ms(own, rows[q], True)) + pass_ms(total_edges[q] - own, rows[q], False)
+                        if priority_own_first is True or t2 < t:
+                            t, plan = t2, [([q], 0.0), ([p for p in range(P) if p != q], prio_ready)]
                 else:
                     t, plan = plan_reader(q, push_ms)
                 plans.append(plan)
@@ -172,7 +183,7 @@ class PushSchedule:
             if best is None or worst < best[0] - 1e-6:  # ties: no priority rank
                 best = (worst, plans, prio, push_ms)
         self.model_ms, plans, self.priority, self.push_ms = best
-        # passes[q]: list of (owners whose edges the pass takes, PRIORITY for the priority rank's single pass, else
+        # passes[q]: list of (owners whose edges the pass takes, PRIORITY for the priority rank's passes, else
         # the pass number)
         self.passes = [[(owners, self.PRIORITY if q == self.priority else j) for j, (owners, _) in enumerate(plan)]
                        for q, plan in enumerate(plans)]

@@ -91,7 +91,7 @@ class PartitionedSpmm:
     peer mode the peers read it during THEIR step, so rewrite it only after a step(fence=True) or a barrier."""
 
     def __init__(self, shard, d, device, group=None, mode="push", weight_mode=ops.W_EDGE, max_passes=3,
-                 priority="auto", priority_own_first=True):
+                 priority="auto", priority_own_first="auto"):
         self.shard, self.d, self.device, self.group = shard, int(d), torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and mode != "local") else 1
         self.rank = shard.rank
@@ -134,7 +134,7 @@ class PartitionedSpmm:
                 self._setup_push(ptrs, max_passes, priority, priority_own_first)
 
     # ------------------------------------------------------------------------------------------ push set-up
-    def _setup_push(self, ptrs, max_passes, priority, priority_own_first=True):
+    def _setup_push(self, ptrs, max_passes, priority, priority_own_first="auto"):
         sh, plan, world, rank, d = self.shard, self.plan, self.world, self.rank, self.d
         need_rows, recv_ids, recv_counts = exchange_need_lists(plan, rank, world, self.group)
         mine = torch.tensor(owner_edge_counts(sh, world), dtype=torch.int64, device=self.device)
