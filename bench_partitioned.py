@@ -246,6 +246,8 @@ def run(args):
     events = []
     ms_step = _time_steps(runner, args.steps, world, events)
     clocks = sampler.stop() if rank == 0 else None
+    if hasattr(runner, "check"):
+        runner.check()  # raises if a wait for a peer's delivery ever ran out: the timed steps would be worthless
     value = nnz * d / (ms_step * 1e-3) / 1e9
 
     spmm_ms = [a.elapsed_time(b) for tag, a, b in events if tag == "spmm"]
