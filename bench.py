@@ -69,12 +69,24 @@ def load_traffic(key, kernel):
 
 
 def spmm_kernel_name(nnz, n_rows, d):
-    """The SpMM instantiation that yitu_spmm_csr_f32 picks for scalar weights and aligned rows of d floats: the
-    edge-stream kernel below 24 edges per row on average, the warp-per-row kernel otherwise."""
-    stream = nnz < 24 * n_rows and 64 < d <= 256
+    """The SpMM instantiation that yitu_spmm_csr_f32 picks for scalar weights and aligned rows of d floats: below 64
+    edges per row on average (24 for rows of more than 128 floats) the edge-stream kernel, with the chunks of hub rows
+    on the warp-per-row kernel; above, the warp-per-row kernel alone."""
+    split = nnz < (24 if d > 128 else 64) * n_rows and 64 < d <= 256
     if d > 128:
-        return "spmm_stream_kernel<8,4,16,true,true>" if stream else "spmm_kernel<32,1,8,4,false,true>"
-    return "spmm_stream_kernel<4,8,16,true,true>" if stream else "spmm_kernel<32,1,4,16,false,true>"
+        return "spmm_stream_kernel<8,4,16,true,true> (+ spmm_kernel<32,1,8,4,false,true> on hub chunks)" if split \
+            else "spmm_kernel<32,1,8,4,false,true>"
+    return "spmm_stream_kernel<4,8,16,true,true> (+ spmm_kernel<32,1,4,16,false,true> on hub chunks)" if split \
+        else "spmm_kernel<32,1,4,16,false,true>"
+
+
+def spmm_launches(nnz, n_rows, d, has_hub_plan):
+    """Kernels one scalar-weight SpMM call launches: the aggregation (two kernels where hub chunks and ordinary rows
+    go to different kernels, see spmm_kernel_name) and, with a hub schedule, the reduction of the chunk partials."""
+    if not has_hub_plan:
+        return 1
+    split = nnz < (24 if d > 128 else 64) * n_rows and 64 < d <= 256
+    return 3 if split else 2
 
 
 def roofline(kernel, algorithmic_bytes, avg_launch_ms, traffic_key, compulsory_bytes=None):
@@ -164,7 +176,8 @@ class SpmmWorkload:
         self.gout = torch.empty_like(self.x)
         self.g.plan(), self.gt.plan()
         self.units_per_step = 2 * self.nnz * d
-        self.launches_per_step = 2 * (1 + (1 if self.g.plan() else 0))
+        self.launches_per_step = (spmm_launches(self.nnz, n, d, bool(self.g.plan())) +
+                                  spmm_launches(self.nnz, n, d, bool(self.gt.plan())))
         self.kernel_launches_per_step = 2
         # algorithmic bytes of ONE SpMM launch: per edge a feature row, a column id and a weight; per row a
         # pointer and the written output row
@@ -431,7 +444,7 @@ class UniformWorkload:
         self.compulsory_bytes = self.nnz * 8 + (n + 1) * 8 + 2 * 4 * n * d
         self.traffic_key = "spmm_uniform_d128"
         self.dominant_kernel = spmm_kernel_name(self.nnz, n, d)
-        self.launches_per_step = 1 + (1 if self.g.plan() else 0)
+        self.launches_per_step = spmm_launches(self.nnz, n, d, bool(self.g.plan()))
         self.kernel_launches_per_step = 1
 
     def step(self, kernel_events=None):

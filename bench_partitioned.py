@@ -271,7 +271,7 @@ def run(args):
         graphs_used = [runner.graph]
     # this library's kernels per step on this rank: the gather / push kernels, one SpMM per pass and one hub
     # reduction for every pass whose graph has split rows
-    launches = n_move + sum(1 + (1 if g.plan() is not None else 0) for g in graphs_used)
+    launches = n_move + sum(bench.spmm_launches(g.nnz, g.n_rows, d, g.plan() is not None) for g in graphs_used)
     k_ms = sum(spmm_ms) / args.steps  # SpMM time per step on this rank (all passes)
     k_bytes = shard.nnz * (4 * d + 8) + (shard.n_local + 1) * 8 + 4 * shard.n_local * d
     by_owner = [0.0] * world  # bytes this rank receives from each owner per step

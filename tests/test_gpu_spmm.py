@@ -138,6 +138,16 @@ def test_stream_kernel_row_patterns(oracle, monkeypatch, pattern, D):
             out = _dev(base).clone()
             ops.spmm(g, _dev(x), out=out, accumulate=True, bias=_dev(bias), activation="relu", chunk_edges=chunk)
             assert_close(out.cpu().numpy(), ref_acc_epi, what=tag + " accumulate+epilogue")
+    # the default dispatch: hub chunks on the warp-per-row kernel, every other row on the edge-stream kernel
+    monkeypatch.setenv("YITU_SPMM_STREAM", "1")
+    monkeypatch.delenv("YITU_SPMM_STREAM_ROWS", raising=False)
+    monkeypatch.delenv("YITU_SPMM_STREAM_EU", raising=False)
+    g = ops.PreparedGraph(_dev(indptr, torch.int64), _dev(indices), n_cols)
+    got = ops.spmm(g, _dev(x), mode=ops.W_NODE, norm_dst=_dev(nd), norm_src=_dev(ns), chunk_edges=chunk)
+    assert_close(got.cpu().numpy(), ref_node, what="split %s D=%d node" % (pattern, D))
+    out = _dev(base).clone()
+    ops.spmm(g, _dev(x), out=out, accumulate=True, bias=_dev(bias), activation="relu", chunk_edges=chunk)
+    assert_close(out.cpu().numpy(), ref_acc_epi, what="split %s D=%d accumulate+epilogue" % (pattern, D))
     # the warp-per-row kernel on the same inputs gives the same sums up to the order of the additions
     monkeypatch.setenv("YITU_SPMM_STREAM", "0")
     g = ops.PreparedGraph(_dev(indptr, torch.int32), _dev(indices), n_cols)

@@ -41,7 +41,9 @@ struct SpmmParams {
     int64_t xs;
     float *out;
     int64_t os;
-    int64_t n_chunks;
+    int64_t n_chunks;     // chunks of the hub schedule (> 0: rows longer than chunk_edges are not aggregated as rows)
+    int64_t chunk_tasks;  // how many of them THIS launch aggregates (its first groups): n_chunks, or 0
+    int64_t row_tasks;    // rows THIS launch aggregates: n_rows, or 0 for a launch that takes the chunks only
     int chunk_edges;
     const int *chunk_row;
     const int64_t *chunk_begin;
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
     int64_t row, eb, ee;
     float *dst;
     bool raw;
-    if (gid < p.n_chunks) {
+    if (gid < p.chunk_tasks) {
         row = __ldg(p.chunk_row + gid);
         eb = __ldg(p.chunk_begin + gid);
         const int64_t rend = load_ptr(p.indptr, p.is64, row + 1);
@@ -83,8 +85,8 @@ __global__ void __launch_bounds__(256) spmm_kernel(const __grid_constant__ SpmmP
         dst = p.scratch + gid * p.D;
         raw = true;
     } else {
-        row = gid - p.n_chunks;
-        if (row >= p.n_rows) return;
+        row = gid - p.chunk_tasks;
+        if (row >= p.row_tasks) return;
         eb = load_ptr(p.indptr, p.is64, row);
         ee = load_ptr(p.indptr, p.is64, row + 1);
         if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;  // hub row: done by its chunks
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(256) spmm_wide_kernel(const __grid_constant__ 
     int64_t row, eb, ee;
     float *dst;
     bool raw;
-    if (gid < p.n_chunks) {
+    if (gid < p.chunk_tasks) {
         row = __ldg(p.chunk_row + gid);
         eb = __ldg(p.chunk_begin + gid);
         const int64_t rend = load_ptr(p.indptr, p.is64, row + 1);
@@ -231,8 +233,8 @@ __global__ void __launch_bounds__(256) spmm_wide_kernel(const __grid_constant__ 
         dst = p.scratch + gid * p.D;
         raw = true;
     } else {
-        row = gid - p.n_chunks;
-        if (row >= p.n_rows) return;
+        row = gid - p.chunk_tasks;
+        if (row >= p.row_tasks) return;
         eb = load_ptr(p.indptr, p.is64, row);
         ee = load_ptr(p.indptr, p.is64, row + 1);
         if (p.n_chunks > 0 && ee - eb > p.chunk_edges) return;
@@ -346,7 +348,7 @@ __global__ void __launch_bounds__(128, (VEC * EU <= 32) ? 6 : 4) spmm_stream_ker
     int64_t r0, E0;
     int nr, rp;
     bool raw;
-    if (gid < p.n_chunks) {  // one chunk of a hub row: a one-row batch whose sum goes to scratch
+    if (gid < p.chunk_tasks) {  // one chunk of a hub row: a one-row batch whose sum goes to scratch
         raw = true;
         nr = 1;
         r0 = __ldg(p.chunk_row + gid);
@@ -355,8 +357,8 @@ __global__ void __launch_bounds__(128, (VEC * EU <= 32) ? 6 : 4) spmm_stream_ker
         rp = lane == 0 ? 0 : static_cast<int>(min(static_cast<int64_t>(p.chunk_edges), rend - E0));
     } else {
         raw = false;
-        r0 = (gid - p.n_chunks) * R;
-        if (r0 >= p.n_rows) return;
+        r0 = (gid - p.chunk_tasks) * R;
+        if (r0 >= p.row_tasks) return;
         nr = static_cast<int>(min(static_cast<int64_t>(R), p.n_rows - r0));
         const int64_t myptr = load_ptr(p.indptr, p.is64, r0 + min(lane, nr));
         E0 = __shfl_sync(FULL, myptr, 0);
@@ -548,8 +550,8 @@ __global__ void __launch_bounds__(128) hub_reduce_kernel(const __grid_constant__
 static int block_threads() { return 128; }
 
 template <int LPR, int NV, int VEC, int EU, int EU_HEAD = 4>
-static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
-    const int64_t groups = p.n_chunks + p.n_rows;
+static int launch(const SpmmParams &p, bool per_head, cudaStream_t st, bool reduce = true) {
+    const int64_t groups = p.chunk_tasks + p.row_tasks;
     if (groups == 0) return YITU_OK;
     const int threads = block_threads();
     const int gpb = threads / LPR;
@@ -568,7 +570,7 @@ static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
         else spmm_kernel<LPR, NV, VEC, EU, false, false><<<grid, threads, 0, st>>>(p);
     }
     YITU_LAUNCH_CHECK();
-    if (p.n_chunks > 0) {
+    if (reduce && p.n_chunks > 0) {
         hub_reduce_kernel<<<static_cast<unsigned>(p.n_chunks), 128, 0, st>>>(p);
         YITU_LAUNCH_CHECK();
     }
@@ -576,8 +578,8 @@ static int launch(const SpmmParams &p, bool per_head, cudaStream_t st) {
 }
 
 template <int VEC, int EU, int R>
-static int launch_stream(const SpmmParams &p, cudaStream_t st) {
-    const int64_t groups = p.n_chunks + (p.n_rows + R - 1) / R;
+static int launch_stream(const SpmmParams &p, cudaStream_t st) {  // always followed by the hub reduction, if any
+    const int64_t groups = p.chunk_tasks + (p.row_tasks + R - 1) / R;
     if (groups == 0) return YITU_OK;
     const int threads = block_threads();
     const int64_t gx = (groups + threads / 32 - 1) / (threads / 32);
@@ -625,7 +627,7 @@ static int dispatch_stream(const SpmmParams &p, cudaStream_t st, int rows_dflt, 
 
 template <int LPE, int EU>
 static int launch_wide(const SpmmParams &p, cudaStream_t st) {
-    const int64_t groups = p.n_chunks + p.n_rows;
+    const int64_t groups = p.chunk_tasks + p.row_tasks;
     if (groups == 0) return YITU_OK;
     const int threads = block_threads();
     const int64_t gx = (groups + threads / 32 - 1) / (threads / 32);
@@ -679,13 +681,14 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     p.norm_dst = a->norm_dst; p.norm_src = a->norm_src; p.row_scale = a->row_scale; p.alpha = a->alpha;
     p.x = a->x; p.xs = a->x_stride; p.out = a->out; p.os = a->out_stride;
     p.bias = a->bias; p.act = a->activation; p.xshared = a->x_shared_heads ? 1 : 0;
+    p.row_tasks = g.n_rows;
     if (a->plan && a->plan->n_chunks > 0) {
         YITU_REQUIRE(a->plan->chunk_edges >= 32, YITU_ERR_INVALID_ARG, "plan.chunk_edges must be >= 32");
         YITU_REQUIRE(a->plan->chunk_row && a->plan->chunk_begin, YITU_ERR_INVALID_ARG, "plan tables are NULL");
         YITU_REQUIRE(a->scratch != nullptr && a->scratch_bytes >= a->plan->n_chunks * D * 4, YITU_ERR_WORKSPACE,
                      "scratch needs %lld bytes, got %lld", (long long)(a->plan->n_chunks * D * 4),
                      (long long)a->scratch_bytes);
-        p.n_chunks = a->plan->n_chunks; p.chunk_edges = a->plan->chunk_edges;
+        p.n_chunks = a->plan->n_chunks; p.chunk_tasks = p.n_chunks; p.chunk_edges = a->plan->chunk_edges;
         p.chunk_row = a->plan->chunk_row; p.chunk_begin = a->plan->chunk_begin; p.scratch = a->scratch;
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -700,17 +703,32 @@ extern "C" int yitu_spmm_csr_f32(const yitu_spmm_args_t *a, yitu_stream_t stream
     // aligned; measured 6.20 ms against 6.44 ms with 128-bit loads on the D=256 R-MAT workload.  Narrower rows would
     // need half-warp groups, which lose more than the wider loads gain.
     const auto aligned32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
-    // Edge-stream kernel for graphs of short rows (fewer than 24 edges per row on average), the warp-per-row kernel
-    // otherwise.  Measured on B200 with 128 features and 65.1 M edges: 7.27 M rows (9 edges per row) 5.60 ms
-    // against 6.40 ms; 82 k rows (800 per row, nearly all in hub chunks) 3.85 ms against 3.43 ms - the stream kernel
-    // holds more state per warp (80 registers, 24 resident warps against 32) and that costs on long rows; at 31 edges
-    // per row the two are equal (34.77 / 34.83 ms on 520.8 M edges).
+    // YITU_SPMM_STREAM (development switch): 0 warp-per-row kernel for everything; 2 edge-stream kernel for everything it
+    // covers, hub chunks included; 3 one of the two by average row length (stream below 24 edges per row);
+    // 1 (default) both: the chunks of the hub rows go to the warp-per-row kernel - long uniform tasks, where its 32
+    // resident warps at 64 registers win - and all other rows to the edge-stream kernel, in two launches on the stream;
+    // for graphs below 64 edges per row (24 for rows of more than 128 floats), the warp-per-row kernel alone above.
+    // Measured on B200, 128 features (ms: warp per row / both / stream alone): R-MAT 16.8 M rows x 31 edges 34.70 /
+    // 32.60 / 35.00; its 8-way shards of 65 M edges each: 7.27 M rows 6.49 / 5.51 / 5.64, 3.07 M rows 4.89 / 4.61 / 4.76,
+    // 1.20 M rows 4.17 / 4.23 / 4.41, 82 k rows (795 per row) 3.43 / 3.68 / 4.03.  256 features, 2.1 M rows x 30: 6.08 /
+    // 6.17 / 6.18.  Uniform graph, 16 edges per row, no hubs: 11.83 / - / 10.74.
     const int stream_mode = env_int("YITU_SPMM_STREAM", 1);
-    const bool stream_ok = !per_head && g.nnz < (1ll << 31) &&
-                           (stream_mode == 2 || (stream_mode == 1 && g.nnz < 24 * g.n_rows));
-    if (stream_ok && D > 128 && D <= 256 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 &&
-        aligned32(a->x) && aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch)))
-        return dispatch_stream<8, 4, 8>(p, st, 16, 4);
+    const bool stream_shape = !per_head && g.nnz < (1ll << 31);
+    const bool stream_ok = stream_shape && (stream_mode == 2 || (stream_mode == 3 && g.nnz < 24 * g.n_rows));
+    const bool split = stream_shape && stream_mode == 1 && g.nnz < (D > 128 ? 24 : 64) * g.n_rows;
+    const bool wide256 = D > 128 && D <= 256 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 &&
+                         aligned32(a->x) && aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch));
+    if (split && (wide256 || (D > 64 && D <= 128))) {
+        if (p.n_chunks > 0) {
+            SpmmParams c = p;
+            c.row_tasks = 0;  // the chunks only; the reduction follows the second launch
+            if (int rc = wide256 ? launch<32, 1, 8, 4>(c, false, st, false) : launch<32, 1, 4, 16>(c, false, st, false)) return rc;
+        }
+        SpmmParams r = p;
+        r.chunk_tasks = 0;  // the rows that are not cut into chunks (those are stepped over), then the reduction
+        return wide256 ? dispatch_stream<8, 4, 8>(r, st, 16, 4) : dispatch_stream<4, 8, 16>(r, st, 16, 8);
+    }
+    if (stream_ok && wide256) return dispatch_stream<8, 4, 8>(p, st, 16, 4);
     if (stream_ok && D > 64 && D <= 128) return dispatch_stream<4, 8, 16>(p, st, 16, 8);
     if (D > 128 && D <= 512 && D % 8 == 0 && a->x_stride % 8 == 0 && a->out_stride % 8 == 0 && aligned32(a->x) &&
         aligned32(a->out) && (p.scratch == nullptr || aligned32(p.scratch)) && (!per_head || a->n_feats % 8 == 0)) {
